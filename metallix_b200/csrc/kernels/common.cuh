@@ -1,0 +1,66 @@
+// Shared device helpers for the hand-written kernels: element types, loads
+// that widen to float, warp and block reductions with a fixed order.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace mxb {
+
+// Element type codes of the C interface.
+enum DType : int { kF32 = 0, kBF16 = 1 };
+
+// Bits of the device status word that kernels set instead of trapping.
+enum StatusBit : int {
+  kStatusBadTokenId = 1,    // a token id outside the vocabulary
+  kStatusBadSlot = 2,       // a cache slot outside the pool
+  kStatusBadPage = 4,       // a block-table entry outside the pool
+  kStatusNonFinite = 8,     // a non-finite logit where a token was picked
+  kStatusWaitTimeout = 16,  // a bounded wait (mbarrier) ran out
+};
+
+__device__ __forceinline__ float to_float(float v) { return v; }
+__device__ __forceinline__ float to_float(__nv_bfloat16 v) { return __bfloat162float(v); }
+
+template <typename T> __device__ __forceinline__ T from_float(float v);
+template <> __device__ __forceinline__ float from_float<float>(float v) { return v; }
+template <> __device__ __forceinline__ __nv_bfloat16 from_float<__nv_bfloat16>(float v) {
+  return __float2bfloat16_rn(v);
+}
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int offset = 16; offset > 0; offset >>= 1) v += __shfl_xor_sync(0xffffffffu, v, offset);
+  return v;
+}
+
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+  for (int offset = 16; offset > 0; offset >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, offset));
+  return v;
+}
+
+// Sum over a block of up to 1024 threads; every thread gets the result. The
+// order of additions depends only on the block size.
+__device__ __forceinline__ float block_sum(float v, float* scratch /* >= 33 floats */) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int warps = (blockDim.x + 31) >> 5;
+  v = warp_sum(v);
+  __syncthreads();
+  if (lane == 0) scratch[warp] = v;
+  __syncthreads();
+  if (warp == 0) {
+    float t = lane < warps ? scratch[lane] : 0.0f;
+    t = warp_sum(t);
+    if (lane == 0) scratch[32] = t;
+  }
+  __syncthreads();
+  return scratch[32];
+}
+
+inline int ceil_div(int a, int b) { return (a + b - 1) / b; }
+
+}  // namespace mxb
+
+#define MXB_API extern "C" __attribute__((visibility("default")))

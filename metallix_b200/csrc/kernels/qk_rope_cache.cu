@@ -1,0 +1,127 @@
+// Per-head q/k RMSNorm, rotate-half RoPE and the write of K and V into the
+// paged cache, in one pass over the projected q, k and v.
+//
+// Replaces, per layer, the reference's two fast::rms_norm calls, two
+// fast::rope calls (crates/models/qwen/src/forward.rs:2031-2062) and the pool
+// scatter (crates/models/qwen/src/forward/paged.rs:300-325). Norm and rotation
+// run in float32; cos and sin come from a table built in float64.
+//
+// Cache layout of one layer: [pages, 2 (K, V), kv_heads, page_tokens, head_dim];
+// position p of a request lives in page table[p / page_tokens] at row
+// p % page_tokens, which the caller passes flattened as slot = page *
+// page_tokens + row.
+#include "common.cuh"
+
+namespace mxb {
+
+template <typename T>
+__global__ void qk_norm_rope_cache_kernel(
+    const T* __restrict__ q_in, const T* __restrict__ k_in, const T* __restrict__ v_in,
+    long long q_stride, long long k_stride, long long v_stride,  // row strides in elements
+    T* __restrict__ q_out,                                        // [tokens, heads, head_dim]
+    T* __restrict__ cache, const int* __restrict__ slots,         // slots may be null: no write
+    const int* __restrict__ positions,
+    const float* __restrict__ q_weight, const float* __restrict__ k_weight,  // null: no norm
+    const float* __restrict__ cos_table, const float* __restrict__ sin_table,  // null: no rotation
+    int table_positions, int rotary_dim, int heads, int kv_heads, int head_dim, int page_tokens,
+    int num_pages, float eps, int* status) {
+  extern __shared__ float head[];  // head_dim values
+  __shared__ float scratch[33];
+  const int t = blockIdx.x;
+  const int h = blockIdx.y;  // 0..heads-1: q, then kv_heads of k, then kv_heads of v
+  const bool is_q = h < heads;
+  const bool is_k = !is_q && h < heads + kv_heads;
+  const int kv = is_q ? 0 : (is_k ? h - heads : h - heads - kv_heads);
+
+  const T* src = is_q ? q_in + t * q_stride + static_cast<long long>(h) * head_dim
+               : is_k ? k_in + t * k_stride + static_cast<long long>(kv) * head_dim
+                      : v_in + t * v_stride + static_cast<long long>(kv) * head_dim;
+
+  T* dst = nullptr;
+  if (is_q) {
+    if (q_out == nullptr) return;
+    dst = q_out + (static_cast<size_t>(t) * heads + h) * head_dim;
+  } else {
+    if (slots == nullptr || cache == nullptr) return;
+    const int slot = slots[t];
+    if (slot < 0) return;  // this token does not write the cache
+    const int page = slot / page_tokens, row = slot - page * page_tokens;
+    if (page >= num_pages) {
+      if (threadIdx.x == 0) atomicOr(status, kStatusBadSlot);
+      return;
+    }
+    dst = cache + (((static_cast<size_t>(page) * 2 + (is_k ? 0 : 1)) * kv_heads + kv) * page_tokens + row) * head_dim;
+  }
+
+  if (!is_q && !is_k) {  // values are stored as projected
+    for (int i = threadIdx.x; i < head_dim; i += blockDim.x) dst[i] = src[i];
+    return;
+  }
+
+  const float* weight = is_q ? q_weight : k_weight;
+  float sum = 0.0f;
+  for (int i = threadIdx.x; i < head_dim; i += blockDim.x) {
+    const float v = to_float(src[i]);
+    head[i] = v;
+    sum += v * v;
+  }
+  if (weight != nullptr) {
+    sum = block_sum(sum, scratch);
+    const float scale = rsqrtf(sum / static_cast<float>(head_dim) + eps);
+    for (int i = threadIdx.x; i < head_dim; i += blockDim.x) head[i] = head[i] * scale * weight[i];
+  }
+  __syncthreads();
+
+  const int half = rotary_dim >> 1;
+  int pos = positions[t];
+  const bool rotate = cos_table != nullptr;
+  if (rotate && (pos < 0 || pos >= table_positions)) {
+    if (threadIdx.x == 0) atomicOr(status, kStatusBadSlot);
+    pos = 0;
+  }
+  for (int i = threadIdx.x; i < head_dim; i += blockDim.x) {
+    float out = head[i];
+    if (rotate && i < rotary_dim) {
+      const int j = i < half ? i : i - half;
+      const float c = cos_table[static_cast<size_t>(pos) * half + j];
+      const float s = sin_table[static_cast<size_t>(pos) * half + j];
+      // out[i] = x[i] cos - x[i + half] sin; out[i + half] = x[i + half] cos + x[i] sin
+      out = i < half ? head[i] * c - head[i + half] * s : head[i] * c + head[i - half] * s;
+    }
+    dst[i] = from_float<T>(out);
+  }
+}
+
+}  // namespace mxb
+
+using namespace mxb;
+
+MXB_API int mxb_qk_norm_rope_cache(
+    const void* q_in, const void* k_in, const void* v_in, long long q_stride, long long k_stride,
+    long long v_stride, void* q_out, void* cache, const int* slots, const int* positions,
+    const float* q_weight, const float* k_weight, const float* cos_table, const float* sin_table,
+    int table_positions, int rotary_dim, int tokens, int heads, int kv_heads, int head_dim,
+    int page_tokens, int num_pages, float eps, int dtype, int* status, cudaStream_t stream) {
+  if (tokens <= 0) return 0;
+  if (rotary_dim < 0 || rotary_dim > head_dim || (rotary_dim & 1)) return static_cast<int>(cudaErrorInvalidValue);
+  int threads = 32;
+  while (threads < head_dim && threads < 256) threads <<= 1;
+  dim3 grid(tokens, heads + 2 * kv_heads);
+  const size_t shared = static_cast<size_t>(head_dim) * sizeof(float);
+  if (dtype == kF32)
+    qk_norm_rope_cache_kernel<float><<<grid, threads, shared, stream>>>(
+        static_cast<const float*>(q_in), static_cast<const float*>(k_in), static_cast<const float*>(v_in),
+        q_stride, k_stride, v_stride, static_cast<float*>(q_out), static_cast<float*>(cache), slots,
+        positions, q_weight, k_weight, cos_table, sin_table, table_positions, rotary_dim, heads,
+        kv_heads, head_dim, page_tokens, num_pages, eps, status);
+  else if (dtype == kBF16)
+    qk_norm_rope_cache_kernel<__nv_bfloat16><<<grid, threads, shared, stream>>>(
+        static_cast<const __nv_bfloat16*>(q_in), static_cast<const __nv_bfloat16*>(k_in),
+        static_cast<const __nv_bfloat16*>(v_in), q_stride, k_stride, v_stride,
+        static_cast<__nv_bfloat16*>(q_out), static_cast<__nv_bfloat16*>(cache), slots, positions,
+        q_weight, k_weight, cos_table, sin_table, table_positions, rotary_dim, heads, kv_heads,
+        head_dim, page_tokens, num_pages, eps, status);
+  else
+    return static_cast<int>(cudaErrorInvalidValue);
+  return static_cast<int>(cudaGetLastError());
+}

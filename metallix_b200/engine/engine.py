@@ -1,0 +1,271 @@
+"""The engine: a model, its cache and the one step function.
+
+``Engine.step`` takes a batch of (request, its next tokens) entries: portions
+of prompts beside single decoded tokens, cut anywhere. It runs only those
+tokens, as one packed batch, against the cache that earlier steps left, and
+returns float32 logits at the wanted places. The reference runs prompt
+portions and decode rows as separate forward passes
+(crates/models/qwen/src/forward/paged.rs:570 and :741); here they share one.
+
+Protocol per step, as in crates/core/engine/src/blocks.rs:17-45: everything is
+checked first and nothing changes on a refusal; then pages are reserved for
+every entry, the forward pass writes them, and the positions are committed. A
+failure after the reservation rolls every entry of the step back.
+"""
+from __future__ import annotations
+
+import os
+from dataclasses import dataclass, field
+from typing import Dict, Hashable, List, Optional, Sequence
+
+import numpy as np
+import torch
+
+from .. import ops
+from ..cache import PagedCache
+from ..config import read_config
+from ..parts.registry import Runtime, StepContext
+from ..weights import load_tensors, random_tensors
+from .model import DecoderModel
+
+_DTYPES = {"bfloat16": torch.bfloat16, "bf16": torch.bfloat16, "float32": torch.float32,
+           "fp32": torch.float32, torch.bfloat16: torch.bfloat16, torch.float32: torch.float32}
+ATTENTION_TILE = 16  # query tokens per attention tile (csrc/kernels/attention_tile.cu)
+
+
+class StepError(ValueError):
+    """A batch the step function refuses; nothing was changed."""
+
+
+@dataclass
+class StepEntry:
+    """One request's share of a step: its next ``tokens`` and the indices
+    among them (``want``) whose logits are asked for."""
+
+    request: Hashable
+    tokens: Sequence[int]
+    want: Sequence[int] = field(default_factory=tuple)
+
+
+def resolve_dtype(dtype) -> torch.dtype:
+    if dtype not in _DTYPES:
+        raise ValueError(f"dtype must be bfloat16 or float32, got {dtype!r}")
+    return _DTYPES[dtype]
+
+
+class Engine:
+    def __init__(self, config, tensors: Dict[str, torch.Tensor], dtype="bfloat16",
+                 page_tokens: int = 16, num_pages: Optional[int] = None,
+                 max_tokens: Optional[int] = None, max_requests: int = 64,
+                 max_context: Optional[int] = None, device="cuda:0", gemm_backend: str = "auto",
+                 spec=None):
+        ops.require_cuda()
+        self.config = config
+        self.device = torch.device(device)
+        self.dtype = resolve_dtype(dtype)
+        self.spec = spec if spec is not None else config.to_model_spec()
+        self.max_context = min(max_context or self.spec.max_positions, self.spec.max_positions)
+        if self.dtype == torch.float32:
+            # True 32-bit everywhere: no reduced-precision matrix mode for
+            # anything torch may run on this path.
+            torch.backends.cuda.matmul.allow_tf32 = False
+            torch.backends.cudnn.allow_tf32 = False
+        self.runtime = Runtime(device=self.device, dtype=self.dtype, max_positions=self.max_context,
+                               gemm_backend=gemm_backend)
+        self.model = DecoderModel(self.spec, tensors, self.runtime)
+        if num_pages is None:
+            tokens = max_tokens if max_tokens is not None else min(self.max_context, 4096) * 4
+            num_pages = -(-tokens // page_tokens)
+        self.cache = PagedCache(self.model.cache_needs(), page_tokens, num_pages, max_requests,
+                                self.dtype, self.device)
+        self.manager = self.cache.manager
+        self._ids: Dict[Hashable, int] = {}   # request name -> manager id
+        self._next_id = 0
+        self.steps = 0
+
+    # ----------------------------------------------------------- construction
+    @classmethod
+    def from_folder(cls, model_dir: str, **options) -> "Engine":
+        """A model folder (config.json + *.safetensors); the model class is
+        chosen by config.json."""
+        config = read_config(model_dir)
+        device = options.get("device", "cuda:0")
+        ops.require_cuda()
+        tensors = load_tensors(model_dir, config, device=device)
+        return cls(config, tensors, **options)
+
+    @classmethod
+    def from_random(cls, config, seed: int, **options) -> "Engine":
+        """Random weights from ``seed`` made directly on the device."""
+        ops.require_cuda()
+        dtype = resolve_dtype(options.get("dtype", "bfloat16"))
+        name = "bfloat16" if dtype == torch.bfloat16 else "float32"
+        tensors = random_tensors(config, seed, dtype=name, device=options.get("device", "cuda:0"))
+        return cls(config, tensors, **options)
+
+    # ---------------------------------------------------------------- requests
+    def live(self, request: Hashable) -> bool:
+        return request in self._ids
+
+    def context_length(self, request: Hashable) -> int:
+        return self.manager.computed(self._ids[request]) if request in self._ids else 0
+
+    def release(self, request: Hashable) -> None:
+        """Gives back everything the request holds."""
+        if request in self._ids:
+            self.manager.release(self._ids.pop(request))
+
+    def release_all(self) -> None:
+        for request in list(self._ids):
+            self.release(request)
+
+    # -------------------------------------------------------------------- step
+    def step(self, entries: Sequence[StepEntry]) -> Optional[torch.Tensor]:
+        """Runs one batch. Returns float32 logits ``[wanted, vocab]`` on the
+        device in the order of the entries and of each entry's ``want``, or
+        None if nothing is wanted. Call ``check()`` after reading results."""
+        entries = [e if isinstance(e, StepEntry) else StepEntry(**e) for e in entries]
+        self._validate(entries)
+        manager, fresh = self.manager, []
+        try:
+            for entry in entries:
+                if entry.request not in self._ids:
+                    self._ids[entry.request] = self._next_id
+                    self._next_id += 1
+                    slot = manager.admit(self._ids[entry.request])
+                    fresh.append(entry.request)
+                    self.cache.zero_state(slot)
+                manager.reserve(self._ids[entry.request], len(entry.tokens))
+            logits = self._run(entries)
+            for entry in entries:
+                manager.commit(self._ids[entry.request], len(entry.tokens))
+        except BaseException:
+            for entry in entries:
+                if entry.request in fresh:
+                    if entry.request in self._ids:
+                        manager.release(self._ids.pop(entry.request))
+                elif entry.request in self._ids:
+                    manager.rollback(self._ids[entry.request])
+            raise
+        self.steps += 1
+        return logits
+
+    def check(self) -> None:
+        """Raises if any kernel since the last check refused its input
+        (synchronises the device)."""
+        ops.check_status(self.device)
+
+    # ------------------------------------------------------------------ pieces
+    def _validate(self, entries: List[StepEntry]) -> None:
+        if not entries:
+            raise StepError("a step needs at least one entry")
+        seen = set()
+        asks = []
+        new_requests = 0
+        vocab = self.spec.vocab_size
+        for entry in entries:
+            if entry.request in seen:
+                raise StepError(f"request {entry.request!r} appears twice in one step")
+            seen.add(entry.request)
+            count = len(entry.tokens)
+            if count == 0:
+                raise StepError(f"request {entry.request!r} brings no tokens")
+            tokens = np.asarray(entry.tokens)
+            if tokens.dtype.kind not in "iu" or tokens.min() < 0 or tokens.max() >= vocab:
+                raise StepError(f"request {entry.request!r}: token ids must lie in 0..{vocab - 1}")
+            for index in entry.want:
+                if not 0 <= index < count:
+                    raise StepError(f"request {entry.request!r}: want index {index} outside its {count} tokens")
+            held = self.context_length(entry.request)
+            if entry.request in self._ids and self.manager.reserved(self._ids[entry.request]) != held:
+                raise StepError(f"request {entry.request!r} has uncommitted positions")
+            if held + count > self.max_context:
+                raise StepError(f"request {entry.request!r}: {held + count} positions exceed the "
+                                f"context limit of {self.max_context}")
+            if entry.request not in self._ids:
+                new_requests += 1
+                asks.append((-1 - new_requests, count))  # an unknown id is costed from zero
+            else:
+                asks.append((self._ids[entry.request], count))
+        if new_requests > self.manager.free_slots():
+            raise StepError(f"{new_requests} new requests but {self.manager.free_slots()} free request slots")
+        if not self.manager.fits(asks):
+            free = [self.manager.free_pages(g) for g in range(self.manager.num_groups())]
+            raise StepError(f"out of cache pages: the step does not fit (free pages per group: {free})")
+
+    def _run(self, entries: List[StepEntry]) -> Optional[torch.Tensor]:
+        manager, cache = self.manager, self.cache
+        page_tokens = cache.page_tokens
+        counts = [len(e.tokens) for e in entries]
+        total = sum(counts)
+        rows = len(entries)
+        offsets = np.zeros(rows + 1, dtype=np.int64)
+        np.cumsum(counts, out=offsets[1:])
+        token_ids = np.empty(total, dtype=np.int32)
+        positions = np.empty(total, dtype=np.int32)
+        token_request = np.empty(total, dtype=np.int32)
+        request_slots = np.empty(rows, dtype=np.int32)
+        starts, wanted = [], []
+        tile_request, tile_start, tile_length = [], [], []
+        group_tables = [[] for _ in cache.groups]
+        for row, entry in enumerate(entries):
+            rid = self._ids[entry.request]
+            begin, count = int(offsets[row]), counts[row]
+            start = manager.computed(rid)
+            starts.append(start)
+            token_ids[begin:begin + count] = np.asarray(entry.tokens, dtype=np.int32)
+            positions[begin:begin + count] = np.arange(start, start + count, dtype=np.int32)
+            token_request[begin:begin + count] = row
+            request_slots[row] = manager.slot(rid)
+            wanted.extend(begin + index for index in entry.want)
+            for first in range(0, count, ATTENTION_TILE):
+                tile_request.append(row)
+                tile_start.append(begin + first)
+                tile_length.append(min(ATTENTION_TILE, count - first))
+            for group in cache.groups:
+                group_tables[group.index].append(manager.table(rid, group.index))
+
+        # One packed int32 buffer, one copy to the device.
+        pieces = [token_ids, positions, token_request, request_slots,
+                  np.asarray(tile_request, dtype=np.int32), np.asarray(tile_start, dtype=np.int32),
+                  np.asarray(tile_length, dtype=np.int32), np.asarray(wanted, dtype=np.int32)]
+        shapes = [None] * len(pieces)
+        for group in cache.groups:
+            tables = group_tables[group.index]
+            width = max(len(t) for t in tables)
+            table = np.full((rows, width), -1, dtype=np.int32)
+            slots = np.empty(total, dtype=np.int32)
+            for row, pages in enumerate(tables):
+                table[row, :len(pages)] = pages
+                begin, count = int(offsets[row]), counts[row]
+                where = positions[begin:begin + count]
+                slots[begin:begin + count] = table[row, where // page_tokens] * page_tokens + where % page_tokens
+            pieces.extend([table.reshape(-1), slots])
+            shapes.extend([(rows, width), None])
+        sizes = [p.size for p in pieces]
+        packed = torch.empty(sum(sizes), dtype=torch.int32, pin_memory=True)
+        packed_np = packed.numpy()
+        cursor = 0
+        for piece, size in zip(pieces, sizes):
+            packed_np[cursor:cursor + size] = piece
+            cursor += size
+        on_device = packed.to(self.device, non_blocking=True)
+        views, cursor = [], 0
+        for size, shape in zip(sizes, shapes):
+            view = on_device[cursor:cursor + size]
+            views.append(view.view(shape) if shape is not None else view)
+            cursor += size
+        (d_ids, d_positions, d_token_request, d_request_slots, d_tile_request, d_tile_start,
+         d_tile_length, d_wanted) = views[:8]
+        tables = {g.index: views[8 + 2 * g.index] for g in cache.groups}
+        slots = {g.index: views[9 + 2 * g.index] for g in cache.groups}
+
+        ctx = StepContext(
+            device=self.device, dtype=self.dtype, num_tokens=total, num_requests=rows,
+            positions=d_positions, token_request=d_token_request, request_slots=d_request_slots,
+            request_offsets=[int(v) for v in offsets], request_positions=starts,
+            tile_request=d_tile_request, tile_start=d_tile_start, tile_length=d_tile_length)
+        self._keep = packed  # the pinned buffer must outlive the asynchronous copy
+        return self.model.forward(
+            d_ids, ctx, lambda entry, write: cache.view(entry, write, tables, slots),
+            d_wanted if wanted else None)

@@ -1,0 +1,413 @@
+"""Python face of the hand-written CUDA kernels.
+
+Every function checks its tensors (device, dtype, layout, sizes) and raises
+``KernelError`` for what the kernels do not take; it never falls back to
+another implementation. Kernels run on torch's current CUDA stream.
+"""
+from __future__ import annotations
+
+import ctypes
+from typing import Optional
+
+import torch
+
+from .csrc import build
+
+F32, BF16 = 0, 1
+_CODES = {torch.float32: F32, torch.bfloat16: BF16}
+
+STATUS_BITS = {1: "a token id outside the vocabulary", 2: "a cache slot or position outside its table",
+               4: "a block-table entry outside the page pool", 8: "non-finite logits",
+               16: "a bounded wait inside a kernel ran out"}
+
+
+class KernelError(RuntimeError):
+    pass
+
+
+_P, _I, _L, _F = ctypes.c_void_p, ctypes.c_int, ctypes.c_longlong, ctypes.c_float
+_SIGNATURES = {
+    "mxb_embed": [_P, _P, _I, _P, _I, _I, _I, _P, _P],
+    "mxb_rmsnorm": [_P, _I, _P, _I, _P, _P, _I, _I, _F, _P],
+    "mxb_add_rmsnorm": [_P, _P, _I, _P, _I, _P, _I, _I, _F, _P],
+    "mxb_add": [_P, _P, _I, _L, _P],
+    "mxb_qk_norm_rope_cache": [_P, _P, _P, _L, _L, _L, _P, _P, _P, _P, _P, _P, _P, _P,
+                               _I, _I, _I, _I, _I, _I, _I, _I, _F, _I, _P, _P],
+    "mxb_paged_attention_tile": [_P, _P, _P, _P, _I, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I,
+                                 _F, _I, _P, _P],
+    "mxb_gemm_simple": [_P, _I, _P, _P, _I, _I, _I, _I, _L, _L, _L, _P],
+    "mxb_silu_mul": [_P, _P, _I, _L, _I, _P],
+    "mxb_argmax": [_P, _L, _I, _I, _P, _P, _P],
+    "mxb_sample_icdf": [_P, _L, _I, _I, _P, _P, _P, _P, _P, _P, _P, _P],
+    "mxb_sample_race": [_P, _L, _I, _I, _P, _P, _P, _P, _P, _P, _P],
+}
+_functions = {}
+_status = {}
+
+
+def _fn(name: str):
+    fn = _functions.get(name)
+    if fn is None:
+        library = build.kernels()
+        try:
+            fn = getattr(library, name)
+        except AttributeError:
+            raise KernelError(f"the kernel library has no entry point {name}") from None
+        fn.argtypes = _SIGNATURES[name]
+        fn.restype = ctypes.c_int
+        _functions[name] = fn
+    return fn
+
+
+def _call(name: str, *args) -> None:
+    code = _fn(name)(*args)
+    if code != 0:
+        raise KernelError(f"{name} failed to launch: CUDA error {code}")
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _ptr(tensor: Optional[torch.Tensor]) -> Optional[int]:
+    return None if tensor is None else tensor.data_ptr()
+
+
+def _need(condition: bool, message: str) -> None:
+    if not condition:
+        raise KernelError(message)
+
+
+def _check(tensor: torch.Tensor, name: str, dtypes, dims: Optional[int] = None) -> None:
+    _need(isinstance(tensor, torch.Tensor), f"{name} must be a tensor")
+    _need(tensor.is_cuda, f"{name} must be on a CUDA device; there is no CPU path")
+    _need(tensor.dtype in dtypes, f"{name} has dtype {tensor.dtype}, expected one of {dtypes}")
+    _need(tensor.is_contiguous(), f"{name} must be contiguous")
+    if dims is not None:
+        _need(tensor.dim() == dims, f"{name} must have {dims} dimensions, has {tensor.dim()}")
+
+
+def require_cuda() -> None:
+    """Fails loudly where the kernels cannot run."""
+    if not torch.cuda.is_available():
+        raise KernelError("no CUDA device: metallix_b200 runs on a B200 only and has no CPU path")
+    build.kernels()
+
+
+def status_word(device) -> torch.Tensor:
+    """The int32 word kernels set bits in instead of trapping."""
+    key = torch.device(device).index or 0
+    if key not in _status:
+        _status[key] = torch.zeros(1, dtype=torch.int32, device=device)
+    return _status[key]
+
+
+def check_status(device) -> None:
+    """Reads the status word (synchronises) and raises on any bit; clears it."""
+    word = status_word(device)
+    value = int(word.item())
+    if value:
+        word.zero_()
+        reasons = [text for bit, text in STATUS_BITS.items() if value & bit]
+        raise KernelError("a kernel refused its input: " + "; ".join(reasons))
+
+
+# ------------------------------------------------------------------ embedding
+def embed(ids: torch.Tensor, table: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """out[t] = table[ids[t]] as float32."""
+    _check(ids, "ids", (torch.int32,), 1)
+    _check(table, "table", tuple(_CODES), 2)
+    tokens, (vocab, hidden) = ids.numel(), table.shape
+    if out is None:
+        out = torch.empty((tokens, hidden), dtype=torch.float32, device=ids.device)
+    _check(out, "out", (torch.float32,), 2)
+    _need(out.shape == (tokens, hidden), "out has the wrong shape")
+    _call("mxb_embed", out.data_ptr(), table.data_ptr(), _CODES[table.dtype], ids.data_ptr(),
+          tokens, hidden, vocab, status_word(ids.device).data_ptr(), _stream())
+    return out
+
+
+# ----------------------------------------------------------------------- norms
+def rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float, out_dtype: torch.dtype,
+            rows_index: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """y = x * rsqrt(mean(x^2) + eps) * w over the last axis, float32 inside.
+    ``rows_index`` picks the rows of ``x`` to normalise."""
+    _check(x, "x", tuple(_CODES))
+    _check(weight, "weight", (torch.float32,), 1)
+    size = x.shape[-1]
+    _need(weight.numel() == size, f"weight has {weight.numel()} values for rows of {size}")
+    rows = x.numel() // size if rows_index is None else rows_index.numel()
+    if rows_index is not None:
+        _check(rows_index, "rows_index", (torch.int32,), 1)
+        _need(x.dim() == 2, "rows_index needs a 2-d input")
+        shape = (rows, size)
+    else:
+        shape = tuple(x.shape)
+    if out is None:
+        out = torch.empty(shape, dtype=out_dtype, device=x.device)
+    _check(out, "out", (out_dtype,))
+    _need(out.numel() == rows * size, "out has the wrong size")
+    _call("mxb_rmsnorm", out.data_ptr(), _CODES[out_dtype], x.data_ptr(), _CODES[x.dtype],
+          weight.data_ptr(), _ptr(rows_index), rows, size, float(eps), _stream())
+    return out
+
+
+def add_rmsnorm(x: torch.Tensor, delta: torch.Tensor, weight: torch.Tensor, eps: float,
+                out_dtype: torch.dtype, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """x += delta in float32 (in place), then returns RMSNorm(x) * w."""
+    _check(x, "x", (torch.float32,), 2)
+    _check(delta, "delta", tuple(_CODES), 2)
+    _check(weight, "weight", (torch.float32,), 1)
+    _need(delta.shape == x.shape, "delta and x differ in shape")
+    rows, size = x.shape
+    _need(weight.numel() == size, "weight has the wrong size")
+    if out is None:
+        out = torch.empty((rows, size), dtype=out_dtype, device=x.device)
+    _check(out, "out", (out_dtype,), 2)
+    _need(out.shape == x.shape, "out has the wrong shape")
+    _call("mxb_add_rmsnorm", x.data_ptr(), delta.data_ptr(), _CODES[delta.dtype], out.data_ptr(),
+          _CODES[out_dtype], weight.data_ptr(), rows, size, float(eps), _stream())
+    return out
+
+
+def add_(x: torch.Tensor, delta: torch.Tensor) -> torch.Tensor:
+    """x += delta, the sum in float32."""
+    _check(x, "x", (torch.float32,))
+    _check(delta, "delta", tuple(_CODES))
+    _need(delta.shape == x.shape, "delta and x differ in shape")
+    _call("mxb_add", x.data_ptr(), delta.data_ptr(), _CODES[delta.dtype], x.numel(), _stream())
+    return x
+
+
+# ------------------------------------------------- q/k norm, rotation, cache
+def qk_norm_rope_cache(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, q_out: Optional[torch.Tensor],
+                       cache: Optional[torch.Tensor], slots: Optional[torch.Tensor],
+                       positions: torch.Tensor, q_weight: Optional[torch.Tensor],
+                       k_weight: Optional[torch.Tensor], cos: Optional[torch.Tensor],
+                       sin: Optional[torch.Tensor], eps: float) -> None:
+    """Per-head RMSNorm of q and k (if weights are given), rotate-half rotation
+    by ``positions`` (if tables are given), q written to ``q_out``
+    [tokens, heads, head_dim], k and v written into ``cache``
+    [pages, 2, kv_heads, page_tokens, head_dim] at ``slots`` (a negative slot
+    skips the token; ``cache=None`` writes nothing). q, k and v are
+    [tokens, heads * head_dim] views whose rows may be strided."""
+    dtype = q.dtype
+    for name, tensor in (("q", q), ("k", k), ("v", v)):
+        _need(tensor.is_cuda and tensor.dtype == dtype and tensor.dtype in _CODES and tensor.dim() == 2
+              and tensor.stride(1) == 1, f"{name} must be a CUDA [tokens, width] tensor with unit column stride")
+    tokens = q.shape[0]
+    _check(positions, "positions", (torch.int32,), 1)
+    _need(positions.numel() == tokens and k.shape[0] == tokens and v.shape[0] == tokens, "token counts differ")
+    if cache is not None:
+        _check(cache, "cache", (dtype,), 5)
+        num_pages, two, kv_heads, page_tokens, head_dim = cache.shape
+        _need(two == 2, "cache must be [pages, 2, kv_heads, page_tokens, head_dim]")
+        _check(slots, "slots", (torch.int32,), 1)
+        _need(slots.numel() == tokens, "one slot per token")
+    else:
+        _need(q_out is not None, "nothing to write")
+        head_dim = q_out.shape[-1]
+        kv_heads = k.shape[1] // head_dim
+        num_pages, page_tokens = 0, 1
+    _need(q.shape[1] % head_dim == 0 and k.shape[1] == kv_heads * head_dim and v.shape[1] == kv_heads * head_dim,
+          "q, k, v widths do not match the head layout")
+    heads = q.shape[1] // head_dim
+    if q_out is not None:
+        _check(q_out, "q_out", (dtype,), 3)
+        _need(q_out.shape == (tokens, heads, head_dim), "q_out must be [tokens, heads, head_dim]")
+    for name, weight in (("q_weight", q_weight), ("k_weight", k_weight)):
+        if weight is not None:
+            _check(weight, name, (torch.float32,), 1)
+            _need(weight.numel() == head_dim, f"{name} must have head_dim values")
+    rotary_dim, table_positions = 0, 0
+    if cos is not None:
+        _check(cos, "cos", (torch.float32,), 2)
+        _check(sin, "sin", (torch.float32,), 2)
+        _need(cos.shape == sin.shape, "cos and sin differ in shape")
+        table_positions, rotary_dim = cos.shape[0], cos.shape[1] * 2
+        _need(rotary_dim <= head_dim, "rotary_dim exceeds head_dim")
+    _call("mxb_qk_norm_rope_cache", q.data_ptr(), k.data_ptr(), v.data_ptr(), q.stride(0), k.stride(0),
+          v.stride(0), _ptr(q_out), _ptr(cache), _ptr(slots), positions.data_ptr(), _ptr(q_weight),
+          _ptr(k_weight), _ptr(cos), _ptr(sin), table_positions, rotary_dim, tokens, heads, kv_heads,
+          head_dim, page_tokens, num_pages, float(eps), _CODES[dtype],
+          status_word(q.device).data_ptr(), _stream())
+
+
+def norm_rotate_heads(x: torch.Tensor, head_dim: int, positions: torch.Tensor,
+                      weight: Optional[torch.Tensor] = None, cos: Optional[torch.Tensor] = None,
+                      sin: Optional[torch.Tensor] = None, eps: float = 0.0) -> torch.Tensor:
+    """Per-head RMSNorm (if ``weight``) and rotation (if tables) of x
+    [tokens, n * head_dim]; returns [tokens, n, head_dim]. Writes no cache."""
+    _need(x.dim() == 2 and x.shape[1] % head_dim == 0, "x must be [tokens, n * head_dim]")
+    out = torch.empty((x.shape[0], x.shape[1] // head_dim, head_dim), dtype=x.dtype, device=x.device)
+    empty = x[:, :0]
+    qk_norm_rope_cache(x, empty, empty, out, None, None, positions, weight, None, cos, sin, eps)
+    return out
+
+
+def write_cache(k: torch.Tensor, v: torch.Tensor, cache: torch.Tensor, slots: torch.Tensor,
+                positions: torch.Tensor) -> None:
+    """Stores k and v [tokens, kv_heads * head_dim] as they are at ``slots``."""
+    qk_norm_rope_cache(k[:, :0], k, v, None, cache, slots, positions, None, None, None, None, 0.0)
+
+
+# ------------------------------------------------------------------ attention
+def paged_attention_tile(q: torch.Tensor, cache: torch.Tensor, out: torch.Tensor,
+                         block_tables: torch.Tensor, tile_request: torch.Tensor,
+                         tile_start: torch.Tensor, tile_length: torch.Tensor,
+                         positions: torch.Tensor, scale: float, window: int = 0) -> torch.Tensor:
+    """Attention of every query token over its request's cached keys (itself
+    included) in float32; q and out are [tokens, heads, head_dim]."""
+    dtype = q.dtype
+    _check(q, "q", tuple(_CODES), 3)
+    _check(out, "out", (dtype,), 3)
+    _check(cache, "cache", (dtype,), 5)
+    _need(out.shape == q.shape, "out and q differ in shape")
+    tokens, heads, head_dim = q.shape
+    num_pages, two, kv_heads, page_tokens, cache_dim = cache.shape
+    _need(two == 2 and cache_dim == head_dim, "cache must be [pages, 2, kv_heads, page_tokens, head_dim]")
+    _need(heads % kv_heads == 0, f"{heads} query heads cannot share {kv_heads} key/value heads")
+    _need(0 < head_dim <= 256, f"head_dim {head_dim} is outside 1..256")
+    _check(block_tables, "block_tables", (torch.int32,), 2)
+    for name, tensor in (("tile_request", tile_request), ("tile_start", tile_start),
+                         ("tile_length", tile_length), ("positions", positions)):
+        _check(tensor, name, (torch.int32,), 1)
+    tiles = tile_request.numel()
+    _need(tile_start.numel() == tiles and tile_length.numel() == tiles, "tile lists differ in length")
+    _need(positions.numel() == tokens, "one position per token")
+    _call("mxb_paged_attention_tile", q.data_ptr(), cache.data_ptr(), out.data_ptr(),
+          block_tables.data_ptr(), block_tables.shape[1], tile_request.data_ptr(),
+          tile_start.data_ptr(), tile_length.data_ptr(), positions.data_ptr(), tiles, heads,
+          kv_heads, head_dim, page_tokens, num_pages, int(window or 0), float(scale), _CODES[dtype],
+          status_word(q.device).data_ptr(), _stream())
+    return out
+
+
+# ------------------------------------------------------------ matrix products
+def gemm_simple(a: torch.Tensor, w: torch.Tensor, out_dtype: Optional[torch.dtype] = None,
+                out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """a [m, k] times w [n, k] transposed on CUDA cores, float32 accumulation
+    in a fixed order."""
+    _need(a.is_cuda and w.is_cuda, "operands must be on a CUDA device")
+    _need(a.dim() == 2 and w.dim() == 2 and a.shape[1] == w.shape[1], "shapes do not match a @ w.T")
+    _need(a.dtype == w.dtype and a.dtype in _CODES, "operands must share float32 or bfloat16")
+    _need(a.stride(1) == 1 and w.stride(1) == 1, "rows must be contiguous")
+    out_dtype = out_dtype or a.dtype
+    m, k = a.shape
+    n = w.shape[0]
+    if out is None:
+        out = torch.empty((m, n), dtype=out_dtype, device=a.device)
+    _need(out.shape == (m, n) and out.dtype == out_dtype and out.stride(1) == 1, "out does not fit")
+    _call("mxb_gemm_simple", out.data_ptr(), _CODES[out_dtype], a.data_ptr(), w.data_ptr(),
+          _CODES[a.dtype], m, n, k, a.stride(0), w.stride(0), out.stride(0), _stream())
+    return out
+
+
+def gemm_bf16(a: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype = torch.bfloat16,
+              backend: str = "auto", out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """bfloat16 a [m, k] times w [n, k] transposed with float32 accumulation.
+
+    ``backend``: "tcgen05" is the hand-written tensor-core kernel, "cublas" the
+    library product (where the reference calls a library matmul too), "simple"
+    the plain CUDA-core kernel, "auto" the tensor-core kernel where its shape
+    rules hold and the library otherwise."""
+    _need(a.is_cuda and w.is_cuda, "operands must be on a CUDA device")
+    _need(a.dtype == torch.bfloat16 and w.dtype == torch.bfloat16, "operands must be bfloat16")
+    _need(a.dim() == 2 and w.dim() == 2 and a.shape[1] == w.shape[1], "shapes do not match a @ w.T")
+    _need(out_dtype in (torch.bfloat16, torch.float32), "out_dtype must be bfloat16 or float32")
+    if backend == "simple":
+        return gemm_simple(a, w, out_dtype=out_dtype, out=out)
+    if backend in ("auto", "tcgen05"):
+        from . import tensor_core
+        if tensor_core.supports(a, w, out_dtype):
+            return tensor_core.gemm(a, w, out_dtype=out_dtype, out=out)
+        _need(backend == "auto", "the tcgen05 kernel does not take this shape: "
+              + tensor_core.why_not(a, w, out_dtype))
+    elif backend != "cublas":
+        raise KernelError(f"unknown gemm backend {backend!r}")
+    if out_dtype == torch.float32:
+        result = torch.mm(a, w.t(), out_dtype=torch.float32)
+    else:
+        result = torch.mm(a, w.t())
+    if out is not None:
+        out.copy_(result)
+        return out
+    return result
+
+
+def silu_mul(gate_up: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """out[t, i] = silu(gate_up[t, i]) * gate_up[t, I + i], float32 inside."""
+    _check(gate_up, "gate_up", tuple(_CODES), 2)
+    tokens, width = gate_up.shape
+    _need(width % 2 == 0, "gate_up must hold gate and up side by side")
+    inter = width // 2
+    if out is None:
+        out = torch.empty((tokens, inter), dtype=gate_up.dtype, device=gate_up.device)
+    _check(out, "out", (gate_up.dtype,), 2)
+    _need(out.shape == (tokens, inter), "out has the wrong shape")
+    _call("mxb_silu_mul", out.data_ptr(), gate_up.data_ptr(), _CODES[gate_up.dtype], tokens, inter,
+          _stream())
+    return out
+
+
+# -------------------------------------------------------------------- picking
+def _logit_rows(logits: torch.Tensor):
+    _need(logits.is_cuda and logits.dtype == torch.float32 and logits.dim() == 2 and logits.stride(1) == 1,
+          "logits must be CUDA float32 [rows, vocab] with contiguous rows")
+    return logits.shape[0], logits.shape[1], logits.stride(0)
+
+
+def argmax(logits: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Lowest index of each row's maximum; -1 and a status bit for a row with
+    a non-finite value."""
+    rows, vocab, stride = _logit_rows(logits)
+    if out is None:
+        out = torch.empty(rows, dtype=torch.int32, device=logits.device)
+    _check(out, "out", (torch.int32,), 1)
+    _call("mxb_argmax", logits.data_ptr(), stride, rows, vocab, out.data_ptr(),
+          status_word(logits.device).data_ptr(), _stream())
+    return out
+
+
+def sample_icdf(logits: torch.Tensor, temperature: torch.Tensor, seed: torch.Tensor,
+                stream_id: torch.Tensor, position: torch.Tensor, legal: Optional[torch.Tensor] = None,
+                out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Inverse-CDF temperature sampling in token-id order, float64 weights;
+    the uniform of row r is a function of (seed[r], stream_id[r], position[r])."""
+    rows, vocab, stride = _logit_rows(logits)
+    _check(temperature, "temperature", (torch.float64,), 1)
+    _check(seed, "seed", (torch.int64, torch.uint64), 1)
+    _check(stream_id, "stream_id", (torch.int64, torch.uint64), 1)
+    _check(position, "position", (torch.int32,), 1)
+    _need(temperature.numel() == rows and seed.numel() == rows and stream_id.numel() == rows
+          and position.numel() == rows, "one temperature, seed, stream and position per row")
+    if legal is not None:
+        _check(legal, "legal", (torch.uint8, torch.bool), 2)
+        _need(legal.shape == (rows, vocab), "legal must be [rows, vocab]")
+    if out is None:
+        out = torch.empty(rows, dtype=torch.int32, device=logits.device)
+    _call("mxb_sample_icdf", logits.data_ptr(), stride, rows, vocab, temperature.data_ptr(),
+          seed.data_ptr(), stream_id.data_ptr(), position.data_ptr(), _ptr(legal), out.data_ptr(),
+          status_word(logits.device).data_ptr(), _stream())
+    return out
+
+
+def sample_race(logits: torch.Tensor, temperature: torch.Tensor, seed: torch.Tensor,
+                position: torch.Tensor, legal: Optional[torch.Tensor] = None,
+                out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Gumbel-max sampling with Philox noise keyed by (seed, position, id)."""
+    rows, vocab, stride = _logit_rows(logits)
+    _check(temperature, "temperature", (torch.float64,), 1)
+    _check(seed, "seed", (torch.int64, torch.uint64), 1)
+    _check(position, "position", (torch.int32,), 1)
+    _need(temperature.numel() == rows and seed.numel() == rows and position.numel() == rows,
+          "one temperature, seed and position per row")
+    if legal is not None:
+        _check(legal, "legal", (torch.uint8, torch.bool), 2)
+        _need(legal.shape == (rows, vocab), "legal must be [rows, vocab]")
+    if out is None:
+        out = torch.empty(rows, dtype=torch.int32, device=logits.device)
+    _call("mxb_sample_race", logits.data_ptr(), stride, rows, vocab, temperature.data_ptr(),
+          seed.data_ptr(), position.data_ptr(), _ptr(legal), out.data_ptr(),
+          status_word(logits.device).data_ptr(), _stream())
+    return out

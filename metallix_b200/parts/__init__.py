@@ -1,0 +1,9 @@
+"""Parts a decoder is put together from: mixers, feed-forwards, norms,
+position encodings, block arrangements and the model's two ends."""
+from . import attention, block, embedding, feed_forward, norm, position  # noqa: F401  (register)
+from .linear import Linear
+from .registry import (CacheView, Runtime, StepContext, WeightStore, build_part, register_part,
+                       unregister_part)
+
+__all__ = ["Linear", "CacheView", "Runtime", "StepContext", "WeightStore", "build_part",
+           "register_part", "unregister_part"]

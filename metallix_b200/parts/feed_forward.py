@@ -1,0 +1,37 @@
+"""SwiGLU feed-forward: d = ((sigmoid(g) * g) * u) Wd^T with g = m Wg^T and
+u = m Wu^T (crates/models/qwen/src/forward.rs:1904-1920). Gate and up weights
+are stacked so that one product yields both; SiLU and the product with u are
+float32 inside the kernel."""
+from __future__ import annotations
+
+import torch
+
+from .. import ops
+from ..config.spec import PartSpec
+from .linear import Linear
+from .registry import Runtime, StepContext, WeightStore, register_part
+
+
+class SwiGLU:
+    kind = "swiglu"
+
+    def __init__(self, spec: PartSpec, weights: WeightStore, runtime: Runtime):
+        hidden, inter = spec["hidden_size"], spec["intermediate_size"]
+        gate, up = weights.take(spec["gate_proj"]), weights.take(spec["up_proj"])
+        down = weights.take(spec["down_proj"])
+        for name, weight, shape in (("gate_proj", gate, (inter, hidden)), ("up_proj", up, (inter, hidden)),
+                                    ("down_proj", down, (hidden, inter))):
+            if tuple(weight.shape) != shape:
+                raise ValueError(f"{spec[name]} is {tuple(weight.shape)}, expected {shape}")
+        self.gate_up = Linear.stacked([gate, up], runtime)  # rows: gate, then up
+        self.down = Linear(down, runtime)
+        self.intermediate_size = inter
+
+    def forward(self, x: torch.Tensor, ctx: StepContext) -> torch.Tensor:
+        return self.down.forward(ops.silu_mul(self.gate_up.forward(x)))
+
+    def weight_bytes(self) -> int:
+        return self.gate_up.weight_bytes() + self.down.weight_bytes()
+
+
+register_part("feed_forward", "swiglu", lambda spec, weights, runtime: SwiGLU(spec, weights, runtime))
