@@ -53,7 +53,8 @@ class LayerSpec:
 class LayerRun:
     """One entry of the execution order.
 
-    ``layer`` indexes ``ModelSpec.layers`` (a layer may be named twice).
+    ``layer`` indexes ``ModelSpec.layers`` (a layer may be named twice; its
+    second run then needs a cache entry of its own, any unused index).
     ``cache`` is the cache entry the mixer uses; by default a layer owns the
     entry with its own index. ``write_cache=False`` lets a layer read the
     entry another layer has written in the same step without writing to it.
@@ -104,6 +105,9 @@ class ModelSpec:
     final_norm: PartSpec
     head: PartSpec
 
+    def num_cache_entries(self) -> int:
+        return max(run.cache_entry() for run in self.order) + 1
+
     def validate(self) -> None:
         if not self.layers:
             raise ValueError("a model needs at least one layer")
@@ -112,8 +116,8 @@ class ModelSpec:
             if not 0 <= run.layer < len(self.layers):
                 raise ValueError(f"order names layer {run.layer}, the model has {len(self.layers)}")
             entry = run.cache_entry()
-            if not 0 <= entry < len(self.layers):
-                raise ValueError(f"order names cache entry {entry}, outside 0..{len(self.layers) - 1}")
+            if entry < 0:
+                raise ValueError(f"order names cache entry {entry}")
             if run.write_cache:
                 written.add(entry)
             elif entry not in written:

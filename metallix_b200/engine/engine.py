@@ -45,6 +45,10 @@ class StepEntry:
     request: Hashable
     tokens: Sequence[int]
     want: Sequence[int] = field(default_factory=tuple)
+    # True: ``request`` is an id a scheduler has already admitted to the cache
+    # manager; the step reserves and commits for it but neither admits nor
+    # releases it.
+    managed: bool = False
 
 
 def resolve_dtype(dtype) -> torch.dtype:
@@ -80,7 +84,7 @@ class Engine:
                                 self.dtype, self.device)
         self.manager = self.cache.manager
         self._ids: Dict[Hashable, int] = {}   # request name -> manager id
-        self._next_id = 0
+        self._next_id = 1 << 40               # above any id a scheduler hands out
         self.steps = 0
 
     # ----------------------------------------------------------- construction
@@ -110,6 +114,12 @@ class Engine:
     def context_length(self, request: Hashable) -> int:
         return self.manager.computed(self._ids[request]) if request in self._ids else 0
 
+    def _rid(self, entry: StepEntry) -> Optional[int]:
+        """The cache manager's id of an entry's request, None if not admitted."""
+        if entry.managed:
+            return int(entry.request)
+        return self._ids.get(entry.request)
+
     def release(self, request: Hashable) -> None:
         """Gives back everything the request holds."""
         if request in self._ids:
@@ -129,23 +139,27 @@ class Engine:
         manager, fresh = self.manager, []
         try:
             for entry in entries:
-                if entry.request not in self._ids:
+                if self._rid(entry) is None:
                     self._ids[entry.request] = self._next_id
                     self._next_id += 1
-                    slot = manager.admit(self._ids[entry.request])
+                    manager.admit(self._ids[entry.request])
                     fresh.append(entry.request)
-                    self.cache.zero_state(slot)
-                manager.reserve(self._ids[entry.request], len(entry.tokens))
+                rid = self._rid(entry)
+                if manager.computed(rid) == 0:
+                    self.cache.zero_state(manager.slot(rid))  # a sequence starts from zero state
+                manager.reserve(rid, len(entry.tokens))
             logits = self._run(entries)
             for entry in entries:
-                manager.commit(self._ids[entry.request], len(entry.tokens))
+                manager.commit(self._rid(entry), len(entry.tokens))
         except BaseException:
             for entry in entries:
-                if entry.request in fresh:
-                    if entry.request in self._ids:
-                        manager.release(self._ids.pop(entry.request))
-                elif entry.request in self._ids:
-                    manager.rollback(self._ids[entry.request])
+                rid = self._rid(entry)
+                if rid is None or not manager.has(rid):
+                    continue
+                if not entry.managed and entry.request in fresh:
+                    manager.release(self._ids.pop(entry.request))
+                else:
+                    manager.rollback(rid)
             raise
         self.steps += 1
         return logits
@@ -176,17 +190,20 @@ class Engine:
             for index in entry.want:
                 if not 0 <= index < count:
                     raise StepError(f"request {entry.request!r}: want index {index} outside its {count} tokens")
-            held = self.context_length(entry.request)
-            if entry.request in self._ids and self.manager.reserved(self._ids[entry.request]) != held:
+            rid = self._rid(entry)
+            if entry.managed and not self.manager.has(rid):
+                raise StepError(f"request {entry.request!r} is not admitted to the cache manager")
+            held = self.manager.computed(rid) if rid is not None else 0
+            if rid is not None and self.manager.reserved(rid) != held:
                 raise StepError(f"request {entry.request!r} has uncommitted positions")
             if held + count > self.max_context:
                 raise StepError(f"request {entry.request!r}: {held + count} positions exceed the "
                                 f"context limit of {self.max_context}")
-            if entry.request not in self._ids:
+            if rid is None:
                 new_requests += 1
                 asks.append((-1 - new_requests, count))  # an unknown id is costed from zero
             else:
-                asks.append((self._ids[entry.request], count))
+                asks.append((rid, count))
         if new_requests > self.manager.free_slots():
             raise StepError(f"{new_requests} new requests but {self.manager.free_slots()} free request slots")
         if not self.manager.fits(asks):
@@ -209,7 +226,7 @@ class Engine:
         tile_request, tile_start, tile_length = [], [], []
         group_tables = [[] for _ in cache.groups]
         for row, entry in enumerate(entries):
-            rid = self._ids[entry.request]
+            rid = self._rid(entry)
             begin, count = int(offsets[row]), counts[row]
             start = manager.computed(rid)
             starts.append(start)

@@ -1,0 +1,169 @@
+"""Generation through the scheduler: the Python entry point.
+
+``Generator`` owns a C++ ``Scheduler`` over the engine's cache manager. Each
+iteration asks the scheduler for a plan (decoded tokens of running requests
+first, then portions of prompts under the token budget, then admissions), runs
+it as ONE engine step, picks a token on the device for every entry that reached
+the end of what it knows, and hands the tokens back; the scheduler finishes and
+frees. The loop is the reference's ``Engine::step``
+(crates/app/cli/src/engine_loop.rs:618-677); the receipt's field names are
+those of ``mx gen`` (crates/app/cli/src/qwen_forward.rs:1021-1050).
+"""
+from __future__ import annotations
+
+import time
+from dataclasses import dataclass, field
+from typing import Callable, Dict, List, Optional, Sequence
+
+import torch
+
+from ..csrc import build
+from ..sampling import SamplingParams, pick
+from .engine import Engine, StepEntry
+
+
+@dataclass
+class GenerationResult:
+    input_ids: List[int]
+    generated_ids: List[int]
+    finish_reason: str          # "eos", "length", "cancelled", or an error text
+    failed: bool = False
+    preemptions: int = 0
+    cached_tokens: int = 0      # positions the request held when it finished
+    prefill_ms: float = 0.0     # from admission to its first token
+    decode_ms: List[float] = field(default_factory=list)  # per later token
+
+
+@dataclass
+class GenerationStats:
+    steps: int = 0
+    decode_tokens: int = 0
+    prefill_tokens: int = 0
+    preemptions: int = 0
+    step_ms: List[float] = field(default_factory=list)
+
+
+class Generator:
+    """Continuous batching over one engine."""
+
+    def __init__(self, engine: Engine, max_num_seqs: int = 8, max_tokens_per_step: int = 8192,
+                 prefill_chunk: int = 0):
+        host = build.host()
+        self.engine = engine
+        self.host = host
+        max_num_seqs = min(max_num_seqs, engine.manager.max_requests())
+        self.scheduler = host.Scheduler(
+            engine.manager, host.Limits(max_num_seqs, max_tokens_per_step, prefill_chunk))
+        self.stats = GenerationStats()
+        self._params: Dict[int, SamplingParams] = {}
+        self._started: Dict[int, float] = {}
+        self._last: Dict[int, float] = {}
+        self._timing: Dict[int, GenerationResult] = {}
+
+    def add(self, prompt: Sequence[int], max_new_tokens: int, params: SamplingParams = SamplingParams(),
+            eos_ids: Sequence[int] = (), ignore_eos: bool = False) -> int:
+        params.validate()
+        prompt = [int(t) for t in prompt]
+        vocab = self.engine.spec.vocab_size
+        if not prompt:
+            raise ValueError("a prompt needs at least one token")
+        if min(prompt) < 0 or max(prompt) >= vocab:
+            raise ValueError(f"prompt token ids must lie in 0..{vocab - 1}")
+        if len(prompt) + max_new_tokens > self.engine.max_context:
+            raise ValueError(f"prompt ({len(prompt)}) plus max_new_tokens ({max_new_tokens}) exceeds "
+                             f"the context limit of {self.engine.max_context}")
+        code = {"icdf": 0, "race": 1}[params.sampler]
+        rid = self.scheduler.add(prompt, int(max_new_tokens), [int(e) for e in eos_ids],
+                                 bool(ignore_eos),
+                                 self.host.SamplingParams(params.temperature, params.seed,
+                                                          params.top_p, params.top_k, code))
+        self._params[rid] = params
+        self._timing[rid] = GenerationResult(input_ids=prompt, generated_ids=[], finish_reason="")
+        self._started[rid] = time.perf_counter()
+        return rid
+
+    def cancel(self, rid: int) -> None:
+        self.scheduler.cancel(rid)
+
+    def idle(self) -> bool:
+        return self.scheduler.idle()
+
+    def step(self) -> List:
+        """One scheduler iteration; returns the events (id, token, finished,
+        finish_reason) of this step."""
+        plan = self.scheduler.plan()
+        self.stats.preemptions += len(plan.preempted)
+        if not plan.entries:
+            return []
+        started = time.perf_counter()
+        entries, rows, positions = [], [], []
+        for entry in plan.entries:
+            count = len(entry.tokens)
+            entries.append(StepEntry(request=entry.id, tokens=entry.tokens,
+                                     want=(count - 1,) if entry.wants_token else (), managed=True))
+            if entry.wants_token:
+                rows.append(self._params[entry.id])
+                positions.append(entry.generated_position)
+        try:
+            logits = self.engine.step(entries)
+            tokens: List[int] = []
+            if logits is not None:
+                tokens = pick(logits, rows, positions).tolist()
+            self.engine.check()
+            if any(t < 0 for t in tokens):
+                raise RuntimeError("non-finite logits")
+        except Exception as error:  # the requests of this step leave with the error
+            self.scheduler.fail_plan(plan, f"step failed: {error}")
+            raise
+        events = self.scheduler.update(plan, tokens)
+        now = time.perf_counter()
+        self.stats.steps += 1
+        self.stats.decode_tokens += plan.decode_tokens
+        self.stats.prefill_tokens += plan.prefill_tokens
+        self.stats.step_ms.append((now - started) * 1e3)
+        for event in events:
+            result = self._timing[event.id]
+            if not result.generated_ids and not result.decode_ms and result.prefill_ms == 0.0:
+                result.prefill_ms = (now - self._started[event.id]) * 1e3
+            else:
+                result.decode_ms.append((now - self._last[event.id]) * 1e3)
+            self._last[event.id] = now
+        return events
+
+    def result(self, rid: int) -> GenerationResult:
+        info = self.scheduler.request(rid)
+        result = self._timing[rid]
+        result.generated_ids = list(info.output)
+        result.finish_reason = info.finish_reason
+        result.failed = info.failed
+        result.preemptions = info.preemptions
+        result.cached_tokens = len(info.prompt) + max(len(info.output) - 1, 0)
+        return result
+
+    def run(self, on_token: Optional[Callable] = None) -> None:
+        """Steps until nothing waits or runs."""
+        while not self.scheduler.idle():
+            for event in self.step():
+                if on_token is not None:
+                    on_token(event.id, event.token, event.finished, event.finish_reason)
+
+
+def generate(engine: Engine, prompts: Sequence[Sequence[int]], max_new_tokens: int = 32,
+             temperature: float = 0.0, seed: int = 0, top_p: float = 1.0, top_k: int = 0,
+             sampler: str = "icdf", eos_ids: Optional[Sequence[int]] = None,
+             ignore_eos: bool = False, max_num_seqs: int = 8, max_tokens_per_step: int = 8192,
+             prefill_chunk: int = 0) -> List[GenerationResult]:
+    """Generates for every prompt (lists of token ids) and returns the results
+    in the prompts' order. ``temperature`` 0 is greedy; otherwise request i
+    draws from (seed, stream i). ``eos_ids`` defaults to the configuration's."""
+    if eos_ids is None:
+        eos_ids = tuple(getattr(engine.config, "eos_token_ids", ()) or ())
+    generator = Generator(engine, max_num_seqs=max_num_seqs,
+                          max_tokens_per_step=max_tokens_per_step, prefill_chunk=prefill_chunk)
+    ids = [generator.add(prompt, max_new_tokens,
+                         SamplingParams(temperature=temperature, seed=seed, stream=index,
+                                        top_p=top_p, top_k=top_k, sampler=sampler),
+                         eos_ids=eos_ids, ignore_eos=ignore_eos)
+           for index, prompt in enumerate(prompts)]
+    generator.run()
+    return [generator.result(rid) for rid in ids]

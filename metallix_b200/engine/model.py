@@ -34,7 +34,7 @@ class DecoderModel:
 
     def cache_needs(self) -> List[Optional[CacheNeed]]:
         """What each cache entry (one per layer index) must hold."""
-        needs: List[Optional[CacheNeed]] = [None] * len(self.blocks)
+        needs: List[Optional[CacheNeed]] = [None] * self.spec.num_cache_entries()
         for run in self.order:
             entry = run.cache_entry()
             need = self.blocks[run.layer].mixer.cache_need()

@@ -40,6 +40,7 @@ _SIGNATURES = {
     "mxb_argmax": [_P, _L, _I, _I, _P, _P, _P],
     "mxb_sample_icdf": [_P, _L, _I, _I, _P, _P, _P, _P, _P, _P, _P, _P],
     "mxb_sample_race": [_P, _L, _I, _I, _P, _P, _P, _P, _P, _P, _P],
+    "mxb_nucleus_mask": [_P, _L, _I, _I, _P, _P, _P, _P, _P, _P],
 }
 _functions = {}
 _status = {}
@@ -410,4 +411,23 @@ def sample_race(logits: torch.Tensor, temperature: torch.Tensor, seed: torch.Ten
     _call("mxb_sample_race", logits.data_ptr(), stride, rows, vocab, temperature.data_ptr(),
           seed.data_ptr(), position.data_ptr(), _ptr(legal), out.data_ptr(),
           status_word(logits.device).data_ptr(), _stream())
+    return out
+
+
+def nucleus_mask(logits: torch.Tensor, temperature: torch.Tensor, top_p: torch.Tensor,
+                 top_k: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """uint8 [rows, vocab]: 1 where a token is inside the row's top-k then
+    top-p nucleus (descending logit, lower id first on ties)."""
+    rows, vocab, stride = _logit_rows(logits)
+    _check(temperature, "temperature", (torch.float64,), 1)
+    _check(top_p, "top_p", (torch.float64,), 1)
+    _check(top_k, "top_k", (torch.int32,), 1)
+    _need(temperature.numel() == rows and top_p.numel() == rows and top_k.numel() == rows,
+          "one temperature, top_p and top_k per row")
+    if out is None:
+        out = torch.empty((rows, vocab), dtype=torch.uint8, device=logits.device)
+    _check(out, "out", (torch.uint8,), 2)
+    _call("mxb_nucleus_mask", logits.data_ptr(), stride, rows, vocab, temperature.data_ptr(),
+          top_p.data_ptr(), top_k.data_ptr(), out.data_ptr(), status_word(logits.device).data_ptr(),
+          _stream())
     return out

@@ -108,7 +108,7 @@ def load_tensors(model_dir: str, config, device: str = "cpu") -> Dict[str, torch
                         if entry.element_count() == 0:
                             value = torch.empty(entry.shape, dtype=dtype)
                         else:
-                            value = torch.frombuffer(piece, dtype=torch.uint8).clone() \
+                            value = torch.frombuffer(bytearray(piece), dtype=torch.uint8) \
                                 .view(dtype).reshape(entry.shape)
                     finally:
                         piece.release()

@@ -135,7 +135,7 @@ def read_tensor(entry: TensorEntry) -> torch.Tensor:
             start = entry.payload_start + entry.begin
             view = memoryview(mapped)[start:start + (entry.end - entry.begin)]
             try:
-                flat = torch.frombuffer(view, dtype=torch.uint8).clone()
+                flat = torch.frombuffer(bytearray(view), dtype=torch.uint8)
             finally:
                 view.release()
     return flat.view(dtype).reshape(entry.shape)

@@ -148,9 +148,13 @@ def swiglu(x, gate_w, up_w, down_w, rounding=None):
     return r(r(activated * up) @ down_w.T)
 
 
-def attention_block(x, positions, w, base, config, rounding=None, window=None):
+def attention_block(x, positions, w, base, config, rounding=None, window=None, shared_kv=None,
+                    keep=None):
     """q/k/v projections, per-head q/k RMSNorm before RoPE, attention, output
-    projection (forward.rs:2012-2065 and :2070-2093)."""
+    projection (forward.rs:2012-2065 and :2070-2093). ``shared_kv``: keys and
+    values another layer produced, used instead of this layer's own (not part
+    of Qwen3; for the tests of the layer order). ``keep``: a list that
+    receives this layer's (k, v)."""
     r = rounding or (lambda a: a)
     tokens = x.shape[0]
     heads, kv_heads, hd = (config["num_attention_heads"], config["num_key_value_heads"],
@@ -164,12 +168,16 @@ def attention_block(x, positions, w, base, config, rounding=None, window=None):
     k = rms_norm(k, w[f"{base}.k_norm.weight"], eps)
     q = r(rope_half(q, positions, theta))
     k = r(rope_half(k, positions, theta))
+    if keep is not None:
+        keep.append((k, v))
+    if shared_kv is not None:
+        k, v = shared_kv
     scale = float(np.float32(hd) ** np.float32(-0.5))  # forward.rs:2290-2295
     out = r(causal_gqa_attention(q, k, v, scale, window))
     return r(out.reshape(tokens, heads * hd) @ w[f"{base}.o_proj.weight"].T)
 
 
-def decoder_layer(x, positions, w, layer, config, rounding=None):
+def decoder_layer(x, positions, w, layer, config, rounding=None, shared_kv=None, keep=None):
     """Pre-norm attention, residual, pre-norm SwiGLU, residual
     (forward.rs:1856-1885 and :1889-1922)."""
     r = rounding or (lambda a: a)
@@ -177,7 +185,7 @@ def decoder_layer(x, positions, w, layer, config, rounding=None):
     eps = f32(config.get("rms_norm_eps", 1e-6))
     attention_in = r(rms_norm(x, w[f"{base}.input_layernorm.weight"], eps))
     residual = x + attention_block(attention_in, positions, w, f"{base}.self_attn", config,
-                                   rounding)
+                                   rounding, shared_kv=shared_kv, keep=keep)
     mlp_in = r(rms_norm(residual, w[f"{base}.post_attention_layernorm.weight"], eps))
     return residual + swiglu(mlp_in, w[f"{base}.mlp.gate_proj.weight"],
                              w[f"{base}.mlp.up_proj.weight"],
@@ -185,21 +193,27 @@ def decoder_layer(x, positions, w, layer, config, rounding=None):
 
 
 def forward_logits(config, tensors, ids, dtype=np.float64, bf16_activations=False,
-                   order=None):
+                   order=None, reads=None):
     """Logits [T, V] at every position of one whole sequence (forward.rs:741-773,
     :995-1020): embedding, the layers in order, final norm, output head through
     the embedding when tied, else lm_head (forward.rs:574-580; an absent
     tie_word_embeddings is false, :2606-2607). ``bf16_activations`` rounds
     activations to bfloat16 where a bfloat16 engine stores them, keeping the
-    residual sum unrounded. ``order`` runs the layers in another order."""
+    residual sum unrounded. ``order`` runs the layers in another order;
+    ``reads[i] = j`` lets the i-th run use the keys and values the j-th run
+    produced."""
     w = {name: value.astype(dtype) for name, value in tensors.items()}
     rounding = bf16_round if bf16_activations else None
     r = rounding or (lambda a: a)
     positions = np.arange(len(ids))
     x = embed(w["model.embed_tokens.weight"], ids)
     layers = range(config["num_hidden_layers"]) if order is None else order
-    for layer in layers:
-        x = decoder_layer(x, positions, w, layer, config, rounding)
+    produced = []
+    for run, layer in enumerate(layers):
+        keep = []
+        shared = produced[reads[run]] if reads and run in reads else None
+        x = decoder_layer(x, positions, w, layer, config, rounding, shared_kv=shared, keep=keep)
+        produced.append(keep[0])
     eps = f32(config.get("rms_norm_eps", 1e-6))
     normed = r(rms_norm(x, w["model.norm.weight"], eps))
     head = (w["model.embed_tokens.weight"] if config.get("tie_word_embeddings", False)

@@ -1,0 +1,146 @@
+"""Generation through the Python entry point and the command line against the
+plain implementation: greedy, sampled, portions of prompts, a pool so small
+that requests are computed again."""
+import json
+import os
+import subprocess
+import sys
+
+import numpy as np
+import pytest
+
+import plain_qwen3 as plain
+from conftest import ROOT, random_ids
+
+pytestmark = pytest.mark.gpu
+
+
+def plain_greedy(config, tensors, prompt, count, margin=None):
+    """Greedy tokens by recomputing the whole sequence, with the gap between
+    the two largest logits at every step."""
+    ids, out, gaps = list(prompt), [], []
+    for _ in range(count):
+        row = plain.forward_logits(config, tensors, ids)[-1]
+        order = np.argsort(-row, kind="stable")
+        out.append(int(order[0]))
+        gaps.append(float(row[order[0]] - row[order[1]]))
+        ids.append(out[-1])
+    return out, gaps
+
+
+def test_greedy_workload_a(model_folders):
+    """Tiny A, float32: 3 requests, prompts 5/17/31, 16 greedy steps, pages of 4."""
+    from metallix_b200.engine import Engine
+    from metallix_b200.engine.generate import generate
+    folder, config, tensors, page = model_folders["A"]
+    prompts = [random_ids(i, n, config["vocab_size"]) for i, n in enumerate((5, 17, 31))]
+    engine = Engine.from_folder(folder, dtype="float32", page_tokens=page, num_pages=64)
+    results = generate(engine, prompts, max_new_tokens=16, eos_ids=())
+    for prompt, result in zip(prompts, results):
+        expected, gaps = plain_greedy(config, tensors, prompt, 16)
+        assert min(gaps) > 1e-4, "a near tie would make the comparison meaningless"
+        assert result.generated_ids == expected and result.finish_reason == "length"
+        assert result.cached_tokens == len(prompt) + 15
+    assert engine.manager.live_requests() == 0 and engine.manager.free_pages(0) == 64
+
+
+def test_greedy_bfloat16_agrees_outside_near_ties(model_folders):
+    """The reference's rule (crates/models/qwen/tests/bf16_agreement.rs:11-22):
+    bfloat16 may leave the float32 tokens only where the two best logits are
+    close."""
+    from metallix_b200.engine import Engine
+    from metallix_b200.engine.generate import generate
+    folder, config, tensors, page = model_folders["B"]
+    prompts = [random_ids(10 + i, n, config["vocab_size"]) for i, n in enumerate((9, 40, 63))]
+    engine = Engine.from_folder(folder, dtype="bfloat16", page_tokens=page, num_pages=64)
+    results = generate(engine, prompts, max_new_tokens=12, eos_ids=())
+    for prompt, result in zip(prompts, results):
+        expected, gaps = plain_greedy(config, tensors, prompt, 12)
+        for step, (got, want) in enumerate(zip(result.generated_ids, expected)):
+            if got != want:
+                assert gaps[step] < 0.05, (step, gaps[step])
+                break
+
+
+def test_sampled_workload_b_with_portions_and_a_small_pool(model_folders):
+    """Tiny B: prompts 1/9/40/63, portions of 16, 24 steps at temperature 0.7
+    with seed 7, pages of 8. A second run over a pool so small that requests
+    lose their pages and are computed again gives the same tokens, and both
+    follow the host definition of the sampler on the plain logits."""
+    from metallix_b200.engine import Engine
+    from metallix_b200.engine.generate import Generator, generate
+    from metallix_b200.sampling import SamplingParams
+    folder, config, tensors, page = model_folders["B"]
+    prompts = [random_ids(20 + i, n, config["vocab_size"]) for i, n in enumerate((1, 9, 40, 63))]
+    engine = Engine.from_folder(folder, dtype="float32", page_tokens=page, num_pages=64)
+    roomy = generate(engine, prompts, max_new_tokens=24, temperature=0.7, seed=7, eos_ids=(),
+                     max_num_seqs=4, prefill_chunk=16, max_tokens_per_step=40)
+    for index, (prompt, result) in enumerate(zip(prompts, roomy)):
+        ids = list(prompt)
+        for position, token in enumerate(result.generated_ids):
+            row = plain.forward_logits(config, tensors, ids)[-1].astype(np.float32)
+            uniform = plain.request_uniform(7, index, position)
+            expected = plain.sample_categorical(row, 0.7, uniform)
+            if expected != token:   # only a target within rounding of a boundary may differ
+                weights = np.exp((row.astype(np.float64) - row.max()) / 0.7)
+                cdf = np.cumsum(weights) / weights.sum()
+                assert min(abs(cdf[expected] - uniform), abs(cdf[token] - uniform)) < 1e-5
+            ids.append(token)
+        assert len(result.generated_ids) == 24
+    tight = Engine.from_folder(folder, dtype="float32", page_tokens=page, num_pages=22)
+    generator = Generator(tight, max_num_seqs=4, prefill_chunk=16, max_tokens_per_step=40)
+    ids = [generator.add(p, 24, SamplingParams(temperature=0.7, seed=7, stream=i)) for i, p in enumerate(prompts)]
+    generator.run()
+    assert generator.stats.preemptions > 0, "the pool was meant to run out"
+    assert [generator.result(r).generated_ids for r in ids] == [r.generated_ids for r in roomy]
+    assert tight.manager.free_pages(0) == 22
+
+
+def test_race_sampler_and_nucleus_through_generate(model_folders):
+    from metallix_b200.engine import Engine
+    from metallix_b200.engine.generate import generate
+    folder, config, tensors, page = model_folders["A"]
+    prompt = random_ids(31, 12, config["vocab_size"])
+    engine = Engine.from_folder(folder, dtype="float32", page_tokens=page, num_pages=64)
+    result = generate(engine, [prompt], max_new_tokens=8, temperature=0.9, seed=5, sampler="race",
+                      top_k=20, top_p=0.8, eos_ids=())[0]
+    ids = list(prompt)
+    for position, token in enumerate(result.generated_ids):
+        row = plain.forward_logits(config, tensors, ids)[-1].astype(np.float32)
+        legal = plain.nucleus_mask(row, 0.9, 0.8, 20)
+        assert legal[token]
+        assert token == plain.sample_race(row, 0.9, 5, position, legal=legal)
+        ids.append(token)
+
+
+def test_eos_stops_and_is_reported(model_folders):
+    from metallix_b200.engine import Engine
+    from metallix_b200.engine.generate import generate
+    folder, config, tensors, page = model_folders["A"]
+    prompt = random_ids(41, 9, config["vocab_size"])
+    engine = Engine.from_folder(folder, dtype="float32", page_tokens=page, num_pages=64)
+    free_run = generate(engine, [prompt], max_new_tokens=10, eos_ids=())[0].generated_ids
+    stop = free_run[3]
+    cut = free_run.index(stop) + 1
+    stopped = generate(engine, [prompt], max_new_tokens=10, eos_ids=(stop,))[0]
+    assert stopped.generated_ids == free_run[:cut] and stopped.finish_reason == "eos"
+    ignored = generate(engine, [prompt], max_new_tokens=10, eos_ids=(stop,), ignore_eos=True)[0]
+    assert ignored.generated_ids == free_run and ignored.finish_reason == "length"
+
+
+def test_command_line(model_folders, tmp_path):
+    folder, config, tensors, page = model_folders["A"]
+    prompt = random_ids(51, 7, config["vocab_size"])
+    expected, gaps = plain_greedy(config, tensors, prompt, 6)
+    assert min(gaps) > 1e-4
+    result = subprocess.run([sys.executable, os.path.join(ROOT, "bin", "mxb"), "gen", "--model", folder,
+                             "--input-ids", ",".join(map(str, prompt)), "--max-tokens", "6",
+                             "--dtype", "float32", "--block-size", str(page), "--num-pages", "32",
+                             "--verify-cache"], capture_output=True, text=True, timeout=600)
+    assert result.returncode == 0, result.stderr[-2000:]
+    report = json.loads(result.stdout.strip().splitlines()[-1])
+    assert report["generated_ids"] == expected and report["finish_reason"] == "length"
+    assert report["input_ids"] == prompt and report["cached_tokens"] == 7 + 5
+    assert report["logical_kv_bytes"] == 12 * 2 * 2 * 2 * 16 * 4   # tokens * layers * (K, V) * heads * dim * bytes
+    assert report["cache_comparisons"]["greedy_tokens_match"] is True
+    assert len(report["decode_ms"]) == 5

@@ -1,0 +1,406 @@
+"""Each CUDA kernel alone against its plain reference, at sizes other than the
+engine tests use: head sizes in steps of 16, head counts and groups of any
+size, widths and vocabularies that are no power of two."""
+import numpy as np
+import pytest
+import torch
+
+import plain_qwen3 as plain
+
+pytestmark = pytest.mark.gpu
+
+DTYPES = [torch.float32, torch.bfloat16]
+
+
+def dev(array, dtype=torch.float32):
+    return torch.tensor(np.asarray(array), dtype=dtype, device="cuda")
+
+
+def rounded(array, dtype):
+    """The values a tensor of ``dtype`` holds, as float64 numpy."""
+    return torch.tensor(np.asarray(array), dtype=dtype).double().numpy()
+
+
+def tol(dtype, f32=1e-5, bf16=2e-2):
+    return f32 if dtype == torch.float32 else bf16
+
+
+@pytest.fixture(scope="module")
+def ops():
+    from metallix_b200 import ops
+    ops.require_cuda()
+    return ops
+
+
+# ------------------------------------------------------------------ embedding
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_embed(ops, dtype):
+    rng = np.random.default_rng(0)
+    table = rng.normal(size=(331, 72))
+    ids = rng.integers(0, 331, size=19)
+    out = ops.embed(dev(ids, torch.int32), dev(table, dtype))
+    assert out.dtype == torch.float32
+    assert np.array_equal(out.cpu().double().numpy(), rounded(table, dtype)[ids])
+
+
+def test_embed_flags_a_bad_id(ops):
+    table = torch.zeros(10, 8, device="cuda")
+    ops.embed(torch.tensor([3, 10], dtype=torch.int32, device="cuda"), table)
+    with pytest.raises(ops.KernelError, match="token id"):
+        ops.check_status("cuda")
+    ops.check_status("cuda")  # cleared
+
+
+# ----------------------------------------------------------------------- norms
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("size", [24, 80, 1000, 3000])
+def test_rmsnorm(ops, dtype, size):
+    rng = np.random.default_rng(size)
+    x = rng.normal(size=(7, size)) * 3
+    w = 1 + rng.uniform(-0.1, 0.1, size=size)
+    eps = 3e-5
+    out = ops.rmsnorm(dev(x), dev(w), eps, dtype)
+    ref = plain.rms_norm(rounded(x, torch.float32), rounded(w, torch.float32), eps)
+    assert np.abs(out.cpu().double().numpy() - ref).max() < tol(dtype, 2e-6, 4e-2)
+    picked = ops.rmsnorm(dev(x), dev(w), eps, dtype, rows_index=dev([5, 0, 5], torch.int32))
+    assert torch.equal(picked, out[[5, 0, 5]])
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_add_rmsnorm_sums_in_float32(ops, dtype):
+    rng = np.random.default_rng(1)
+    x = rng.normal(size=(5, 136))
+    delta = rng.normal(size=(5, 136))
+    w = 1 + rng.uniform(-0.1, 0.1, size=136)
+    residual = dev(x)
+    out = ops.add_rmsnorm(residual, dev(delta, dtype), dev(w), 1e-6, dtype)
+    total = rounded(x, torch.float32) + rounded(delta, dtype)
+    assert np.abs(residual.cpu().double().numpy() - total).max() < 1e-6   # the sum itself stays float32
+    ref = plain.rms_norm(total, rounded(w, torch.float32), 1e-6)
+    assert np.abs(out.cpu().double().numpy() - ref).max() < tol(dtype, 2e-6, 2e-2)
+    again = dev(x)
+    ops.add_(again, dev(delta, dtype))
+    assert torch.equal(again, residual)
+
+
+# ------------------------------------------------- q/k norm, rotation, cache
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("heads, kv_heads, head_dim, rotary", [(5, 5, 16, 16), (6, 2, 48, 48),
+                                                              (3, 1, 112, 112), (4, 2, 64, 32)])
+def test_qk_norm_rope_cache(ops, dtype, heads, kv_heads, head_dim, rotary):
+    rng = np.random.default_rng(heads * head_dim)
+    tokens, page_tokens, pages, theta, eps = 11, 4, 9, 1e4, 1e-5
+    width = (heads + 2 * kv_heads) * head_dim
+    qkv = rng.normal(size=(tokens, width))
+    positions = rng.integers(0, 200, size=tokens)
+    slots = rng.permutation(pages * page_tokens)[:tokens]
+    slots[3] = -1  # this token writes nothing
+    qw, kw = 1 + rng.uniform(-0.1, 0.1, size=(2, head_dim))
+    half = rotary // 2
+    angle = np.arange(256)[:, None] * theta ** (-2.0 * np.arange(half) / rotary)[None, :]
+    qkv_d = dev(qkv, dtype)
+    q_out = torch.empty(tokens, heads, head_dim, dtype=dtype, device="cuda")
+    cache = torch.zeros(pages, 2, kv_heads, page_tokens, head_dim, dtype=dtype, device="cuda")
+    q_size, kv_size = heads * head_dim, kv_heads * head_dim
+    ops.qk_norm_rope_cache(qkv_d[:, :q_size], qkv_d[:, q_size:q_size + kv_size], qkv_d[:, q_size + kv_size:],
+                           q_out, cache, dev(slots, torch.int32), dev(positions, torch.int32), dev(qw), dev(kw),
+                           dev(np.cos(angle)), dev(np.sin(angle)), eps)
+    ops.check_status("cuda")
+    stored = rounded(qkv, dtype)
+    q = stored[:, :q_size].reshape(tokens, heads, head_dim)
+    k = stored[:, q_size:q_size + kv_size].reshape(tokens, kv_heads, head_dim)
+    v = stored[:, q_size + kv_size:].reshape(tokens, kv_heads, head_dim)
+
+    def norm_rotate(x, w):
+        x = plain.rms_norm(x, rounded(w, torch.float32), eps)
+        turned = plain.rope_half(x[..., :rotary], positions, theta)
+        return np.concatenate([turned, x[..., rotary:]], axis=-1)
+
+    q_ref, k_ref = norm_rotate(q, qw), norm_rotate(k, kw)
+    limit = tol(dtype, 5e-6, 3e-2)
+    assert np.abs(q_out.cpu().double().numpy() - q_ref).max() < limit
+    got = cache.cpu().double().numpy()
+    expected = np.zeros_like(got)
+    for t in range(tokens):
+        if slots[t] < 0:
+            continue
+        page, row = divmod(int(slots[t]), page_tokens)
+        expected[page, 0, :, row] = k_ref[t]
+        expected[page, 1, :, row] = v[t]
+    assert np.abs(got - expected).max() < limit
+    assert np.array_equal(got[:, 1], expected[:, 1])  # values are stored as projected
+
+
+def test_rotation_keeps_accuracy_at_far_positions(ops):
+    """cos and sin come from a float64 table: at position 4000 a float32
+    product of position and frequency would already be off by 1e-4."""
+    head_dim, theta = 64, 1e6
+    positions = np.array([0, 1, 4000, 8191])
+    x = np.random.default_rng(2).normal(size=(4, 2 * head_dim))
+    angle = np.arange(8192)[:, None] * theta ** (-2.0 * np.arange(head_dim // 2) / head_dim)[None, :]
+    out = ops.norm_rotate_heads(dev(x), head_dim, dev(positions, torch.int32), cos=dev(np.cos(angle)),
+                                sin=dev(np.sin(angle)))
+    ref = plain.rope_half(rounded(x, torch.float32).reshape(4, 2, head_dim), positions, theta)
+    assert np.abs(out.cpu().double().numpy() - ref).max() < 2e-6
+
+
+# ------------------------------------------------------------------ attention
+def run_attention(ops, dtype, q, k, v, lengths, page_tokens, scale, window=0, shuffle_seed=0):
+    """Several requests; request r's last ``lengths[r][1]`` positions are the
+    queries, all ``lengths[r][0]`` positions sit in a cache whose pages are
+    handed out in shuffled order."""
+    heads, head_dim = q[0].shape[1], q[0].shape[2]
+    kv_heads = k[0].shape[1]
+    rng = np.random.default_rng(shuffle_seed)
+    pages_needed = [-(-total // page_tokens) for total, _ in lengths]
+    order = rng.permutation(sum(pages_needed) + 3)
+    cache = torch.zeros(len(order), 2, kv_heads, page_tokens, head_dim, dtype=dtype, device="cuda")
+    host_cache = np.zeros(cache.shape)
+    width = max(pages_needed)
+    tables = np.full((len(lengths), width), -1, dtype=np.int32)
+    cursor = 0
+    q_rows, positions, tile_request, tile_start, tile_length = [], [], [], [], []
+    for r, (total, queries) in enumerate(lengths):
+        tables[r, :pages_needed[r]] = order[cursor:cursor + pages_needed[r]]
+        cursor += pages_needed[r]
+        for p in range(total):
+            page, row = tables[r, p // page_tokens], p % page_tokens
+            host_cache[page, 0, :, row] = k[r][p]
+            host_cache[page, 1, :, row] = v[r][p]
+        begin = len(positions)
+        q_rows.append(q[r][total - queries:])
+        positions += list(range(total - queries, total))
+        for first in range(0, queries, 16):
+            tile_request.append(r)
+            tile_start.append(begin + first)
+            tile_length.append(min(16, queries - first))
+    cache.copy_(dev(host_cache, dtype))
+    q_all = dev(np.concatenate(q_rows), dtype)
+    out = torch.empty_like(q_all)
+    ops.paged_attention_tile(q_all, cache, out, dev(tables, torch.int32), dev(tile_request, torch.int32),
+                             dev(tile_start, torch.int32), dev(tile_length, torch.int32),
+                             dev(positions, torch.int32), scale, window)
+    ops.check_status("cuda")
+    return out.cpu().double().numpy()
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("heads, kv_heads, head_dim, page_tokens", [(4, 4, 16, 4), (6, 2, 48, 8),
+                                                                   (5, 1, 80, 16), (8, 2, 128, 32),
+                                                                   (2, 1, 256, 16)])
+def test_paged_attention_mixed_batch(ops, dtype, heads, kv_heads, head_dim, page_tokens):
+    rng = np.random.default_rng(head_dim + heads)
+    lengths = [(70, 70), (45, 1), (33, 17), (100, 2), (1, 1)]  # (positions, of which queries)
+    q = [rounded(rng.normal(size=(n, heads, head_dim)), dtype) for n, _ in lengths]
+    k = [rounded(rng.normal(size=(n, kv_heads, head_dim)), dtype) for n, _ in lengths]
+    v = [rounded(rng.normal(size=(n, kv_heads, head_dim)), dtype) for n, _ in lengths]
+    scale = head_dim ** -0.5
+    out = run_attention(ops, dtype, q, k, v, lengths, page_tokens, scale)
+    cursor = 0
+    for r, (total, queries) in enumerate(lengths):
+        ref = plain.causal_gqa_attention(q[r], k[r], v[r], scale)[total - queries:]
+        got = out[cursor:cursor + queries]
+        cursor += queries
+        assert np.abs(got - ref).max() < tol(dtype, 5e-6, 2e-2), (r, total, queries)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("window", [1, 5, 16, 33])
+def test_paged_attention_window(ops, dtype, window):
+    rng = np.random.default_rng(window)
+    heads, kv_heads, head_dim = 4, 2, 32
+    lengths = [(90, 90), (77, 1), (50, 9)]
+    q = [rounded(rng.normal(size=(n, heads, head_dim)), dtype) for n, _ in lengths]
+    k = [rounded(rng.normal(size=(n, kv_heads, head_dim)), dtype) for n, _ in lengths]
+    v = [rounded(rng.normal(size=(n, kv_heads, head_dim)), dtype) for n, _ in lengths]
+    out = run_attention(ops, dtype, q, k, v, lengths, 8, 0.25, window=window)
+    cursor = 0
+    for r, (total, queries) in enumerate(lengths):
+        ref = plain.causal_gqa_attention(q[r], k[r], v[r], 0.25, window=window)[total - queries:]
+        assert np.abs(out[cursor:cursor + queries] - ref).max() < tol(dtype, 5e-6, 2e-2)
+        cursor += queries
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_one_far_key_among_hundreds(ops, dtype):
+    """Random keys would average a lost key away. Here one key matches the
+    query so strongly that the output must be that key's value: at the first
+    position, around page and tile edges, and at the query itself."""
+    heads, kv_heads, head_dim, page_tokens, total = 2, 1, 64, 16, 700
+    rng = np.random.default_rng(9)
+    for target in (0, 15, 16, 31, 32, 511, 512, 683, 698, 699):
+        k = rounded(rng.normal(size=(total, kv_heads, head_dim)) * 0.1, dtype)
+        v = rounded(rng.normal(size=(total, kv_heads, head_dim)), dtype)
+        q = rounded(rng.normal(size=(total, heads, head_dim)) * 0.1, dtype)
+        k[target, 0, :] = 0.0
+        k[target, 0, 7] = 16.0
+        q[-1, :, 7] = 16.0   # score 256 * scale = 32 above everything else
+        out = run_attention(ops, dtype, [q], [k], [v], [(total, 1)], page_tokens, head_dim ** -0.5,
+                            shuffle_seed=target)
+        assert np.abs(out[0] - v[target, 0]).max() < tol(dtype, 1e-5, 1e-2), target
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_window_edge(ops, dtype):
+    """The strong key sits exactly on the window's edge: one position inside
+    it is seen, one position outside it is not."""
+    heads, kv_heads, head_dim, total, window = 2, 1, 32, 200, 48
+    rng = np.random.default_rng(10)
+    k = rounded(rng.normal(size=(total, kv_heads, head_dim)) * 0.1, dtype)
+    v = rounded(rng.normal(size=(total, kv_heads, head_dim)), dtype)
+    q = rounded(rng.normal(size=(total, heads, head_dim)) * 0.1, dtype)
+    q[-1, :, 3] = 16.0
+    for target, seen in ((total - window, True), (total - window - 1, False)):
+        keys = k.copy()
+        keys[target, 0, :] = 0.0
+        keys[target, 0, 3] = 16.0
+        out = run_attention(ops, dtype, [q], [keys], [v], [(total, 1)], 16, head_dim ** -0.5, window=window)
+        near = np.abs(out[0] - v[target, 0]).max() < 1e-2
+        assert near == seen, (target, seen)
+
+
+def test_attention_does_not_depend_on_the_cut(ops):
+    """float32: the same query gives the same bits alone, in a tile of 16 and
+    beside other requests."""
+    rng = np.random.default_rng(11)
+    heads, kv_heads, head_dim, total = 3, 1, 48, 130
+    q = [rng.normal(size=(total, heads, head_dim))]
+    k = [rng.normal(size=(total, kv_heads, head_dim))]
+    v = [rng.normal(size=(total, kv_heads, head_dim))]
+    whole = run_attention(ops, torch.float32, q, k, v, [(total, total)], 8, 0.3)
+    last = run_attention(ops, torch.float32, q, k, v, [(total, 1)], 8, 0.3, shuffle_seed=5)
+    part = run_attention(ops, torch.float32, q + q, k + k, v + v, [(total, 37), (total - 9, 3)], 8, 0.3,
+                         shuffle_seed=6)
+    assert np.array_equal(last[0], whole[-1])
+    assert np.array_equal(part[:37], whole[-37:])
+    assert np.array_equal(part[37:], whole[total - 12:total - 9])
+
+
+def test_attention_flags_a_bad_page(ops):
+    q = torch.zeros(1, 1, 16, device="cuda")
+    cache = torch.zeros(2, 2, 1, 4, 16, device="cuda")
+    table = torch.tensor([[0, 7]], dtype=torch.int32, device="cuda")
+    one = torch.tensor([0], dtype=torch.int32, device="cuda")
+    ops.paged_attention_tile(q, cache, torch.empty_like(q), table, one, one, one + 0,
+                             torch.tensor([5], dtype=torch.int32, device="cuda"), 1.0)
+    with pytest.raises(ops.KernelError, match="block-table"):
+        ops.check_status("cuda")
+
+
+# ------------------------------------------------------------ matrix products
+@pytest.mark.parametrize("m, n, k", [(1, 331, 80), (7, 96, 224), (64, 200, 72), (130, 65, 1000)])
+def test_gemm_simple_float32_is_true_32_bit(ops, m, n, k):
+    rng = np.random.default_rng(m + n)
+    a, w = rng.normal(size=(m, k)), rng.normal(size=(n, k))
+    out = ops.gemm_simple(dev(a), dev(w))
+    ref = rounded(a, torch.float32) @ rounded(w, torch.float32).T
+    # float32 products and sums: error of a few ulp times sqrt(k), far below
+    # what a reduced-precision matrix mode (10 mantissa bits) would leave
+    assert np.abs(out.cpu().double().numpy() - ref).max() < 2e-5 * np.sqrt(k / 64)
+    one_row = ops.gemm_simple(dev(a[3:4] if m > 3 else a[:1]), dev(w))
+    assert torch.equal(one_row[0], out[3 if m > 3 else 0])   # a row does not depend on the batch
+
+
+@pytest.mark.parametrize("backend", ["simple", "cublas", "auto"])
+@pytest.mark.parametrize("m, n, k", [(1, 384, 96), (5, 200, 136), (64, 331, 80), (300, 448, 192)])
+def test_gemm_bf16(ops, backend, m, n, k):
+    rng = np.random.default_rng(n)
+    a, w = rng.normal(size=(m, k)), rng.normal(size=(n, k))
+    ref = rounded(a, torch.bfloat16) @ rounded(w, torch.bfloat16).T
+    out32 = ops.gemm_bf16(dev(a, torch.bfloat16), dev(w, torch.bfloat16), torch.float32, backend=backend)
+    assert out32.dtype == torch.float32
+    assert np.abs(out32.cpu().double().numpy() - ref).max() < 1e-3
+    out16 = ops.gemm_bf16(dev(a, torch.bfloat16), dev(w, torch.bfloat16), torch.bfloat16, backend=backend)
+    assert np.abs(out16.cpu().double().numpy() - ref).max() < 0.02 * np.abs(ref).max()
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_silu_mul(ops, dtype):
+    rng = np.random.default_rng(4)
+    gate_up = rng.normal(size=(9, 2 * 136)) * 3
+    out = ops.silu_mul(dev(gate_up, dtype))
+    g, u = rounded(gate_up, dtype)[:, :136], rounded(gate_up, dtype)[:, 136:]
+    ref = g / (1 + np.exp(-g)) * u
+    assert np.abs(out.cpu().double().numpy() - ref).max() < tol(dtype, 5e-6, 5e-2)
+
+
+# -------------------------------------------------------------------- picking
+def test_argmax_first_maximum_and_finite_flag(ops):
+    rng = np.random.default_rng(5)
+    logits = rng.normal(size=(6, 151_937)).astype(np.float32)
+    logits[0, [100, 90_000]] = 9.0          # a tie: the lower id wins
+    logits[1, 151_936] = 11.0               # the last vocabulary row
+    logits[2, 0] = 12.0
+    ids = ops.argmax(dev(logits)).tolist()
+    ops.check_status("cuda")
+    assert ids == [plain.greedy_pick(row) for row in logits] and ids[:3] == [100, 151_936, 0]
+    logits[4, 77] = np.inf
+    ids = ops.argmax(dev(logits)).tolist()
+    assert ids[4] == -1 and ids[3] == plain.greedy_pick(logits[3])
+    with pytest.raises(ops.KernelError, match="non-finite"):
+        ops.check_status("cuda")
+
+
+@pytest.mark.parametrize("vocab", [8, 331, 5000])
+def test_sample_icdf_matches_the_host_definition(ops, vocab):
+    rng = np.random.default_rng(vocab)
+    rows = 40
+    logits = (rng.normal(size=(rows, vocab)) * 2).astype(np.float32)
+    temperature = rng.uniform(0.3, 1.5, size=rows)
+    seeds = rng.integers(0, 2 ** 63, size=rows)
+    streams = rng.integers(0, 2 ** 40, size=rows)
+    positions = rng.integers(0, 5000, size=rows)
+    ids = ops.sample_icdf(dev(logits), dev(temperature, torch.float64), dev(seeds, torch.int64),
+                          dev(streams, torch.int64), dev(positions, torch.int32)).tolist()
+    ops.check_status("cuda")
+    for r in range(rows):
+        uniform = plain.request_uniform(int(seeds[r]), int(streams[r]), int(positions[r]))
+        assert ids[r] == plain.sample_categorical(logits[r], float(temperature[r]), uniform), r
+
+
+def test_sample_icdf_legal_mask_and_law(ops):
+    logits = np.array([[0.3, -0.6, 1.1, 0.0, 0.7, 2.0]], dtype=np.float32).repeat(4000, axis=0)
+    legal = np.array([[1, 1, 1, 1, 1, 0]], dtype=np.uint8).repeat(4000, axis=0)
+    temperature = np.full(4000, 0.6)
+    ids = ops.sample_icdf(dev(logits), dev(temperature, torch.float64),
+                          dev(np.full(4000, 11), torch.int64), dev(np.zeros(4000), torch.int64),
+                          dev(np.arange(4000), torch.int32), dev(legal, torch.uint8)).cpu().numpy()
+    counts = np.bincount(ids, minlength=6)
+    assert counts[5] == 0
+    weights = np.exp(logits[0, :5].astype(np.float64) / 0.6)
+    expected = weights / weights.sum() * 4000
+    assert (((counts[:5] - expected) ** 2) / expected).sum() < 40.0   # race.rs:292-330 uses the same bound
+
+
+def test_sample_race_matches_the_reference_tokens(ops):
+    import json, os
+    golden = json.load(open(os.path.join(os.path.dirname(__file__), "golden",
+                                         "reference_sampler_vectors.json")))["race_v2_tokens"]
+    rows = len(golden["tokens"])
+    logits = np.array([golden["logits"]], dtype=np.float32).repeat(rows, axis=0)
+    legal = np.array([golden["legal"]], dtype=np.uint8).repeat(rows, axis=0)
+    ids = ops.sample_race(dev(logits), dev(np.full(rows, golden["temperature"]), torch.float64),
+                          dev(np.full(rows, golden["seed"]), torch.int64),
+                          dev(np.arange(rows), torch.int32), dev(legal, torch.uint8)).tolist()
+    assert ids == golden["tokens"]
+    rng = np.random.default_rng(6)
+    big = (rng.normal(size=(5, 3001)) * 2).astype(np.float32)
+    ids = ops.sample_race(dev(big), dev(np.full(5, 0.8), torch.float64), dev(np.arange(5) + 2 ** 33, torch.int64),
+                          dev(np.arange(5) * 7, torch.int32)).tolist()
+    assert ids == [plain.sample_race(big[r], 0.8, r + 2 ** 33, r * 7) for r in range(5)]
+
+
+@pytest.mark.parametrize("top_p, top_k", [(1.0, 5), (0.7, 0), (0.35, 12), (0.9, 1), (1.0, 0), (0.999, 4000)])
+def test_nucleus_mask(ops, top_p, top_k):
+    rng = np.random.default_rng(int(top_p * 100) + top_k)
+    logits = (rng.normal(size=(6, 3000)) * 1.5).astype(np.float32)
+    logits[1, :40] = logits[1, 0]        # many equal logits across the cut
+    logits[2, :] = 0.25                  # all equal
+    logits[3] = np.round(logits[3])      # many ties everywhere
+    temperature = np.array([1.0, 0.7, 1.0, 0.5, 2.0, 0.9])
+    mask = ops.nucleus_mask(dev(logits), dev(temperature, torch.float64), dev(np.full(6, top_p), torch.float64),
+                            dev(np.full(6, top_k), torch.int32)).cpu().numpy().astype(bool)
+    ops.check_status("cuda")
+    for r in range(6):
+        ref = plain.nucleus_mask(logits[r], float(temperature[r]), top_p, top_k or None)
+        assert np.array_equal(mask[r], ref), (r, mask[r].sum(), ref.sum())

@@ -1,0 +1,262 @@
+"""Each part alone against the plain implementation, the layer order as data,
+and a toy mixer with state of its own that is defined here, registered, built
+and stepped without any change to the framework's files."""
+import dataclasses
+
+import numpy as np
+import pytest
+import torch
+
+import plain_qwen3 as plain
+from conftest import TOL_BF16_VS_EXACT, TOL_F32, random_ids
+
+pytestmark = pytest.mark.gpu
+
+
+def runtime(dtype, max_positions=512):
+    from metallix_b200.parts import Runtime
+    return Runtime(device=torch.device("cuda:0"), dtype=dtype, max_positions=max_positions)
+
+
+def store(tensors):
+    from metallix_b200.parts import WeightStore
+    return WeightStore({k: torch.tensor(v) for k, v in tensors.items()})
+
+
+def context(dtype, counts, starts):
+    """A StepContext for requests with ``counts`` tokens starting at ``starts``."""
+    from metallix_b200.parts import StepContext
+    positions, token_request, tile_request, tile_start, tile_length, offsets = [], [], [], [], [], [0]
+    for row, (count, start) in enumerate(zip(counts, starts)):
+        begin = len(positions)
+        positions += list(range(start, start + count))
+        token_request += [row] * count
+        for first in range(0, count, 16):
+            tile_request.append(row)
+            tile_start.append(begin + first)
+            tile_length.append(min(16, count - first))
+        offsets.append(len(positions))
+    as_int = lambda v: torch.tensor(v, dtype=torch.int32, device="cuda")
+    return StepContext(device=torch.device("cuda:0"), dtype=dtype, num_tokens=len(positions),
+                       num_requests=len(counts), positions=as_int(positions),
+                       token_request=as_int(token_request), request_slots=as_int(list(range(len(counts)))),
+                       request_offsets=offsets, request_positions=list(starts),
+                       tile_request=as_int(tile_request), tile_start=as_int(tile_start),
+                       tile_length=as_int(tile_length))
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_norm_part(dtype):
+    from metallix_b200.config import PartSpec
+    from metallix_b200.parts import build_part
+    rng = np.random.default_rng(0)
+    w = (1 + rng.uniform(-0.1, 0.1, size=72)).astype(np.float32)
+    norm = build_part("norm", PartSpec("rmsnorm", {"size": 72, "eps": 2e-5, "weight": "n.weight"}),
+                      store({"n.weight": w}), runtime(dtype))
+    x = rng.normal(size=(5, 72)).astype(np.float32)
+    delta = rng.normal(size=(5, 72)).astype(np.float32)
+    residual = torch.tensor(x, device="cuda")
+    out = norm.add_forward(residual, torch.tensor(delta, device="cuda").to(dtype), dtype)
+    total = x.astype(np.float64) + torch.tensor(delta).to(dtype).double().numpy()
+    ref = plain.rms_norm(total, w.astype(np.float64), float(np.float32(2e-5)))
+    assert np.abs(out.cpu().double().numpy() - ref).max() < (2e-6 if dtype == torch.float32 else 2e-2)
+    assert np.abs(residual.cpu().double().numpy() - total).max() < 1e-6
+    with pytest.raises(ValueError):
+        build_part("norm", PartSpec("rmsnorm", {"size": 71, "eps": 1e-6, "weight": "n.weight"}),
+                   store({"n.weight": w}), runtime(dtype))
+
+
+def test_position_part():
+    from metallix_b200.config import PartSpec
+    from metallix_b200.parts import build_part
+    rope = build_part("position", PartSpec("rope_half", {"theta": 5e4, "rotary_dim": 48, "head_dim": 48}),
+                      store({}), runtime(torch.float32, 300))
+    rng = np.random.default_rng(1)
+    q, k = rng.normal(size=(6, 3 * 48)).astype(np.float32), rng.normal(size=(6, 48)).astype(np.float32)
+    positions = [0, 1, 2, 150, 151, 299]
+    q_out, k_out = rope.apply(torch.tensor(q, device="cuda"), torch.tensor(k, device="cuda"),
+                              torch.tensor(positions, dtype=torch.int32, device="cuda"))
+    assert np.abs(q_out.cpu().double().numpy()
+                  - plain.rope_half(q.astype(np.float64).reshape(6, 3, 48), positions, 5e4)).max() < 2e-6
+    assert np.abs(k_out.cpu().double().numpy()
+                  - plain.rope_half(k.astype(np.float64).reshape(6, 1, 48), positions, 5e4)).max() < 2e-6
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_feed_forward_part(dtype):
+    from metallix_b200.config import PartSpec
+    from metallix_b200.parts import build_part
+    rng = np.random.default_rng(2)
+    hidden, inter = 72, 200
+    weights = {"g": rng.normal(size=(inter, hidden)) * 0.1, "u": rng.normal(size=(inter, hidden)) * 0.1,
+               "d": rng.normal(size=(hidden, inter)) * 0.1}
+    weights = {k: torch.tensor(v).to(dtype).double().numpy() for k, v in weights.items()}
+    part = build_part("feed_forward", PartSpec("swiglu", {
+        "hidden_size": hidden, "intermediate_size": inter, "gate_proj": "g", "up_proj": "u",
+        "down_proj": "d"}), store(weights), runtime(dtype))
+    x = torch.tensor(rng.normal(size=(9, hidden))).to(dtype)
+    out = part.forward(x.cuda(), None)
+    ref = plain.swiglu(x.double().numpy(), weights["g"], weights["u"], weights["d"])
+    assert np.abs(out.cpu().double().numpy() - ref).max() < (1e-5 if dtype == torch.float32 else 3e-2)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_attention_part_with_its_cache(model_folders, dtype):
+    """The mixer alone: a prompt portion, then the rest beside another
+    request's tokens, against whole-sequence attention."""
+    from metallix_b200.config import Qwen3Config
+    from metallix_b200.parts import CacheView, build_part
+    _, config, tensors, _ = model_folders["B"]
+    spec = Qwen3Config.from_dict(config).to_model_spec().layers[1].mixer
+    mixer = build_part("mixer", spec, store(tensors), runtime(dtype))
+    need = mixer.cache_need()
+    assert (need.kind, need.kv_heads, need.head_dim, need.window) == ("kv_pages", 2, 32, None)
+    rng = np.random.default_rng(3)
+    x = torch.tensor(rng.normal(size=(50, 96))).to(dtype)
+    ref = plain.attention_block(x.double().numpy(), np.arange(50), tensors, "model.layers.1.self_attn", config)
+    pool = torch.zeros(16, 2, 2, 8, 32, dtype=dtype, device="cuda")
+    tables = torch.tensor([[5, 2, 9, 0, 11, 3, 7], [1, 4, 6, 8, 10, 12, 13]], dtype=torch.int32, device="cuda")
+
+    def slots(row, start, count):
+        where = np.arange(start, start + count)
+        return tables[row].cpu().numpy()[where // 8] * 8 + where % 8
+
+    def run(counts, starts, rows, xs):
+        ctx = context(dtype, counts, starts)
+        all_slots = np.concatenate([slots(r, s, c) for r, s, c in zip(rows, starts, counts)])
+        view = CacheView(need=need, pool=pool, block_tables=tables[rows],
+                         slots=torch.tensor(all_slots, dtype=torch.int32, device="cuda"))
+        return mixer.forward(torch.cat(xs).cuda(), ctx, view).cpu().double().numpy()
+
+    limit = 1e-5 if dtype == torch.float32 else 3e-2
+    first = run([30], [0], [0], [x[:30]])
+    assert np.abs(first - ref[:30]).max() < limit
+    other = run([7], [0], [1], [x[:7]])          # another request starts in its own pages
+    both = run([20, 5], [30, 7], [0, 1], [x[30:], x[7:12]])
+    assert np.abs(both[:20] - ref[30:]).max() < limit
+    assert np.abs(np.concatenate([other, both[20:]]) - ref[:12]).max() < limit
+
+
+def test_layer_order_is_data(model_folders):
+    """A layer named twice (with a cache entry of its own for the second run)
+    and a layer that reads the cache another layer wrote."""
+    from metallix_b200.config import LayerRun, Qwen3Config
+    from metallix_b200.engine import Engine, StepEntry
+    from metallix_b200.weights import load_tensors
+    folder, config, tensors, page = model_folders["B"]
+    typed = Qwen3Config.from_dict(config)
+    ids = random_ids(8, 45, config["vocab_size"])
+    cases = {
+        "twice": ([LayerRun(0), LayerRun(1), LayerRun(1, cache=3), LayerRun(2)], [0, 1, 1, 2], None),
+        "reads": ([LayerRun(0), LayerRun(1), LayerRun(2, cache=1, write_cache=False)], [0, 1, 2], {2: 1}),
+    }
+    for label, (order, layers, reads) in cases.items():
+        spec = dataclasses.replace(typed.to_model_spec(), order=tuple(order))
+        reference = plain.forward_logits(config, tensors, ids, order=layers, reads=reads)
+        engine = Engine(typed, load_tensors(folder, typed, device="cuda:0"), dtype="float32",
+                        page_tokens=page, num_pages=32, spec=spec)
+        whole = engine.step([StepEntry("w", ids, list(range(45)))]).cpu().double().numpy()
+        assert np.abs(whole - reference).max() < TOL_F32, label
+        parts = [engine.step([StepEntry("p", ids[:20], [19])]), engine.step([StepEntry("p", ids[20:44], [23])]),
+                 engine.step([StepEntry("p", ids[44:], [0])])]
+        got = np.stack([p.cpu().double().numpy()[0] for p in parts])
+        assert np.abs(got - reference[[19, 43, 44]]).max() < TOL_F32, label
+        if label == "reads":
+            assert len(engine.cache.groups[0].entries) == 2   # layer 2 holds no pages of its own
+    with pytest.raises(ValueError, match="before any layer has written"):
+        dataclasses.replace(typed.to_model_spec(), order=(LayerRun(0, cache=1, write_cache=False),)).validate()
+
+
+# ----------------------------------------------------------------- a toy mixer
+class RunningMeanMixer:
+    """out_t = mean over the request's positions 0..t of (x W^T). The running
+    sum is state of fixed size per request; no pages. Torch operations only:
+    it stands for a mixer somebody else wrote."""
+
+    def __init__(self, spec, weights, runtime):
+        self.weight = weights.take(spec["weight"]).to(runtime.device, torch.float32)
+        self.hidden = spec["hidden_size"]
+        self.dtype = runtime.dtype
+
+    def cache_need(self):
+        from metallix_b200.config import CacheNeed
+        return CacheNeed(kind="state", state_shape=(self.hidden,), state_dtype="float32")
+
+    def forward(self, x, ctx, cache):
+        projected = x.float() @ self.weight.t()
+        out = torch.empty_like(projected)
+        for row in range(ctx.num_requests):
+            begin, end = ctx.request_offsets[row], ctx.request_offsets[row + 1]
+            slot = int(ctx.request_slots[row])
+            sums = cache.state[slot] + torch.cumsum(projected[begin:end], dim=0)
+            counts = torch.arange(ctx.request_positions[row] + 1, ctx.request_positions[row] + 1 + end - begin,
+                                  device=x.device, dtype=torch.float32)
+            out[begin:end] = sums / counts[:, None]
+            cache.state[slot] = sums[-1]
+        return out.to(self.dtype)
+
+
+def plain_with_running_mean(config, tensors, ids, toy_layer, toy_weight):
+    """The plain model with layer ``toy_layer``'s attention replaced by the
+    running mean."""
+    w = {k: v.astype(np.float64) for k, v in tensors.items()}
+    x = plain.embed(w["model.embed_tokens.weight"], ids)
+    eps = plain.f32(config["rms_norm_eps"])
+    positions = np.arange(len(ids))
+    for layer in range(config["num_hidden_layers"]):
+        base = f"model.layers.{layer}"
+        if layer != toy_layer:
+            x = plain.decoder_layer(x, positions, w, layer, config)
+            continue
+        mixed_in = plain.rms_norm(x, w[f"{base}.input_layernorm.weight"], eps)
+        projected = mixed_in @ toy_weight.T
+        residual = x + np.cumsum(projected, axis=0) / (positions + 1)[:, None]
+        mlp_in = plain.rms_norm(residual, w[f"{base}.post_attention_layernorm.weight"], eps)
+        x = residual + plain.swiglu(mlp_in, w[f"{base}.mlp.gate_proj.weight"], w[f"{base}.mlp.up_proj.weight"],
+                                    w[f"{base}.mlp.down_proj.weight"])
+    normed = plain.rms_norm(x, w["model.norm.weight"], eps)
+    return normed @ w["lm_head.weight"].T
+
+
+def test_a_toy_mixer_with_state_of_its_own(model_folders):
+    from metallix_b200.config import PartSpec, Qwen3Config
+    from metallix_b200.engine import Engine, StepEntry
+    from metallix_b200.parts import register_part, unregister_part
+    from metallix_b200.weights import load_tensors
+    folder, config, tensors, page = model_folders["B"]
+    typed = Qwen3Config.from_dict(config)
+    register_part("mixer", "running_mean", RunningMeanMixer)
+    try:
+        base = typed.to_model_spec()
+        layers = list(base.layers)
+        layers[1] = dataclasses.replace(layers[1], mixer=PartSpec("running_mean", {
+            "hidden_size": 96, "weight": "toy.weight"}))
+        spec = dataclasses.replace(base, layers=tuple(layers))
+        toy = np.random.default_rng(4).normal(size=(96, 96)) * 0.05
+        loaded = load_tensors(folder, typed, device="cuda:0")
+        loaded["toy.weight"] = torch.tensor(toy, dtype=torch.float32, device="cuda:0")
+        engine = Engine(typed, loaded, dtype="float32", page_tokens=page, num_pages=32, max_requests=3,
+                        spec=spec)
+        # one group of pages for the two attention layers, one state entry for the toy
+        assert len(engine.cache.groups) == 1 and engine.cache.groups[0].entries == [0, 2]
+        assert list(engine.cache.states) == [1] and engine.cache.states[1].shape == (3, 96)
+        requests = {"a": random_ids(1, 40, 384), "b": random_ids(2, 23, 384), "c": random_ids(3, 31, 384)}
+        reference = {k: plain_with_running_mean(config, tensors, ids, 1, toy) for k, ids in requests.items()}
+        whole = engine.step([StepEntry("a", requests["a"], list(range(40)))]).cpu().double().numpy()
+        assert np.abs(whole - reference["a"]).max() < 5e-5
+        engine.release("a")
+        # mixed: portions of one request beside another's single tokens; "c"
+        # later takes the slot that "b" gives back and must start from zero
+        a, b, c = requests["a"], requests["b"], requests["c"]
+        engine.step([StepEntry("a", a[:17], [])])
+        engine.step([StepEntry("b", b[:22], [])])
+        logits = engine.step([StepEntry("a", a[17:39], [21]), StepEntry("b", b[22:], [0])]).cpu().double().numpy()
+        assert np.abs(logits[0] - reference["a"][38]).max() < 5e-5
+        assert np.abs(logits[1] - reference["b"][22]).max() < 5e-5
+        engine.release("b")
+        logits = engine.step([StepEntry("a", a[39:], [0]), StepEntry("c", c, [30])]).cpu().double().numpy()
+        assert np.abs(logits[0] - reference["a"][39]).max() < 5e-5
+        assert np.abs(logits[1] - reference["c"][30]).max() < 5e-5
+        engine.check()
+    finally:
+        unregister_part("mixer", "running_mean")
