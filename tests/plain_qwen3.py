@@ -276,7 +276,10 @@ def nucleus_mask(logits, temperature, top_p, top_k=None):
     if top_p >= 1.0 and top_k is None:
         return np.ones(size, dtype=bool)
     weights = np.exp((row - row.max()) / temperature)
-    order = sorted(range(size), key=lambda i: (-row[i], i))
+    # f32::total_cmp (qwen_forward.rs:498-502): -0.0 sorts below +0.0
+    bits = np.asarray(logits, dtype=np.float32).view(np.uint32).astype(np.int64)
+    total_order = np.where(bits & 0x80000000, 0xFFFFFFFF - bits, bits | 0x80000000)
+    order = sorted(range(size), key=lambda i: (-total_order[i], i))
     if top_k is not None:
         order = order[:top_k]
     kept = sum(weights[i] for i in order)
