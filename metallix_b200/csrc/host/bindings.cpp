@@ -38,6 +38,7 @@ PYBIND11_MODULE(_mxb_host, m) {
       .def("has", &CacheManager::has)
       .def("admit", &CacheManager::admit)
       .def("slot", &CacheManager::slot)
+      .def("epoch", &CacheManager::epoch)
       .def("reserved", &CacheManager::reserved)
       .def("computed", &CacheManager::computed)
       .def("cost", &CacheManager::cost)

@@ -76,6 +76,7 @@ class CacheManager {
     Request r;
     r.slot = free_slots_.back();
     free_slots_.pop_back();
+    r.epoch = ++admissions_;
     r.tables.resize(groups_.size());
     r.first_live.assign(groups_.size(), 0);
     requests_.emplace(id, std::move(r));
@@ -83,6 +84,9 @@ class CacheManager {
   }
 
   int slot(int64_t id) const { return get(id).slot; }
+  // Counts admissions: an id that was released and admitted again has a new
+  // epoch, so whoever mirrors its table knows the mirror is stale.
+  uint64_t epoch(int64_t id) const { return get(id).epoch; }
   int64_t reserved(int64_t id) const { return get(id).reserved; }
   int64_t computed(int64_t id) const { return get(id).computed; }
 
@@ -240,6 +244,7 @@ class CacheManager {
 
   struct Request {
     int slot = -1;
+    uint64_t epoch = 0;
     int64_t reserved = 0;  // positions with a page slot
     int64_t computed = 0;  // positions whose keys and values are written
     std::vector<std::vector<int>> tables;  // [group][logical page]
@@ -272,7 +277,7 @@ class CacheManager {
   std::vector<std::vector<bool>> ever_used_;
   std::vector<int> free_slots_;
   std::unordered_map<int64_t, Request> requests_;
-  uint64_t pages_handed_out_ = 0, pages_reused_ = 0;
+  uint64_t pages_handed_out_ = 0, pages_reused_ = 0, admissions_ = 0;
 };
 
 }  // namespace mxb

@@ -1,0 +1,279 @@
+// Attention of single decoded tokens over the paged cache, split along the
+// keys so that a handful of requests still fills the GPU.
+//
+// One block takes one request's token, one key/value head and one split of
+// kSplitKeys absolute key positions, and serves every query head of that
+// key/value head from a single read of K and V. It writes an unnormalised
+// partial result (running maximum, sum, accumulator) per (token, head,
+// split); a second kernel merges the splits of a head in ascending order.
+// Split boundaries sit at multiples of kSplitKeys of the absolute position
+// and the merge order is fixed, so a token's result does not depend on what
+// else is in the batch. Scores, softmax and accumulators are float32.
+//
+// Replaces the reference's per-step gather of every row's whole context into
+// [rows, kv_heads, longest, head_dim] plus a masked SDPA call
+// (crates/models/qwen/src/forward/paged.rs:189-219, :1067-1076, :1216-1232).
+#include "common.cuh"
+
+namespace mxb {
+
+constexpr int kSplitKeys = 256;
+constexpr int kDecodeThreads = 128;
+constexpr float kDecodeMinusHuge = -1.0e30f;
+
+template <typename T> struct Vec16;  // 16 bytes of T
+template <> struct Vec16<float> {
+  static constexpr int kElems = 4;
+  float4 raw;
+  __device__ __forceinline__ void unpack(float* out) const { out[0] = raw.x; out[1] = raw.y; out[2] = raw.z; out[3] = raw.w; }
+};
+template <> struct Vec16<__nv_bfloat16> {
+  static constexpr int kElems = 8;
+  uint4 raw;
+  __device__ __forceinline__ void unpack(float* out) const {
+    const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      out[2 * i] = __uint_as_float(w[i] << 16);
+      out[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
+    }
+  }
+};
+
+// Partial layout per (token row, head, split): [head_dim] accumulator, then
+// the running maximum and the running sum.
+template <typename T, int HD, int G>
+__global__ void __launch_bounds__(kDecodeThreads)
+paged_attention_decode_kernel(const T* __restrict__ q, const T* __restrict__ cache,
+                              float* __restrict__ partial, const int* __restrict__ block_tables,
+                              int max_pages, const int* __restrict__ row_token,
+                              const int* __restrict__ row_request, const int* __restrict__ positions,
+                              int heads, int kv_heads, int page_tokens, int num_pages, int max_splits,
+                              int window, float scale, int* status) {
+  constexpr int E = Vec16<T>::kElems;  // elements per 16-byte load
+  constexpr int LPK = HD / E;          // lanes that share one key row
+  constexpr int KPW = 32 / LPK;        // key rows a warp loads at once
+  static_assert(HD % E == 0 && 32 % LPK == 0, "head_dim must split into 16-byte pieces over a warp");
+  __shared__ float s_score[G][kSplitKeys];
+  __shared__ float s_stat[G][2];
+  __shared__ float s_acc[kDecodeThreads / LPK][G][HD + 4];
+
+  const int split = blockIdx.x, kv = blockIdx.y, row = blockIdx.z;
+  const int token = row_token[row];
+  if (token < 0) return;  // a padding row
+  const int pos = positions[token];
+  const int group = heads / kv_heads;  // query heads per key/value head, <= G
+  const int first_key = window > 0 ? max(0, pos - window + 1) : 0;
+  const int begin = max(split * kSplitKeys, first_key);
+  const int end = min((split + 1) * kSplitKeys, pos + 1);
+  if (begin >= end) return;  // the merge skips splits outside [first_key, pos]
+  const int count = end - begin;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int* table = block_tables + static_cast<size_t>(row_request[row]) * max_pages;
+  const size_t page_stride = static_cast<size_t>(2) * kv_heads * page_tokens * HD;
+  const size_t v_offset = static_cast<size_t>(kv_heads) * page_tokens * HD;
+  const T* head_base = cache + static_cast<size_t>(kv) * page_tokens * HD;
+
+  // ---- scores: a group of LPK lanes per key row
+  const int sub = lane % LPK, which = lane / LPK;
+  float qreg[G][E];
+#pragma unroll
+  for (int h = 0; h < G; ++h) {
+    if (h < group) {
+      Vec16<T> v;
+      v.raw = *reinterpret_cast<const decltype(v.raw)*>(
+          q + (static_cast<size_t>(token) * heads + kv * group + h) * HD + sub * E);
+      v.unpack(qreg[h]);
+    } else {
+#pragma unroll
+      for (int e = 0; e < E; ++e) qreg[h][e] = 0.0f;
+    }
+  }
+  for (int base = warp * KPW; base < count; base += (kDecodeThreads / 32) * KPW) {
+    const int kk = base + which;
+    float dots[G];
+#pragma unroll
+    for (int h = 0; h < G; ++h) dots[h] = 0.0f;
+    if (kk < count) {
+      const int key = begin + kk;
+      const int page = table[key / page_tokens];
+      if (page < 0 || page >= num_pages) {
+        if (sub == 0) atomicOr(status, kStatusBadPage);
+      } else {
+        Vec16<T> v;
+        v.raw = *reinterpret_cast<const decltype(v.raw)*>(
+            head_base + page * page_stride + static_cast<size_t>(key % page_tokens) * HD + sub * E);
+        float kf[E];
+        v.unpack(kf);
+#pragma unroll
+        for (int h = 0; h < G; ++h)
+#pragma unroll
+          for (int e = 0; e < E; ++e) dots[h] = fmaf(qreg[h][e], kf[e], dots[h]);
+      }
+    }
+#pragma unroll
+    for (int h = 0; h < G; ++h) {
+#pragma unroll
+      for (int offset = LPK / 2; offset > 0; offset >>= 1)
+        dots[h] += __shfl_xor_sync(0xffffffffu, dots[h], offset);
+      if (sub == 0 && kk < count) s_score[h][kk] = dots[h] * scale;
+    }
+  }
+  __syncthreads();
+
+  // ---- softmax statistics of this split, one warp per head
+  for (int h = warp; h < group; h += kDecodeThreads / 32) {
+    float m = kDecodeMinusHuge;
+    for (int kk = lane; kk < count; kk += 32) m = fmaxf(m, s_score[h][kk]);
+    m = warp_max(m);
+    float l = 0.0f;
+    for (int kk = lane; kk < count; kk += 32) {
+      const float p = expf(s_score[h][kk] - m);
+      s_score[h][kk] = p;
+      l += p;
+    }
+    l = warp_sum(l);
+    if (lane == 0) { s_stat[h][0] = m; s_stat[h][1] = l; }
+  }
+  __syncthreads();
+
+  // ---- P V: LPK threads per value row, kDecodeThreads / LPK rows in flight
+  constexpr int ROWS = kDecodeThreads / LPK;
+  const int vsub = tid % LPK, vrow = tid / LPK;
+  float acc[G][E];
+#pragma unroll
+  for (int h = 0; h < G; ++h)
+#pragma unroll
+    for (int e = 0; e < E; ++e) acc[h][e] = 0.0f;
+  for (int kk = vrow; kk < count; kk += ROWS) {
+    const int key = begin + kk;
+    const int page = table[key / page_tokens];
+    if (page < 0 || page >= num_pages) continue;  // already flagged above
+    Vec16<T> v;
+    v.raw = *reinterpret_cast<const decltype(v.raw)*>(
+        head_base + page * page_stride + v_offset + static_cast<size_t>(key % page_tokens) * HD + vsub * E);
+    float vf[E];
+    v.unpack(vf);
+#pragma unroll
+    for (int h = 0; h < G; ++h) {
+      const float p = s_score[h][kk];
+#pragma unroll
+      for (int e = 0; e < E; ++e) acc[h][e] = fmaf(p, vf[e], acc[h][e]);
+    }
+  }
+#pragma unroll
+  for (int h = 0; h < G; ++h)
+#pragma unroll
+    for (int e = 0; e < E; ++e) s_acc[vrow][h][vsub * E + e] = acc[h][e];
+  __syncthreads();
+  // Sum the ROWS partial accumulators in a fixed order and write the partial.
+  for (int i = tid; i < group * HD; i += kDecodeThreads) {
+    const int h = i / HD, d = i - h * HD;
+    float sum = 0.0f;
+#pragma unroll
+    for (int r = 0; r < ROWS; ++r) sum += s_acc[r][h][d];
+    const int head = kv * group + h;
+    float* dst = partial + ((static_cast<size_t>(row) * heads + head) * max_splits + split) * (HD + 2);
+    dst[d] = sum;
+    if (d == 0) { dst[HD] = s_stat[h][0]; dst[HD + 1] = s_stat[h][1]; }
+  }
+}
+
+// out[token, head, :] = sum_s exp(m_s - M) acc_s / sum_s exp(m_s - M) l_s over
+// the splits that hold keys of this token, in ascending order.
+template <typename T>
+__global__ void paged_attention_merge_kernel(const float* __restrict__ partial, T* __restrict__ out,
+                                             const int* __restrict__ row_token,
+                                             const int* __restrict__ positions, int heads, int head_dim,
+                                             int max_splits, int window) {
+  const int row = blockIdx.x, head = blockIdx.y;
+  const int token = row_token[row];
+  if (token < 0) return;
+  const int pos = positions[token];
+  const int first_key = window > 0 ? max(0, pos - window + 1) : 0;
+  const int first_split = first_key / kSplitKeys, last_split = pos / kSplitKeys;
+  const float* base = partial + (static_cast<size_t>(row) * heads + head) * max_splits * (head_dim + 2);
+  float m = kDecodeMinusHuge;
+  for (int s = first_split; s <= last_split; ++s) m = fmaxf(m, base[static_cast<size_t>(s) * (head_dim + 2) + head_dim]);
+  float l = 0.0f;
+  for (int s = first_split; s <= last_split; ++s) {
+    const float* p = base + static_cast<size_t>(s) * (head_dim + 2);
+    l += expf(p[head_dim] - m) * p[head_dim + 1];
+  }
+  const float inv = 1.0f / l;
+  for (int d = threadIdx.x; d < head_dim; d += blockDim.x) {
+    float sum = 0.0f;
+    for (int s = first_split; s <= last_split; ++s) {
+      const float* p = base + static_cast<size_t>(s) * (head_dim + 2);
+      sum += expf(p[head_dim] - m) * p[d];
+    }
+    out[(static_cast<size_t>(token) * heads + head) * head_dim + d] = from_float<T>(sum * inv);
+  }
+}
+
+template <typename T, int HD, int G>
+static int launch_decode(const void* q, const void* cache, void* out, float* partial,
+                         const int* block_tables, int max_pages, const int* row_token,
+                         const int* row_request, const int* positions, int rows, int heads,
+                         int kv_heads, int page_tokens, int num_pages, int max_splits, int window,
+                         float scale, int* status, cudaStream_t stream) {
+  dim3 grid(max_splits, kv_heads, rows);
+  paged_attention_decode_kernel<T, HD, G><<<grid, kDecodeThreads, 0, stream>>>(
+      static_cast<const T*>(q), static_cast<const T*>(cache), partial, block_tables, max_pages,
+      row_token, row_request, positions, heads, kv_heads, page_tokens, num_pages, max_splits, window,
+      scale, status);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return static_cast<int>(e);
+  dim3 merge_grid(rows, heads);
+  paged_attention_merge_kernel<T><<<merge_grid, HD >= 128 ? 128 : 64, 0, stream>>>(
+      partial, static_cast<T*>(out), row_token, positions, heads, HD, max_splits, window);
+  return static_cast<int>(cudaGetLastError());
+}
+
+}  // namespace mxb
+
+using namespace mxb;
+
+// Whether the split kernel takes this shape (else the caller uses the general
+// tile kernel): head_dim 64 or 128 (and 256 in bfloat16), up to 8 query heads
+// per key/value head.
+MXB_API int mxb_paged_attention_decode_supported(int head_dim, int heads, int kv_heads, int dtype) {
+  if (kv_heads <= 0 || heads % kv_heads != 0 || heads / kv_heads > 8) return 0;
+  if (dtype != kF32 && dtype != kBF16) return 0;
+  return head_dim == 64 || head_dim == 128 || (head_dim == 256 && dtype == kBF16) ? 1 : 0;
+}
+
+MXB_API int mxb_paged_attention_split_keys() { return kSplitKeys; }
+
+// partial: float32 scratch of rows * heads * max_splits * (head_dim + 2) values.
+// rows of row_token that are negative are padding. max_splits must cover the
+// longest context: ceil(longest / 256).
+MXB_API int mxb_paged_attention_decode(const void* q, const void* cache, void* out, float* partial,
+                                       const int* block_tables, int max_pages, const int* row_token,
+                                       const int* row_request, const int* positions, int rows,
+                                       int heads, int kv_heads, int head_dim, int page_tokens,
+                                       int num_pages, int max_splits, int window, float scale,
+                                       int dtype, int* status, cudaStream_t stream) {
+  if (rows <= 0) return 0;
+  if (!mxb_paged_attention_decode_supported(head_dim, heads, kv_heads, dtype) || max_splits <= 0)
+    return static_cast<int>(cudaErrorInvalidValue);
+  const int group = heads / kv_heads;
+#define ARGS q, cache, out, partial, block_tables, max_pages, row_token, row_request, positions, rows, \
+             heads, kv_heads, page_tokens, num_pages, max_splits, window, scale, status, stream
+#define BY_GROUP(T, HD)                                        \
+  if (group == 1) return launch_decode<T, HD, 1>(ARGS);        \
+  if (group == 2) return launch_decode<T, HD, 2>(ARGS);        \
+  if (group <= 4) return launch_decode<T, HD, 4>(ARGS);        \
+  return launch_decode<T, HD, 8>(ARGS);
+  if (dtype == kBF16) {
+    if (head_dim == 64) { BY_GROUP(__nv_bfloat16, 64) }
+    if (head_dim == 128) { BY_GROUP(__nv_bfloat16, 128) }
+    if (head_dim == 256) { BY_GROUP(__nv_bfloat16, 256) }
+  } else {
+    if (head_dim == 64) { BY_GROUP(float, 64) }
+    if (head_dim == 128) { BY_GROUP(float, 128) }
+  }
+#undef BY_GROUP
+#undef ARGS
+  return static_cast<int>(cudaErrorInvalidValue);
+}

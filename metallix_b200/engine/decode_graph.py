@@ -1,0 +1,188 @@
+"""Decode steps as CUDA graphs.
+
+A step in which every request brings exactly one token launches the same
+kernels every time; only ids, positions, slots and block tables change. Such a
+step is captured once per batch-size bucket and replayed: one copy of the
+step's integers into the graph's static buffer, one graph launch. The
+reference hides the same launch cost by queueing step t+1 before step t is
+read (crates/models/qwen/src/forward/paged.rs:784-858); here the launches
+themselves go away.
+
+Rows beyond the live requests are padding: id 0, position 0, slot -1 (no cache
+write) and a negative decode row (no attention). Block tables are padded to
+the width of the longest context the engine allows.
+"""
+from __future__ import annotations
+
+from typing import Dict, List, Optional, Sequence
+
+import numpy as np
+import torch
+
+from ..parts.registry import StepContext
+
+BUCKETS = (1, 2, 4, 8, 16, 24, 32, 48, 64, 96, 128, 192, 256)
+
+
+class _Bucket:
+    def __init__(self, size: int):
+        self.size = size
+        self.graph: Optional[torch.cuda.CUDAGraph] = None
+        self.static: Optional[torch.Tensor] = None   # int32 metadata on the device
+        self.logits: Optional[torch.Tensor] = None
+        self.layout: Dict[str, slice] = {}
+        self.kernels = 0                              # our kernel launches inside the graph
+
+
+class DecodeGraphs:
+    def __init__(self, engine):
+        self.engine = engine
+        self.buckets: Dict[int, _Bucket] = {}
+        self.pool = None
+        cache = engine.cache
+        self.table_width = -(-engine.max_context // cache.page_tokens)
+        self._windowed = any(g.need.window for g in cache.groups)
+        self.h2d_bytes = 0
+        # Mirrors of the manager's tables: manager id -> (epoch, pages, per-group rows)
+        self._host_tables: Dict[int, tuple] = {}
+
+    @staticmethod
+    def usable(model) -> bool:
+        """Every mixer must promise to launch the same kernels whatever the
+        step's integers are (no host reads of device values)."""
+        return all(getattr(block.mixer, "graph_safe", False) for block in model.blocks)
+
+    def bucket_for(self, rows: int) -> Optional[int]:
+        for size in BUCKETS:
+            if size >= rows:
+                return size
+        return None
+
+    # ----------------------------------------------------------------- layout
+    def _layout(self, size: int) -> Dict[str, slice]:
+        groups = len(self.engine.cache.groups)
+        names = ["ids", "positions", "token_request", "request_slots", "tile_request", "tile_start",
+                 "tile_length", "wanted", "decode_token", "decode_request"]
+        layout, cursor = {}, 0
+        for name in names:
+            layout[name] = slice(cursor, cursor + size)
+            cursor += size
+        for g in range(groups):
+            layout[f"slots{g}"] = slice(cursor, cursor + size)
+            cursor += size
+            layout[f"table{g}"] = slice(cursor, cursor + size * self.table_width)
+            cursor += size * self.table_width
+        layout["end"] = slice(cursor, cursor)
+        return layout
+
+    def _context(self, bucket: _Bucket) -> StepContext:
+        s, size, engine = bucket.static, bucket.size, self.engine
+        cut = lambda name: s[bucket.layout[name]]
+        return StepContext(
+            device=engine.device, dtype=engine.dtype, num_tokens=size, num_requests=size,
+            positions=cut("positions"), token_request=cut("token_request"),
+            request_slots=cut("request_slots"), request_offsets=list(range(size + 1)),
+            request_positions=[0] * size, tile_request=cut("tile_request"),
+            tile_start=cut("tile_start"), tile_length=cut("tile_length"), multi_tiles=0,
+            decode_token=cut("decode_token"), decode_request=cut("decode_request"),
+            longest_context=engine.max_context)
+
+    def _views(self, bucket: _Bucket):
+        s, size, cache = bucket.static, bucket.size, self.engine.cache
+        tables = {g.index: s[bucket.layout[f"table{g.index}"]].view(size, self.table_width)
+                  for g in cache.groups}
+        slots = {g.index: s[bucket.layout[f"slots{g.index}"]] for g in cache.groups}
+        return lambda entry, write: cache.view(entry, write, tables, slots)
+
+    def _host_fill(self, bucket: _Bucket, rows: Sequence, out: np.ndarray) -> None:
+        """rows: (manager id, token id, position, state slot) of the live
+        requests; fills one step's integers."""
+        size, layout, cache = bucket.size, bucket.layout, self.engine.cache
+        manager, page_tokens = self.engine.manager, cache.page_tokens
+        live = len(rows)
+        index = np.arange(size, dtype=np.int32)
+        out[layout["ids"]] = 0
+        out[layout["positions"]] = 0
+        out[layout["token_request"]] = index
+        out[layout["request_slots"]] = 0
+        out[layout["tile_request"]] = index
+        out[layout["tile_start"]] = index
+        out[layout["tile_length"]] = 0
+        out[layout["tile_length"]][:live] = 1
+        out[layout["wanted"]] = index
+        out[layout["decode_token"]] = -1
+        out[layout["decode_token"]][:live] = index[:live]
+        out[layout["decode_request"]] = index
+        ids, positions, request_slots = (out[layout[k]] for k in ("ids", "positions", "request_slots"))
+        for g in cache.groups:
+            out[layout[f"slots{g.index}"]] = -1
+        for row, (rid, token, position, slot) in enumerate(rows):
+            ids[row], positions[row], request_slots[row] = token, position, slot
+            pages = -(-(position + 1) // page_tokens)
+            epoch = manager.epoch(rid)
+            mirror = self._host_tables.get(rid)
+            if mirror is None or mirror[0] != epoch or mirror[1] < pages or self._windowed:
+                held = []
+                for g in cache.groups:
+                    padded = np.full(self.table_width, -1, dtype=np.int32)
+                    table = manager.table(rid, g.index)
+                    padded[:len(table)] = table
+                    held.append(padded)
+                if len(self._host_tables) > 4 * manager.max_requests():
+                    self._host_tables.clear()   # requests that left long ago
+                self._host_tables[rid] = (epoch, pages, held)
+            else:
+                held = mirror[2]
+            for g in cache.groups:
+                table = out[layout[f"table{g.index}"]]
+                table[row * self.table_width:(row + 1) * self.table_width] = held[g.index]
+                out[layout[f"slots{g.index}"]][row] = \
+                    held[g.index][position // page_tokens] * page_tokens + position % page_tokens
+
+    # ---------------------------------------------------------------- capture
+    def _capture(self, size: int) -> _Bucket:
+        from .. import ops
+        engine = self.engine
+        bucket = _Bucket(size)
+        bucket.layout = self._layout(size)
+        total = bucket.layout["end"].start
+        host = np.zeros(total, dtype=np.int32)
+        self._host_fill(bucket, [], host)   # all padding: nothing is read or written
+        bucket.static = torch.from_numpy(host).to(engine.device)
+        ctx, views = self._context(bucket), self._views(bucket)
+        ids, wanted = bucket.static[bucket.layout["ids"]], bucket.static[bucket.layout["wanted"]]
+        stream = torch.cuda.Stream(device=engine.device)
+        stream.wait_stream(torch.cuda.current_stream(engine.device))
+        with torch.cuda.stream(stream):
+            for _ in range(2):   # libraries and lazily loaded kernels settle before the capture
+                engine.model.forward(ids, ctx, views, wanted)
+        torch.cuda.current_stream(engine.device).wait_stream(stream)
+        torch.cuda.synchronize(engine.device)
+        graph = torch.cuda.CUDAGraph()
+        before = ops.launch_count()
+        with torch.cuda.graph(graph, pool=self.pool):
+            bucket.logits = engine.model.forward(ids, ctx, views, wanted)
+        bucket.kernels = ops.launch_count() - before
+        if self.pool is None:
+            self.pool = graph.pool()
+        bucket.graph = graph
+        return bucket
+
+    # -------------------------------------------------------------------- run
+    def run(self, rows: Sequence) -> torch.Tensor:
+        """rows: (manager id, token id, position, state slot). Returns float32
+        logits [len(rows), vocab]: a view of the graph's output that the next
+        replay of the same bucket overwrites."""
+        from .. import ops
+        size = self.bucket_for(len(rows))
+        bucket = self.buckets.get(size)
+        if bucket is None:
+            bucket = self.buckets[size] = self._capture(size)
+        total = bucket.layout["end"].start
+        packed = torch.empty(total, dtype=torch.int32, pin_memory=True)
+        self._host_fill(bucket, rows, packed.numpy())
+        bucket.static.copy_(packed, non_blocking=True)
+        bucket.graph.replay()
+        ops.count_launches(bucket.kernels)
+        self.h2d_bytes = total * 4
+        return bucket.logits[:len(rows)]

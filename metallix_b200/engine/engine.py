@@ -62,7 +62,7 @@ class Engine:
                  page_tokens: int = 16, num_pages: Optional[int] = None,
                  max_tokens: Optional[int] = None, max_requests: int = 64,
                  max_context: Optional[int] = None, device="cuda:0", gemm_backend: str = "auto",
-                 spec=None):
+                 spec=None, cuda_graphs: bool = True):
         ops.require_cuda()
         self.config = config
         self.device = torch.device(device)
@@ -83,6 +83,8 @@ class Engine:
         self.cache = PagedCache(self.model.cache_needs(), page_tokens, num_pages, max_requests,
                                 self.dtype, self.device)
         self.manager = self.cache.manager
+        from .decode_graph import DecodeGraphs
+        self.graphs = DecodeGraphs(self) if cuda_graphs and DecodeGraphs.usable(self.model) else None
         self._ids: Dict[Hashable, int] = {}   # request name -> manager id
         self._next_id = 1 << 40               # above any id a scheduler hands out
         self.steps = 0
@@ -133,7 +135,9 @@ class Engine:
     def step(self, entries: Sequence[StepEntry]) -> Optional[torch.Tensor]:
         """Runs one batch. Returns float32 logits ``[wanted, vocab]`` on the
         device in the order of the entries and of each entry's ``want``, or
-        None if nothing is wanted. Call ``check()`` after reading results."""
+        None if nothing is wanted. The tensor may be a view of a buffer that
+        the next step overwrites: read it before stepping again. Call
+        ``check()`` after reading results."""
         entries = [e if isinstance(e, StepEntry) else StepEntry(**e) for e in entries]
         self._validate(entries)
         manager, fresh = self.manager, []
@@ -148,7 +152,7 @@ class Engine:
                 if manager.computed(rid) == 0:
                     self.cache.zero_state(manager.slot(rid))  # a sequence starts from zero state
                 manager.reserve(rid, len(entry.tokens))
-            logits = self._run(entries)
+            logits = self._run_graph(entries) if self._all_decode(entries) else self._run(entries)
             for entry in entries:
                 manager.commit(self._rid(entry), len(entry.tokens))
         except BaseException:
@@ -163,6 +167,28 @@ class Engine:
             raise
         self.steps += 1
         return logits
+
+    def _all_decode(self, entries: List[StepEntry]) -> bool:
+        """Every request brings one token after earlier ones: a decode step,
+        which runs as a captured graph."""
+        if self.graphs is None or self.graphs.bucket_for(len(entries)) is None:
+            return False
+        return all(len(e.tokens) == 1 and self.manager.computed(self._rid(e)) > 0 for e in entries)
+
+    def _run_graph(self, entries: List[StepEntry]) -> Optional[torch.Tensor]:
+        manager = self.manager
+        rows, wanted = [], []
+        for row, entry in enumerate(entries):
+            rid = self._rid(entry)
+            rows.append((rid, int(entry.tokens[0]), manager.computed(rid), manager.slot(rid)))
+            if len(entry.want):
+                wanted.append(row)
+        logits = self.graphs.run(rows)
+        if not wanted:
+            return None
+        if len(wanted) == len(entries):
+            return logits
+        return logits[torch.tensor(wanted, device=self.device)]
 
     def check(self) -> None:
         """Raises if any kernel since the last check refused its input
@@ -224,6 +250,7 @@ class Engine:
         request_slots = np.empty(rows, dtype=np.int32)
         starts, wanted = [], []
         tile_request, tile_start, tile_length = [], [], []
+        single_tiles, decode_token, decode_request, longest = [], [], [], 0
         group_tables = [[] for _ in cache.groups]
         for row, entry in enumerate(entries):
             rid = self._rid(entry)
@@ -235,17 +262,29 @@ class Engine:
             token_request[begin:begin + count] = row
             request_slots[row] = manager.slot(rid)
             wanted.extend(begin + index for index in entry.want)
-            for first in range(0, count, ATTENTION_TILE):
-                tile_request.append(row)
-                tile_start.append(begin + first)
-                tile_length.append(min(ATTENTION_TILE, count - first))
+            if count == 1:
+                single_tiles.append((row, begin, 1))
+                decode_token.append(begin)
+                decode_request.append(row)
+                longest = max(longest, start + 1)
+            else:
+                for first in range(0, count, ATTENTION_TILE):
+                    tile_request.append(row)
+                    tile_start.append(begin + first)
+                    tile_length.append(min(ATTENTION_TILE, count - first))
             for group in cache.groups:
                 group_tables[group.index].append(manager.table(rid, group.index))
 
+        multi_tiles = len(tile_request)
+        for row, begin, count in single_tiles:  # tiles of multi-token requests first
+            tile_request.append(row)
+            tile_start.append(begin)
+            tile_length.append(count)
         # One packed int32 buffer, one copy to the device.
         pieces = [token_ids, positions, token_request, request_slots,
                   np.asarray(tile_request, dtype=np.int32), np.asarray(tile_start, dtype=np.int32),
-                  np.asarray(tile_length, dtype=np.int32), np.asarray(wanted, dtype=np.int32)]
+                  np.asarray(tile_length, dtype=np.int32), np.asarray(wanted, dtype=np.int32),
+                  np.asarray(decode_token, dtype=np.int32), np.asarray(decode_request, dtype=np.int32)]
         shapes = [None] * len(pieces)
         for group in cache.groups:
             tables = group_tables[group.index]
@@ -273,15 +312,17 @@ class Engine:
             views.append(view.view(shape) if shape is not None else view)
             cursor += size
         (d_ids, d_positions, d_token_request, d_request_slots, d_tile_request, d_tile_start,
-         d_tile_length, d_wanted) = views[:8]
-        tables = {g.index: views[8 + 2 * g.index] for g in cache.groups}
-        slots = {g.index: views[9 + 2 * g.index] for g in cache.groups}
+         d_tile_length, d_wanted, d_decode_token, d_decode_request) = views[:10]
+        tables = {g.index: views[10 + 2 * g.index] for g in cache.groups}
+        slots = {g.index: views[11 + 2 * g.index] for g in cache.groups}
 
         ctx = StepContext(
             device=self.device, dtype=self.dtype, num_tokens=total, num_requests=rows,
             positions=d_positions, token_request=d_token_request, request_slots=d_request_slots,
             request_offsets=[int(v) for v in offsets], request_positions=starts,
-            tile_request=d_tile_request, tile_start=d_tile_start, tile_length=d_tile_length)
+            tile_request=d_tile_request, tile_start=d_tile_start, tile_length=d_tile_length,
+            multi_tiles=multi_tiles, decode_token=d_decode_token if decode_token else None,
+            decode_request=d_decode_request if decode_token else None, longest_context=longest)
         self._keep = packed  # the pinned buffer must outlive the asynchronous copy
         return self.model.forward(
             d_ids, ctx, lambda entry, write: cache.view(entry, write, tables, slots),

@@ -35,6 +35,10 @@ _SIGNATURES = {
                                _I, _I, _I, _I, _I, _I, _I, _I, _F, _I, _P, _P],
     "mxb_paged_attention_tile": [_P, _P, _P, _P, _I, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I,
                                  _F, _I, _P, _P],
+    "mxb_paged_attention_decode": [_P, _P, _P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I,
+                                   _F, _I, _P, _P],
+    "mxb_paged_attention_decode_supported": [_I, _I, _I, _I],
+    "mxb_paged_attention_split_keys": [],
     "mxb_gemm_simple": [_P, _I, _P, _P, _I, _I, _I, _I, _L, _L, _L, _P],
     "mxb_silu_mul": [_P, _P, _I, _L, _I, _P],
     "mxb_argmax": [_P, _L, _I, _I, _P, _P, _P],
@@ -60,7 +64,23 @@ def _fn(name: str):
     return fn
 
 
+_launches = 0
+
+
+def launch_count() -> int:
+    """How many of this library's kernel entry points have been called
+    (a replayed CUDA graph counts the calls it captured)."""
+    return _launches
+
+
+def count_launches(count: int) -> None:
+    global _launches
+    _launches += count
+
+
 def _call(name: str, *args) -> None:
+    global _launches
+    _launches += 1
     code = _fn(name)(*args)
     if code != 0:
         raise KernelError(f"{name} failed to launch: CUDA error {code}")
@@ -281,6 +301,56 @@ def paged_attention_tile(q: torch.Tensor, cache: torch.Tensor, out: torch.Tensor
           tile_start.data_ptr(), tile_length.data_ptr(), positions.data_ptr(), tiles, heads,
           kv_heads, head_dim, page_tokens, num_pages, int(window or 0), float(scale), _CODES[dtype],
           status_word(q.device).data_ptr(), _stream())
+    return out
+
+
+def decode_attention_supported(head_dim: int, heads: int, kv_heads: int, dtype: torch.dtype) -> bool:
+    """Whether the split-key decode kernel takes this head layout."""
+    if dtype not in _CODES:
+        return False
+    return bool(_fn("mxb_paged_attention_decode_supported")(head_dim, heads, kv_heads, _CODES[dtype]))
+
+
+def decode_split_keys() -> int:
+    return _fn("mxb_paged_attention_split_keys")()
+
+
+def paged_attention_decode(q: torch.Tensor, cache: torch.Tensor, out: torch.Tensor,
+                           block_tables: torch.Tensor, row_token: torch.Tensor,
+                           row_request: torch.Tensor, positions: torch.Tensor, scale: float,
+                           longest_context: int, window: int = 0,
+                           partial: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Attention of single tokens over their requests' cached keys, split
+    along the keys. ``row_token[i]`` is the token (row of q and out) of the
+    i-th decoded request, negative for a padding row; ``row_request[i]`` its
+    row of ``block_tables``. ``longest_context`` bounds positions + 1 and
+    fixes the number of splits. ``partial`` is float32 scratch of
+    rows * heads * splits * (head_dim + 2) values, allocated here if absent."""
+    dtype = q.dtype
+    _check(q, "q", tuple(_CODES), 3)
+    _check(out, "out", (dtype,), 3)
+    _check(cache, "cache", (dtype,), 5)
+    _need(out.shape == q.shape, "out and q differ in shape")
+    tokens, heads, head_dim = q.shape
+    num_pages, two, kv_heads, page_tokens, cache_dim = cache.shape
+    _need(two == 2 and cache_dim == head_dim, "cache must be [pages, 2, kv_heads, page_tokens, head_dim]")
+    _need(decode_attention_supported(head_dim, heads, kv_heads, dtype),
+          f"the split-key decode kernel does not take head_dim {head_dim} with {heads}/{kv_heads} heads in {dtype}")
+    _check(block_tables, "block_tables", (torch.int32,), 2)
+    for name, tensor in (("row_token", row_token), ("row_request", row_request), ("positions", positions)):
+        _check(tensor, name, (torch.int32,), 1)
+    rows = row_token.numel()
+    _need(row_request.numel() == rows and positions.numel() == tokens, "row lists do not fit")
+    splits = max(1, -(-int(longest_context) // decode_split_keys()))
+    need = rows * heads * splits * (head_dim + 2)
+    if partial is None:
+        partial = torch.empty(need, dtype=torch.float32, device=q.device)
+    _check(partial, "partial", (torch.float32,))
+    _need(partial.numel() >= need, f"partial holds {partial.numel()} values, {need} are needed")
+    _call("mxb_paged_attention_decode", q.data_ptr(), cache.data_ptr(), out.data_ptr(), partial.data_ptr(),
+          block_tables.data_ptr(), block_tables.shape[1], row_token.data_ptr(), row_request.data_ptr(),
+          positions.data_ptr(), rows, heads, kv_heads, head_dim, page_tokens, num_pages, splits,
+          int(window or 0), float(scale), _CODES[dtype], status_word(q.device).data_ptr(), _stream())
     return out
 
 

@@ -26,6 +26,7 @@ from .registry import CacheView, Runtime, StepContext, WeightStore, build_part, 
 
 class GQAttention:
     kind = "gqa_attention"
+    graph_safe = True  # launches the same kernels whatever the step's integers are
 
     def __init__(self, spec: PartSpec, weights: WeightStore, runtime: Runtime):
         self.hidden_size = spec["hidden_size"]
@@ -57,6 +58,8 @@ class GQAttention:
         position_fuses = self.position is None or getattr(self.position, "fused_tables", False)
         self.fused = norms_fuse and eps_agree and position_fuses
         self.dtype = runtime.dtype
+        self.split_decode = ops.decode_attention_supported(self.head_dim, self.num_heads,
+                                                           self.num_kv_heads, self.dtype)
 
     def cache_need(self) -> CacheNeed:
         return CacheNeed(kind="kv_pages", kv_heads=self.num_kv_heads, head_dim=self.head_dim,
@@ -95,8 +98,22 @@ class GQAttention:
             if write:
                 ops.write_cache(k, v, cache.pool, cache.slots, ctx.positions)
         out = torch.empty_like(q_heads)
-        ops.paged_attention_tile(q_heads, cache.pool, out, cache.block_tables, ctx.tile_request,
-                                 ctx.tile_start, ctx.tile_length, ctx.positions, self.scale, self.window)
+        decode_rows = 0 if ctx.decode_token is None else ctx.decode_token.numel()
+        if decode_rows and self.split_decode:
+            # Requests that bring one token: split along the keys. The others
+            # (tiles listed first) go through the general kernel.
+            if ctx.multi_tiles:
+                ops.paged_attention_tile(q_heads, cache.pool, out, cache.block_tables,
+                                         ctx.tile_request[:ctx.multi_tiles], ctx.tile_start[:ctx.multi_tiles],
+                                         ctx.tile_length[:ctx.multi_tiles], ctx.positions, self.scale,
+                                         self.window)
+            ops.paged_attention_decode(q_heads, cache.pool, out, cache.block_tables, ctx.decode_token,
+                                       ctx.decode_request, ctx.positions, self.scale,
+                                       ctx.longest_context, self.window)
+        else:
+            ops.paged_attention_tile(q_heads, cache.pool, out, cache.block_tables, ctx.tile_request,
+                                     ctx.tile_start, ctx.tile_length, ctx.positions, self.scale,
+                                     self.window)
         return self.o.forward(out.view(tokens, self.q_size))
 
     def weight_bytes(self) -> int:

@@ -108,7 +108,15 @@ class StepContext:
     request_slots: torch.Tensor        # int32 [requests], state slot of each request row
     request_offsets: List[int]         # host, [requests + 1]
     request_positions: List[int]       # host, first position of each row's tokens
-    tile_request: torch.Tensor         # int32 [tiles], attention query tiles
+    tile_request: torch.Tensor         # int32 [tiles], attention query tiles of every request
     tile_start: torch.Tensor
     tile_length: torch.Tensor
+    # The same batch split by kind of request, for mixers with a kernel of
+    # their own for single decoded tokens: tiles of the requests that bring
+    # several tokens, and (token, request row) of those that bring one.
+    # ``decode_token`` may hold negative entries (padding rows).
+    multi_tiles: int = 0               # the first ``multi_tiles`` tiles belong to multi-token requests
+    decode_token: Optional[torch.Tensor] = None    # int32 [decode rows]
+    decode_request: Optional[torch.Tensor] = None  # int32 [decode rows]
+    longest_context: int = 0           # upper bound of position + 1 over the decode rows
     extras: Dict[str, object] = field(default_factory=dict)

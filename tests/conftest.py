@@ -28,7 +28,13 @@ TINY_C = dict(architectures=["Qwen3ForCausalLM"], model_type="qwen3", hidden_act
               num_hidden_layers=4, hidden_size=80, num_attention_heads=3, num_key_value_heads=1,
               head_dim=48, intermediate_size=136, vocab_size=331, rope_theta=50000.0,
               rms_norm_eps=3e-6, tie_word_embeddings=False, max_position_embeddings=1024)
-TINY = {"A": (TINY_A, 0, 4), "B": (TINY_B, 1, 8), "C": (TINY_C, 2, 16)}  # config, seed, page size
+# Tiny D: head_dim 64 with three query heads per key/value head: the head
+# layout the split-key decode kernel takes.
+TINY_D = dict(architectures=["Qwen3ForCausalLM"], model_type="qwen3", hidden_act="silu",
+              num_hidden_layers=2, hidden_size=128, num_attention_heads=6, num_key_value_heads=2,
+              head_dim=64, intermediate_size=192, vocab_size=500, rope_theta=100000.0,
+              rms_norm_eps=1e-6, tie_word_embeddings=True, max_position_embeddings=768)
+TINY = {"A": (TINY_A, 0, 4), "B": (TINY_B, 1, 8), "C": (TINY_C, 2, 16), "D": (TINY_D, 3, 16)}  # config, seed, page size
 
 # Stated tolerances on logits (tiny models: |logit| stays below about 2).
 # float32: the engine against the float64 plain implementation; measured

@@ -276,6 +276,103 @@ def test_attention_does_not_depend_on_the_cut(ops):
     assert np.array_equal(part[37:], whole[total - 12:total - 9])
 
 
+def run_decode_attention(ops, dtype, q, k, v, totals, page_tokens, scale, window=0, pad_rows=0, seed=0):
+    """One query (the last position) per request through the split-key kernel."""
+    heads, head_dim, kv_heads = q[0].shape[1], q[0].shape[2], k[0].shape[1]
+    rng = np.random.default_rng(seed)
+    pages_needed = [-(-total // page_tokens) for total in totals]
+    order = rng.permutation(sum(pages_needed) + 2)
+    host_cache = np.zeros((len(order), 2, kv_heads, page_tokens, head_dim))
+    tables = np.full((len(totals), max(pages_needed)), -1, dtype=np.int32)
+    cursor = 0
+    for r, total in enumerate(totals):
+        tables[r, :pages_needed[r]] = order[cursor:cursor + pages_needed[r]]
+        cursor += pages_needed[r]
+        for p in range(total):
+            host_cache[tables[r, p // page_tokens], 0, :, p % page_tokens] = k[r][p]
+            host_cache[tables[r, p // page_tokens], 1, :, p % page_tokens] = v[r][p]
+    q_all = dev(np.stack([q[r][total - 1] for r, total in enumerate(totals)]), dtype)
+    out = torch.full_like(q_all, float("nan"))
+    rows = list(range(len(totals))) + [-1] * pad_rows
+    ops.paged_attention_decode(q_all, dev(host_cache, dtype), out, dev(tables, torch.int32),
+                               dev(rows, torch.int32), dev([max(r, 0) for r in rows], torch.int32),
+                               dev([t - 1 for t in totals], torch.int32), scale, max(totals) + 300, window)
+    ops.check_status("cuda")
+    return out.cpu().double().numpy()
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("heads, kv_heads, head_dim, page_tokens", [(2, 2, 64, 16), (6, 2, 64, 8),
+                                                                   (4, 2, 128, 16), (8, 1, 128, 32),
+                                                                   (5, 1, 128, 4)])
+def test_split_key_decode_attention(ops, dtype, heads, kv_heads, head_dim, page_tokens):
+    rng = np.random.default_rng(heads + head_dim)
+    totals = [1, 255, 256, 257, 700, 33, 512, 1030]
+    q = [rounded(rng.normal(size=(n, heads, head_dim)), dtype) for n in totals]
+    k = [rounded(rng.normal(size=(n, kv_heads, head_dim)), dtype) for n in totals]
+    v = [rounded(rng.normal(size=(n, kv_heads, head_dim)), dtype) for n in totals]
+    scale = head_dim ** -0.5
+    assert ops.decode_attention_supported(head_dim, heads, kv_heads, dtype)
+    out = run_decode_attention(ops, dtype, q, k, v, totals, page_tokens, scale, pad_rows=3)
+    for r, total in enumerate(totals):
+        ref = plain.causal_gqa_attention(q[r], k[r], v[r], scale)[-1]
+        assert np.abs(out[r] - ref).max() < tol(dtype, 5e-6, 2e-2), (r, total)
+    for window in (1, 100, 256, 300):
+        out = run_decode_attention(ops, dtype, q, k, v, totals, page_tokens, scale, window=window)
+        for r, total in enumerate(totals):
+            ref = plain.causal_gqa_attention(q[r], k[r], v[r], scale, window=window)[-1]
+            assert np.abs(out[r] - ref).max() < tol(dtype, 5e-6, 2e-2), (window, r, total)
+
+
+def test_split_key_decode_bfloat16_head_dim_256_and_refusals(ops):
+    rng = np.random.default_rng(21)
+    totals = [300, 17]
+    q = [rounded(rng.normal(size=(n, 2, 256)), torch.bfloat16) for n in totals]
+    k = [rounded(rng.normal(size=(n, 1, 256)), torch.bfloat16) for n in totals]
+    v = [rounded(rng.normal(size=(n, 1, 256)), torch.bfloat16) for n in totals]
+    out = run_decode_attention(ops, torch.bfloat16, q, k, v, totals, 16, 1 / 16)
+    for r in range(2):
+        assert np.abs(out[r] - plain.causal_gqa_attention(q[r], k[r], v[r], 1 / 16)[-1]).max() < 2e-2
+    assert not ops.decode_attention_supported(48, 3, 1, torch.bfloat16)    # the caller takes the general kernel
+    assert not ops.decode_attention_supported(256, 2, 1, torch.float32)
+    assert not ops.decode_attention_supported(128, 16, 1, torch.bfloat16)  # 16 query heads per key/value head
+    with pytest.raises(ops.KernelError, match="does not take"):
+        ops.paged_attention_decode(torch.zeros(1, 3, 48, device="cuda"), torch.zeros(2, 2, 1, 4, 48, device="cuda"),
+                                   torch.zeros(1, 3, 48, device="cuda"),
+                                   torch.zeros(1, 1, dtype=torch.int32, device="cuda"),
+                                   torch.zeros(1, dtype=torch.int32, device="cuda"),
+                                   torch.zeros(1, dtype=torch.int32, device="cuda"),
+                                   torch.zeros(1, dtype=torch.int32, device="cuda"), 1.0, 4)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_split_key_decode_one_far_key(ops, dtype):
+    heads, kv_heads, head_dim, total = 4, 2, 128, 1500
+    rng = np.random.default_rng(22)
+    for target in (0, 15, 16, 255, 256, 257, 1023, 1024, 1279, 1280, 1498, 1499):
+        k = rounded(rng.normal(size=(total, kv_heads, head_dim)) * 0.1, dtype)
+        v = rounded(rng.normal(size=(total, kv_heads, head_dim)), dtype)
+        q = rounded(rng.normal(size=(total, heads, head_dim)) * 0.1, dtype)
+        k[target, :, :] = 0.0
+        k[target, :, 9] = 16.0
+        q[-1, :, 9] = 16.0
+        out = run_decode_attention(ops, dtype, [q], [k], [v], [total], 16, head_dim ** -0.5, seed=target)
+        for head in range(heads):
+            assert np.abs(out[0, head] - v[target, head // 2]).max() < tol(dtype, 1e-5, 1e-2), (target, head)
+
+
+def test_split_key_decode_does_not_depend_on_the_batch(ops):
+    rng = np.random.default_rng(23)
+    totals = [900, 40, 300]
+    q = [rng.normal(size=(n, 4, 64)) for n in totals]
+    k = [rng.normal(size=(n, 2, 64)) for n in totals]
+    v = [rng.normal(size=(n, 2, 64)) for n in totals]
+    together = run_decode_attention(ops, torch.float32, q, k, v, totals, 16, 0.125, pad_rows=5)
+    for r in range(3):
+        alone = run_decode_attention(ops, torch.float32, [q[r]], [k[r]], [v[r]], [totals[r]], 16, 0.125, seed=r + 1)
+        assert np.array_equal(alone[0], together[r])
+
+
 def test_attention_flags_a_bad_page(ops):
     q = torch.zeros(1, 1, 16, device="cuda")
     cache = torch.zeros(2, 2, 1, 4, 16, device="cuda")

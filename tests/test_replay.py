@@ -17,7 +17,8 @@ from conftest import (ROOT, TOL_BF16_VS_EXACT, TOL_BF16_VS_ROUNDED, TOL_CUTS_BF1
 
 pytestmark = pytest.mark.gpu
 
-LENGTHS = {"A": [5, 17, 31, 70, 100], "B": [1, 9, 40, 63, 130, 97], "C": [3, 50, 200, 33]}
+LENGTHS = {"A": [5, 17, 31, 70, 100], "B": [1, 9, 40, 63, 130, 97], "C": [3, 50, 200, 33],
+           "D": [300, 2, 64, 540, 257]}
 
 
 @pytest.fixture(scope="module")
@@ -46,7 +47,7 @@ def bounds(dtype):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["A", "B", "C"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "D"])
 def test_every_cut_matches_the_plain_implementation(model_folders, references, name, dtype):
     from metallix_b200.engine import StepEntry
     requests, exact, rounded = references[name]
@@ -67,7 +68,7 @@ def test_every_cut_matches_the_plain_implementation(model_folders, references, n
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["A", "B", "C"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "D"])
 def test_mixed_batches_with_pages_used_again(model_folders, references, name, dtype):
     from metallix_b200.engine import StepEntry
     requests, exact, _ = references[name]
@@ -90,14 +91,15 @@ def test_mixed_batches_with_pages_used_again(model_folders, references, name, dt
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-def test_long_decoding(model_folders, dtype):
-    """600 tokens one by one after a short prompt (configuration C allows 1024
-    positions), every tenth compared."""
+@pytest.mark.parametrize("name", ["C", "D"])
+def test_long_decoding(model_folders, name, dtype):
+    """600 tokens one by one after a short prompt (configurations C and D allow
+    that many positions), every tenth compared."""
     from metallix_b200.engine import StepEntry
-    folder, config, tensors, page = model_folders["C"]
+    folder, config, tensors, page = model_folders[name]
     ids = random_ids(77, 640, config["vocab_size"])
     reference = plain.forward_logits(config, tensors, ids)
-    engine = make_engine(model_folders, "C", dtype)
+    engine = make_engine(model_folders, name, dtype)
     limit, _ = bounds(dtype)
     logits = engine.step([StepEntry("long", ids[:40], [39])])
     assert np.abs(logits.cpu().double().numpy()[0] - reference[39]).max() < limit
