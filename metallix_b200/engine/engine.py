@@ -30,7 +30,8 @@ from .model import DecoderModel
 
 _DTYPES = {"bfloat16": torch.bfloat16, "bf16": torch.bfloat16, "float32": torch.float32,
            "fp32": torch.float32, torch.bfloat16: torch.bfloat16, torch.float32: torch.float32}
-ATTENTION_TILE = 16  # query tokens per attention tile (csrc/kernels/attention_tile.cu)
+ATTENTION_TILE = 16  # query tokens per tile of the general kernel (csrc/kernels/attention_tile.cu)
+WIDE_TILE = 64       # and of the tensor-core prompt kernel (csrc/kernels/attention_prefill.cu)
 
 
 class StepError(ValueError):
@@ -251,6 +252,7 @@ class Engine:
         starts, wanted = [], []
         tile_request, tile_start, tile_length = [], [], []
         single_tiles, decode_token, decode_request, longest = [], [], [], 0
+        wide = []   # (keys to walk, row, first token, count) of 64-token tiles
         group_tables = [[] for _ in cache.groups]
         for row, entry in enumerate(entries):
             rid = self._rid(entry)
@@ -272,10 +274,14 @@ class Engine:
                     tile_request.append(row)
                     tile_start.append(begin + first)
                     tile_length.append(min(ATTENTION_TILE, count - first))
+                for first in range(0, count, WIDE_TILE):
+                    size = min(WIDE_TILE, count - first)
+                    wide.append((start + first + size, row, begin + first, size))
             for group in cache.groups:
                 group_tables[group.index].append(manager.table(rid, group.index))
 
         multi_tiles = len(tile_request)
+        wide.sort(key=lambda item: -item[0])   # the tiles with most keys start first
         for row, begin, count in single_tiles:  # tiles of multi-token requests first
             tile_request.append(row)
             tile_start.append(begin)
@@ -284,7 +290,10 @@ class Engine:
         pieces = [token_ids, positions, token_request, request_slots,
                   np.asarray(tile_request, dtype=np.int32), np.asarray(tile_start, dtype=np.int32),
                   np.asarray(tile_length, dtype=np.int32), np.asarray(wanted, dtype=np.int32),
-                  np.asarray(decode_token, dtype=np.int32), np.asarray(decode_request, dtype=np.int32)]
+                  np.asarray(decode_token, dtype=np.int32), np.asarray(decode_request, dtype=np.int32),
+                  np.asarray([w[1] for w in wide], dtype=np.int32),
+                  np.asarray([w[2] for w in wide], dtype=np.int32),
+                  np.asarray([w[3] for w in wide], dtype=np.int32)]
         shapes = [None] * len(pieces)
         for group in cache.groups:
             tables = group_tables[group.index]
@@ -312,9 +321,10 @@ class Engine:
             views.append(view.view(shape) if shape is not None else view)
             cursor += size
         (d_ids, d_positions, d_token_request, d_request_slots, d_tile_request, d_tile_start,
-         d_tile_length, d_wanted, d_decode_token, d_decode_request) = views[:10]
-        tables = {g.index: views[10 + 2 * g.index] for g in cache.groups}
-        slots = {g.index: views[11 + 2 * g.index] for g in cache.groups}
+         d_tile_length, d_wanted, d_decode_token, d_decode_request, d_wide_request, d_wide_start,
+         d_wide_length) = views[:13]
+        tables = {g.index: views[13 + 2 * g.index] for g in cache.groups}
+        slots = {g.index: views[14 + 2 * g.index] for g in cache.groups}
 
         ctx = StepContext(
             device=self.device, dtype=self.dtype, num_tokens=total, num_requests=rows,
@@ -322,7 +332,9 @@ class Engine:
             request_offsets=[int(v) for v in offsets], request_positions=starts,
             tile_request=d_tile_request, tile_start=d_tile_start, tile_length=d_tile_length,
             multi_tiles=multi_tiles, decode_token=d_decode_token if decode_token else None,
-            decode_request=d_decode_request if decode_token else None, longest_context=longest)
+            decode_request=d_decode_request if decode_token else None, longest_context=longest,
+            wide_tile_request=d_wide_request, wide_tile_start=d_wide_start,
+            wide_tile_length=d_wide_length)
         self._keep = packed  # the pinned buffer must outlive the asynchronous copy
         return self.model.forward(
             d_ids, ctx, lambda entry, write: cache.view(entry, write, tables, slots),

@@ -39,6 +39,9 @@ _SIGNATURES = {
                                    _F, _I, _P, _P],
     "mxb_paged_attention_decode_supported": [_I, _I, _I, _I],
     "mxb_paged_attention_split_keys": [],
+    "mxb_flash_prefill": [_P, _P, _P, _P, _I, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _F, _I, _P, _P],
+    "mxb_flash_prefill_supported": [_I, _I, _I, _I],
+    "mxb_flash_prefill_tile": [],
     "mxb_gemm_simple": [_P, _I, _P, _P, _I, _I, _I, _I, _L, _L, _L, _P],
     "mxb_silu_mul": [_P, _P, _I, _L, _I, _P],
     "mxb_argmax": [_P, _L, _I, _I, _P, _P, _P],
@@ -301,6 +304,47 @@ def paged_attention_tile(q: torch.Tensor, cache: torch.Tensor, out: torch.Tensor
           tile_start.data_ptr(), tile_length.data_ptr(), positions.data_ptr(), tiles, heads,
           kv_heads, head_dim, page_tokens, num_pages, int(window or 0), float(scale), _CODES[dtype],
           status_word(q.device).data_ptr(), _stream())
+    return out
+
+
+def flash_prefill_supported(head_dim: int, heads: int, kv_heads: int, dtype: torch.dtype) -> bool:
+    """Whether the tensor-core prompt kernel takes this head layout."""
+    if dtype not in _CODES:
+        return False
+    return bool(_fn("mxb_flash_prefill_supported")(head_dim, heads, kv_heads, _CODES[dtype]))
+
+
+def flash_prefill_tile() -> int:
+    """Query tokens per tile of the tensor-core prompt kernel."""
+    return _fn("mxb_flash_prefill_tile")()
+
+
+def flash_prefill(q: torch.Tensor, cache: torch.Tensor, out: torch.Tensor, block_tables: torch.Tensor,
+                  tile_request: torch.Tensor, tile_start: torch.Tensor, tile_length: torch.Tensor,
+                  positions: torch.Tensor, scale: float, window: int = 0) -> torch.Tensor:
+    """Causal attention of prompt portions on the tensor cores (bfloat16,
+    float32 softmax and accumulation); tiles hold up to 64 consecutive tokens
+    of one request."""
+    _check(q, "q", (torch.bfloat16,), 3)
+    _check(out, "out", (torch.bfloat16,), 3)
+    _check(cache, "cache", (torch.bfloat16,), 5)
+    _need(out.shape == q.shape, "out and q differ in shape")
+    tokens, heads, head_dim = q.shape
+    num_pages, two, kv_heads, page_tokens, cache_dim = cache.shape
+    _need(two == 2 and cache_dim == head_dim, "cache must be [pages, 2, kv_heads, page_tokens, head_dim]")
+    _need(flash_prefill_supported(head_dim, heads, kv_heads, q.dtype),
+          f"the tensor-core prompt kernel does not take head_dim {head_dim} with {heads}/{kv_heads} heads")
+    _check(block_tables, "block_tables", (torch.int32,), 2)
+    for name, tensor in (("tile_request", tile_request), ("tile_start", tile_start),
+                         ("tile_length", tile_length), ("positions", positions)):
+        _check(tensor, name, (torch.int32,), 1)
+    tiles = tile_request.numel()
+    _need(tile_start.numel() == tiles and tile_length.numel() == tiles, "tile lists differ in length")
+    _need(positions.numel() == tokens, "one position per token")
+    _call("mxb_flash_prefill", q.data_ptr(), cache.data_ptr(), out.data_ptr(), block_tables.data_ptr(),
+          block_tables.shape[1], tile_request.data_ptr(), tile_start.data_ptr(), tile_length.data_ptr(),
+          positions.data_ptr(), tiles, heads, kv_heads, head_dim, page_tokens, num_pages,
+          int(window or 0), float(scale), _CODES[q.dtype], status_word(q.device).data_ptr(), _stream())
     return out
 
 

@@ -60,6 +60,8 @@ class GQAttention:
         self.dtype = runtime.dtype
         self.split_decode = ops.decode_attention_supported(self.head_dim, self.num_heads,
                                                            self.num_kv_heads, self.dtype)
+        self.flash = ops.flash_prefill_supported(self.head_dim, self.num_heads, self.num_kv_heads,
+                                                 self.dtype)
 
     def cache_need(self) -> CacheNeed:
         return CacheNeed(kind="kv_pages", kv_heads=self.num_kv_heads, head_dim=self.head_dim,
@@ -99,21 +101,25 @@ class GQAttention:
                 ops.write_cache(k, v, cache.pool, cache.slots, ctx.positions)
         out = torch.empty_like(q_heads)
         decode_rows = 0 if ctx.decode_token is None else ctx.decode_token.numel()
-        if decode_rows and self.split_decode:
-            # Requests that bring one token: split along the keys. The others
-            # (tiles listed first) go through the general kernel.
-            if ctx.multi_tiles:
-                ops.paged_attention_tile(q_heads, cache.pool, out, cache.block_tables,
-                                         ctx.tile_request[:ctx.multi_tiles], ctx.tile_start[:ctx.multi_tiles],
-                                         ctx.tile_length[:ctx.multi_tiles], ctx.positions, self.scale,
-                                         self.window)
+        split = decode_rows and self.split_decode
+        if split:
+            # Requests that bring one token: split along the keys.
             ops.paged_attention_decode(q_heads, cache.pool, out, cache.block_tables, ctx.decode_token,
                                        ctx.decode_request, ctx.positions, self.scale,
                                        ctx.longest_context, self.window)
+        if self.flash and ctx.wide_tile_request is not None:
+            # Requests that bring several tokens: tensor cores, tiles of 64.
+            if ctx.wide_tile_request.numel():
+                ops.flash_prefill(q_heads, cache.pool, out, cache.block_tables, ctx.wide_tile_request,
+                                  ctx.wide_tile_start, ctx.wide_tile_length, ctx.positions, self.scale,
+                                  self.window)
+            rest = None if split else slice(ctx.multi_tiles, None)   # single tokens not yet served
         else:
-            ops.paged_attention_tile(q_heads, cache.pool, out, cache.block_tables, ctx.tile_request,
-                                     ctx.tile_start, ctx.tile_length, ctx.positions, self.scale,
-                                     self.window)
+            rest = slice(0, ctx.multi_tiles) if split else slice(0, None)
+        if rest is not None and ctx.tile_request[rest].numel():
+            ops.paged_attention_tile(q_heads, cache.pool, out, cache.block_tables, ctx.tile_request[rest],
+                                     ctx.tile_start[rest], ctx.tile_length[rest], ctx.positions,
+                                     self.scale, self.window)
         return self.o.forward(out.view(tokens, self.q_size))
 
     def weight_bytes(self) -> int:

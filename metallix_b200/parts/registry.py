@@ -119,4 +119,9 @@ class StepContext:
     decode_token: Optional[torch.Tensor] = None    # int32 [decode rows]
     decode_request: Optional[torch.Tensor] = None  # int32 [decode rows]
     longest_context: int = 0           # upper bound of position + 1 over the decode rows
+    # Tiles of up to 64 tokens over the multi-token requests, for the
+    # tensor-core prompt kernel; longest keys first.
+    wide_tile_request: Optional[torch.Tensor] = None
+    wide_tile_start: Optional[torch.Tensor] = None
+    wide_tile_length: Optional[torch.Tensor] = None
     extras: Dict[str, object] = field(default_factory=dict)
