@@ -14,6 +14,8 @@ the width of the longest context the engine allows.
 """
 from __future__ import annotations
 
+import gc
+import weakref
 from typing import Dict, List, Optional, Sequence
 
 import numpy as np
@@ -36,7 +38,7 @@ class _Bucket:
 
 class DecodeGraphs:
     def __init__(self, engine):
-        self.engine = engine
+        self._engine = weakref.ref(engine)   # the engine owns this object, not the reverse
         self.buckets: Dict[int, _Bucket] = {}
         self.pool = None
         cache = engine.cache
@@ -45,6 +47,10 @@ class DecodeGraphs:
         self.h2d_bytes = 0
         # Mirrors of the manager's tables: manager id -> (epoch, pages, per-group rows)
         self._host_tables: Dict[int, tuple] = {}
+
+    @property
+    def engine(self):
+        return self._engine()
 
     @staticmethod
     def usable(model) -> bool:
@@ -160,8 +166,17 @@ class DecodeGraphs:
         torch.cuda.synchronize(engine.device)
         graph = torch.cuda.CUDAGraph()
         before = ops.launch_count()
-        with torch.cuda.graph(graph, pool=self.pool):
-            bucket.logits = engine.model.forward(ids, ctx, views, wanted)
+        # No garbage collection while the stream captures: freeing another
+        # engine's graph or device memory in the middle would invalidate it.
+        collecting = gc.isenabled()
+        gc.collect()
+        gc.disable()
+        try:
+            with torch.cuda.graph(graph, pool=self.pool):
+                bucket.logits = engine.model.forward(ids, ctx, views, wanted)
+        finally:
+            if collecting:
+                gc.enable()
         bucket.kernels = ops.launch_count() - before
         if self.pool is None:
             self.pool = graph.pool()
