@@ -277,3 +277,70 @@ MXB_API int mxb_paged_attention_decode(const void* q, const void* cache, void* o
 #undef ARGS
   return static_cast<int>(cudaErrorInvalidValue);
 }
+
+// ---------------------------------------------------------------------------
+// The same attention for callers that cannot allocate: see
+// attention_decode_noalloc.h. The partial results live in a fixed array
+// inside the library instead of a buffer from the caller.
+#include <cstdio>
+#include <mutex>
+
+#include "attention_decode_noalloc.h"
+
+namespace mxb {
+
+// Device memory of every GPU that loads this library, until the process ends.
+static __device__ __align__(256) unsigned char noalloc_scratch[MXB_NOALLOC_SCRATCH_BYTES];
+
+constexpr int kMaxDevices = 64;
+static float* noalloc_address[kMaxDevices];  // the array's device address, per device
+static std::mutex noalloc_mutex;
+
+// In host code `noalloc_scratch` is only a handle of the symbol, not memory a
+// kernel may touch; the address kernels can use comes from the runtime, once
+// per device, with that device current.
+static cudaError_t noalloc_scratch_address(float** address) {
+  int device = 0;
+  cudaError_t e = cudaGetDevice(&device);
+  if (e != cudaSuccess) return e;
+  if (device < 0 || device >= kMaxDevices) return cudaErrorInvalidDevice;
+  std::lock_guard<std::mutex> guard(noalloc_mutex);
+  if (noalloc_address[device] == nullptr) {
+    void* found = nullptr;
+    e = cudaGetSymbolAddress(&found, noalloc_scratch);
+    if (e != cudaSuccess) return e;
+    noalloc_address[device] = static_cast<float*>(found);
+  }
+  *address = noalloc_address[device];
+  return cudaSuccess;
+}
+
+}  // namespace mxb
+
+MXB_API int mxb_paged_attention_decode_noalloc(const void* q, const void* cache, void* out,
+                                               const int* block_tables, int max_pages,
+                                               const int* row_token, const int* row_request,
+                                               const int* positions, int rows, int heads, int kv_heads,
+                                               int head_dim, int page_tokens, int num_pages,
+                                               int longest_context, int window, float scale, int dtype,
+                                               int* status, cudaStream_t stream) {
+  if (rows <= 0) return 0;
+  if (longest_context <= 0 || heads <= 0 || head_dim <= 0) return static_cast<int>(cudaErrorInvalidValue);
+  const int splits = (longest_context + kSplitKeys - 1) / kSplitKeys;
+  const unsigned long long need = static_cast<unsigned long long>(rows) * heads * splits *
+                                  (head_dim + 2) * sizeof(float);
+  if (need > MXB_NOALLOC_SCRATCH_BYTES) {
+    std::fprintf(stderr,
+                 "mxb_paged_attention_decode_noalloc: %d rows x %d heads x %d splits x (%d + 2) floats "
+                 "= %llu bytes of scratch, the built-in array holds %u; use fewer rows per call or "
+                 "mxb_paged_attention_decode with a buffer of your own\n",
+                 rows, heads, splits, head_dim, need, MXB_NOALLOC_SCRATCH_BYTES);
+    return static_cast<int>(cudaErrorInvalidValue);
+  }
+  float* scratch = nullptr;
+  const cudaError_t e = noalloc_scratch_address(&scratch);
+  if (e != cudaSuccess) return static_cast<int>(e);
+  return mxb_paged_attention_decode(q, cache, out, scratch, block_tables, max_pages, row_token,
+                                    row_request, positions, rows, heads, kv_heads, head_dim, page_tokens,
+                                    num_pages, splits, window, scale, dtype, status, stream);
+}
