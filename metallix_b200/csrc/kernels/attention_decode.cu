@@ -17,7 +17,7 @@
 
 namespace mxb {
 
-constexpr int kSplitKeys = 256;
+constexpr int kSplitKeys = 128;
 constexpr int kDecodeThreads = 128;
 constexpr float kDecodeMinusHuge = -1.0e30f;
 
@@ -40,8 +40,18 @@ template <> struct Vec16<__nv_bfloat16> {
   }
 };
 
+__device__ __forceinline__ void decode_copy_async_16(void* dst, const void* src, int src_bytes) {
+  const uint32_t address = static_cast<uint32_t>(__cvta_generic_to_shared(dst));
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(address), "l"(src), "r"(src_bytes));
+}
+
 // Partial layout per (token row, head, split): [head_dim] accumulator, then
 // the running maximum and the running sum.
+//
+// The split's keys and values are first brought into shared memory whole,
+// with every 16-byte copy of the block in flight at once (keys as one group of
+// asynchronous copies, values as a second): a decoded token has no arithmetic
+// to hide memory latency behind, so the copies must overlap each other.
 template <typename T, int HD, int G>
 __global__ void __launch_bounds__(kDecodeThreads)
 paged_attention_decode_kernel(const T* __restrict__ q, const T* __restrict__ cache,
@@ -50,13 +60,20 @@ paged_attention_decode_kernel(const T* __restrict__ q, const T* __restrict__ cac
                               const int* __restrict__ row_request, const int* __restrict__ positions,
                               int heads, int kv_heads, int page_tokens, int num_pages, int max_splits,
                               int window, float scale, int* status) {
-  constexpr int E = Vec16<T>::kElems;  // elements per 16-byte load
-  constexpr int LPK = HD / E;          // lanes that share one key row
-  constexpr int KPW = 32 / LPK;        // key rows a warp loads at once
+  constexpr int E = Vec16<T>::kElems;  // elements per 16-byte piece
+  constexpr int LPK = HD / E;          // 16-byte pieces (and lanes) per key row
+  constexpr int KPW = 32 / LPK;        // key rows a warp reads at once
+  constexpr int ROWS = kDecodeThreads / LPK;
   static_assert(HD % E == 0 && 32 % LPK == 0, "head_dim must split into 16-byte pieces over a warp");
-  __shared__ float s_score[G][kSplitKeys];
-  __shared__ float s_stat[G][2];
-  __shared__ float s_acc[kDecodeThreads / LPK][G][HD + 4];
+  extern __shared__ __align__(16) unsigned char decode_shared[];
+  T* sK = reinterpret_cast<T*>(decode_shared);                  // [kSplitKeys][HD]
+  T* sV = sK + kSplitKeys * HD;                                 // [kSplitKeys][HD]
+  constexpr size_t kStageBytes = 2 * static_cast<size_t>(kSplitKeys) * HD * sizeof(T);
+  constexpr size_t kReduceBytes = static_cast<size_t>(ROWS) * G * (HD + 4) * sizeof(float);
+  constexpr size_t kFront = kStageBytes > kReduceBytes ? kStageBytes : kReduceBytes;
+  float* s_score = reinterpret_cast<float*>(decode_shared + kFront);  // [G][kSplitKeys]
+  float* s_stat = s_score + G * kSplitKeys;                     // [G][2]
+  float* s_acc = reinterpret_cast<float*>(decode_shared);       // [ROWS][G][HD + 4], over K and V once they are used up
 
   const int split = blockIdx.x, kv = blockIdx.y, row = blockIdx.z;
   const int token = row_token[row];
@@ -74,6 +91,26 @@ paged_attention_decode_kernel(const T* __restrict__ q, const T* __restrict__ cac
   const size_t v_offset = static_cast<size_t>(kv_heads) * page_tokens * HD;
   const T* head_base = cache + static_cast<size_t>(kv) * page_tokens * HD;
 
+  // ---- every copy of the split in flight: keys, then values
+  const int piece = tid % LPK;
+#pragma unroll 1
+  for (int pass = 0; pass < 2; ++pass) {
+    T* dst_base = pass == 0 ? sK : sV;
+    for (int kk = tid / LPK; kk < count; kk += ROWS) {
+      const int key = begin + kk;
+      int page = table[key / page_tokens];
+      bool ok = page >= 0 && page < num_pages;
+      if (!ok) {
+        if (piece == 0 && pass == 0) atomicOr(status, kStatusBadPage);
+        page = 0;
+      }
+      const T* src = head_base + page * page_stride + (pass == 0 ? 0 : v_offset) +
+                     static_cast<size_t>(key % page_tokens) * HD + piece * E;
+      decode_copy_async_16(dst_base + kk * HD + piece * E, src, ok ? 16 : 0);
+    }
+    asm volatile("cp.async.commit_group;\n" ::);
+  }
+
   // ---- scores: a group of LPK lanes per key row
   const int sub = lane % LPK, which = lane / LPK;
   float qreg[G][E];
@@ -89,34 +126,29 @@ paged_attention_decode_kernel(const T* __restrict__ q, const T* __restrict__ cac
       for (int e = 0; e < E; ++e) qreg[h][e] = 0.0f;
     }
   }
+  asm volatile("cp.async.wait_group 1;\n" ::);  // the keys have landed
+  __syncthreads();
   for (int base = warp * KPW; base < count; base += (kDecodeThreads / 32) * KPW) {
     const int kk = base + which;
     float dots[G];
 #pragma unroll
     for (int h = 0; h < G; ++h) dots[h] = 0.0f;
     if (kk < count) {
-      const int key = begin + kk;
-      const int page = table[key / page_tokens];
-      if (page < 0 || page >= num_pages) {
-        if (sub == 0) atomicOr(status, kStatusBadPage);
-      } else {
-        Vec16<T> v;
-        v.raw = *reinterpret_cast<const decltype(v.raw)*>(
-            head_base + page * page_stride + static_cast<size_t>(key % page_tokens) * HD + sub * E);
-        float kf[E];
-        v.unpack(kf);
+      Vec16<T> v;
+      v.raw = *reinterpret_cast<const decltype(v.raw)*>(sK + kk * HD + sub * E);
+      float kf[E];
+      v.unpack(kf);
 #pragma unroll
-        for (int h = 0; h < G; ++h)
+      for (int h = 0; h < G; ++h)
 #pragma unroll
-          for (int e = 0; e < E; ++e) dots[h] = fmaf(qreg[h][e], kf[e], dots[h]);
-      }
+        for (int e = 0; e < E; ++e) dots[h] = fmaf(qreg[h][e], kf[e], dots[h]);
     }
 #pragma unroll
     for (int h = 0; h < G; ++h) {
 #pragma unroll
       for (int offset = LPK / 2; offset > 0; offset >>= 1)
         dots[h] += __shfl_xor_sync(0xffffffffu, dots[h], offset);
-      if (sub == 0 && kk < count) s_score[h][kk] = dots[h] * scale;
+      if (sub == 0 && kk < count) s_score[h * kSplitKeys + kk] = dots[h] * scale;
     }
   }
   __syncthreads();
@@ -124,21 +156,21 @@ paged_attention_decode_kernel(const T* __restrict__ q, const T* __restrict__ cac
   // ---- softmax statistics of this split, one warp per head
   for (int h = warp; h < group; h += kDecodeThreads / 32) {
     float m = kDecodeMinusHuge;
-    for (int kk = lane; kk < count; kk += 32) m = fmaxf(m, s_score[h][kk]);
+    for (int kk = lane; kk < count; kk += 32) m = fmaxf(m, s_score[h * kSplitKeys + kk]);
     m = warp_max(m);
     float l = 0.0f;
     for (int kk = lane; kk < count; kk += 32) {
-      const float p = expf(s_score[h][kk] - m);
-      s_score[h][kk] = p;
+      const float p = expf(s_score[h * kSplitKeys + kk] - m);
+      s_score[h * kSplitKeys + kk] = p;
       l += p;
     }
     l = warp_sum(l);
-    if (lane == 0) { s_stat[h][0] = m; s_stat[h][1] = l; }
+    if (lane == 0) { s_stat[h * 2] = m; s_stat[h * 2 + 1] = l; }
   }
+  asm volatile("cp.async.wait_group 0;\n" ::);  // the values have landed
   __syncthreads();
 
-  // ---- P V: LPK threads per value row, kDecodeThreads / LPK rows in flight
-  constexpr int ROWS = kDecodeThreads / LPK;
+  // ---- P V: LPK threads per value row, ROWS rows at a time
   const int vsub = tid % LPK, vrow = tid / LPK;
   float acc[G][E];
 #pragma unroll
@@ -146,36 +178,33 @@ paged_attention_decode_kernel(const T* __restrict__ q, const T* __restrict__ cac
 #pragma unroll
     for (int e = 0; e < E; ++e) acc[h][e] = 0.0f;
   for (int kk = vrow; kk < count; kk += ROWS) {
-    const int key = begin + kk;
-    const int page = table[key / page_tokens];
-    if (page < 0 || page >= num_pages) continue;  // already flagged above
     Vec16<T> v;
-    v.raw = *reinterpret_cast<const decltype(v.raw)*>(
-        head_base + page * page_stride + v_offset + static_cast<size_t>(key % page_tokens) * HD + vsub * E);
+    v.raw = *reinterpret_cast<const decltype(v.raw)*>(sV + kk * HD + vsub * E);
     float vf[E];
     v.unpack(vf);
 #pragma unroll
     for (int h = 0; h < G; ++h) {
-      const float p = s_score[h][kk];
+      const float p = s_score[h * kSplitKeys + kk];
 #pragma unroll
       for (int e = 0; e < E; ++e) acc[h][e] = fmaf(p, vf[e], acc[h][e]);
     }
   }
+  __syncthreads();  // s_acc lies over the keys and values: everybody is done reading them
 #pragma unroll
   for (int h = 0; h < G; ++h)
 #pragma unroll
-    for (int e = 0; e < E; ++e) s_acc[vrow][h][vsub * E + e] = acc[h][e];
+    for (int e = 0; e < E; ++e) s_acc[(vrow * G + h) * (HD + 4) + vsub * E + e] = acc[h][e];
   __syncthreads();
   // Sum the ROWS partial accumulators in a fixed order and write the partial.
   for (int i = tid; i < group * HD; i += kDecodeThreads) {
     const int h = i / HD, d = i - h * HD;
     float sum = 0.0f;
 #pragma unroll
-    for (int r = 0; r < ROWS; ++r) sum += s_acc[r][h][d];
+    for (int r = 0; r < ROWS; ++r) sum += s_acc[(r * G + h) * (HD + 4) + d];
     const int head = kv * group + h;
     float* dst = partial + ((static_cast<size_t>(row) * heads + head) * max_splits + split) * (HD + 2);
     dst[d] = sum;
-    if (d == 0) { dst[HD] = s_stat[h][0]; dst[HD + 1] = s_stat[h][1]; }
+    if (d == 0) { dst[HD] = s_stat[h * 2]; dst[HD + 1] = s_stat[h * 2 + 1]; }
   }
 }
 
@@ -218,7 +247,17 @@ static int launch_decode(const void* q, const void* cache, void* out, float* par
                          int kv_heads, int page_tokens, int num_pages, int max_splits, int window,
                          float scale, int* status, cudaStream_t stream) {
   dim3 grid(max_splits, kv_heads, rows);
-  paged_attention_decode_kernel<T, HD, G><<<grid, kDecodeThreads, 0, stream>>>(
+  constexpr int kElems = Vec16<T>::kElems;
+  constexpr size_t kStage = 2 * static_cast<size_t>(kSplitKeys) * HD * sizeof(T);       // keys and values
+  constexpr size_t kReduce = static_cast<size_t>(kDecodeThreads / (HD / kElems)) * G * (HD + 4) * sizeof(float);
+  const size_t shared = (kStage > kReduce ? kStage : kReduce) +
+                        (static_cast<size_t>(G) * kSplitKeys + G * 2) * sizeof(float);
+  auto kernel = paged_attention_decode_kernel<T, HD, G>;
+  if (shared > 48 * 1024) {
+    cudaError_t attribute = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(shared));
+    if (attribute != cudaSuccess) return static_cast<int>(attribute);
+  }
+  kernel<<<grid, kDecodeThreads, shared, stream>>>(
       static_cast<const T*>(q), static_cast<const T*>(cache), partial, block_tables, max_pages,
       row_token, row_request, positions, heads, kv_heads, page_tokens, num_pages, max_splits, window,
       scale, status);
@@ -247,7 +286,7 @@ MXB_API int mxb_paged_attention_split_keys() { return kSplitKeys; }
 
 // partial: float32 scratch of rows * heads * max_splits * (head_dim + 2) values.
 // rows of row_token that are negative are padding. max_splits must cover the
-// longest context: ceil(longest / 256).
+// longest context: ceil(longest / 128).
 MXB_API int mxb_paged_attention_decode(const void* q, const void* cache, void* out, float* partial,
                                        const int* block_tables, int max_pages, const int* row_token,
                                        const int* row_request, const int* positions, int rows,

@@ -13,7 +13,7 @@
 //  * The scratch is MXB_NOALLOC_SCRATCH_BYTES (16 MiB) of device memory per
 //    GPU that loads the library, held until the process exits.
 //    rows * heads * splits * (head_dim + 2) * 4 bytes must fit, where
-//    splits = ceil(longest_context / 256); a larger call is refused with
+//    splits = ceil(longest_context / 128); a larger call is refused with
 //    cudaErrorInvalidValue (1) and a message on stderr, and nothing runs.
 //  * The first call on each device looks up the array's device address
 //    (with that device current). Make that first call outside any stream

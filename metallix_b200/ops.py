@@ -43,6 +43,8 @@ _SIGNATURES = {
     "mxb_flash_prefill_supported": [_I, _I, _I, _I],
     "mxb_flash_prefill_tile": [],
     "mxb_gemm_simple": [_P, _I, _P, _P, _I, _I, _I, _I, _L, _L, _L, _P],
+    "mxb_gemm_skinny": [_P, _I, _P, _P, _I, _I, _I, _L, _L, _L, _I, _P],
+    "mxb_gemm_skinny_supported": [_I, _I, _I, _L, _L],
     "mxb_silu_mul": [_P, _P, _I, _L, _I, _P],
     "mxb_argmax": [_P, _L, _I, _I, _P, _P, _P],
     "mxb_sample_icdf": [_P, _L, _I, _I, _P, _P, _P, _P, _P, _P, _P, _P],
@@ -418,20 +420,56 @@ def gemm_simple(a: torch.Tensor, w: torch.Tensor, out_dtype: Optional[torch.dtyp
     return out
 
 
+def gemm_skinny_supported(a: torch.Tensor, w: torch.Tensor) -> bool:
+    """Whether the weight-streaming kernel takes a [m, k] times w [n, k]
+    transposed: bfloat16, at most 64 rows, k a multiple of 32, rows on 16-byte
+    boundaries."""
+    if a.dtype != torch.bfloat16 or w.dtype != torch.bfloat16 or a.dim() != 2 or w.dim() != 2:
+        return False
+    if a.stride(1) != 1 or w.stride(1) != 1 or a.data_ptr() % 16 or w.data_ptr() % 16:
+        return False
+    return bool(_fn("mxb_gemm_skinny_supported")(a.shape[0], w.shape[0], a.shape[1], a.stride(0), w.stride(0)))
+
+
+def gemm_skinny(a: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype = torch.bfloat16,
+                swiglu: bool = False, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """a [m <= 64, k] times w [n, k] transposed, reading w once. With
+    ``swiglu`` w holds gate rows then up rows and the result is
+    silu(gate) * up, [m, n / 2]."""
+    _need(a.is_cuda and w.is_cuda and a.shape[1] == w.shape[1], "operands do not fit a @ w.T on a CUDA device")
+    _need(gemm_skinny_supported(a, w), "the weight-streaming kernel takes bfloat16, at most 64 rows, "
+          "k a multiple of 32 and rows on 16-byte boundaries")
+    _need(out_dtype in (torch.bfloat16, torch.float32), "out_dtype must be bfloat16 or float32")
+    m, k = a.shape
+    n = w.shape[0]
+    _need(not swiglu or n % 2 == 0, "gate and up rows must pair up")
+    columns = n // 2 if swiglu else n
+    if out is None:
+        out = torch.empty((m, columns), dtype=out_dtype, device=a.device)
+    _need(out.shape == (m, columns) and out.dtype == out_dtype and out.stride(1) == 1, "out does not fit")
+    _call("mxb_gemm_skinny", out.data_ptr(), _CODES[out_dtype], a.data_ptr(), w.data_ptr(), m, n, k,
+          a.stride(0), w.stride(0), out.stride(0), columns if swiglu else 0, _stream())
+    return out
+
+
 def gemm_bf16(a: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype = torch.bfloat16,
               backend: str = "auto", out: Optional[torch.Tensor] = None) -> torch.Tensor:
     """bfloat16 a [m, k] times w [n, k] transposed with float32 accumulation.
 
-    ``backend``: "tcgen05" is the hand-written tensor-core kernel, "cublas" the
-    library product (where the reference calls a library matmul too), "simple"
-    the plain CUDA-core kernel, "auto" the tensor-core kernel where its shape
-    rules hold and the library otherwise."""
+    ``backend``: "skinny" is the weight-streaming kernel for at most 64 rows,
+    "tcgen05" the hand-written tensor-core kernel, "cublas" the library product
+    (where the reference calls a library matmul too), "simple" the plain
+    CUDA-core kernel, "auto" the hand-written kernel whose shape rules hold and
+    the library otherwise."""
     _need(a.is_cuda and w.is_cuda, "operands must be on a CUDA device")
     _need(a.dtype == torch.bfloat16 and w.dtype == torch.bfloat16, "operands must be bfloat16")
     _need(a.dim() == 2 and w.dim() == 2 and a.shape[1] == w.shape[1], "shapes do not match a @ w.T")
     _need(out_dtype in (torch.bfloat16, torch.float32), "out_dtype must be bfloat16 or float32")
     if backend == "simple":
         return gemm_simple(a, w, out_dtype=out_dtype, out=out)
+    if backend in ("auto", "skinny") and a.shape[0] <= 64 and gemm_skinny_supported(a, w):
+        return gemm_skinny(a, w, out_dtype=out_dtype, out=out)
+    _need(backend != "skinny", "the weight-streaming kernel does not take this shape")
     if backend in ("auto", "tcgen05"):
         from . import tensor_core
         if tensor_core.supports(a, w, out_dtype):

@@ -490,6 +490,40 @@ def test_gemm_bf16(ops, backend, m, n, k):
     assert np.abs(out16.cpu().double().numpy() - ref).max() < 0.02 * np.abs(ref).max()
 
 
+@pytest.mark.parametrize("m", [1, 3, 8, 9, 16, 31, 64])
+@pytest.mark.parametrize("n, k", [(331, 96), (1024, 3072), (40, 32), (4096, 1024)])
+def test_gemm_skinny(ops, m, n, k):
+    rng = np.random.default_rng(m + n)
+    a, w = rng.normal(size=(m, k)), rng.normal(size=(n, k)) * 0.05
+    a_d, w_d = dev(a, torch.bfloat16), dev(w, torch.bfloat16)
+    assert ops.gemm_skinny_supported(a_d, w_d)
+    ref = rounded(a, torch.bfloat16) @ rounded(w, torch.bfloat16).T
+    out32 = ops.gemm_skinny(a_d, w_d, torch.float32)
+    assert np.abs(out32.cpu().double().numpy() - ref).max() < 1e-4 * np.sqrt(k / 32)
+    out16 = ops.gemm_skinny(a_d, w_d, torch.bfloat16)
+    assert (np.abs(out16.cpu().double().numpy() - ref) <= 2.0 ** -8 * np.abs(ref) + 1e-4).all()
+    # a row's result does not depend on how many other rows ride along
+    alone = ops.gemm_skinny(a_d[m - 1:m].contiguous(), w_d, torch.float32)
+    assert torch.equal(alone[0], out32[m - 1])
+    assert torch.equal(ops.gemm_bf16(a_d, w_d, torch.float32, backend="auto"), out32)
+
+
+@pytest.mark.parametrize("m", [1, 8, 24, 64])
+def test_gemm_skinny_swiglu(ops, m):
+    rng = np.random.default_rng(m)
+    inter, k = 3 * 56, 96
+    a, w = rng.normal(size=(m, k)), rng.normal(size=(2 * inter, k)) * 0.3
+    out = ops.gemm_skinny(dev(a, torch.bfloat16), dev(w, torch.bfloat16), swiglu=True)
+    gate_up = rounded(rounded(a, torch.bfloat16) @ rounded(w, torch.bfloat16).T, torch.bfloat16)
+    g, u = gate_up[:, :inter], gate_up[:, inter:]
+    ref = g / (1 + np.exp(-g)) * u
+    error = np.abs(out.cpu().double().numpy() - ref)
+    # gate and up may each land one bfloat16 step away from the float64 product's rounding
+    assert (error <= 3 * 2.0 ** -8 * (np.abs(ref) + np.abs(u) * 0.3 + np.abs(g) * 0.3) + 1e-4).all()
+    assert not ops.gemm_skinny_supported(dev(a[:, :80], torch.bfloat16).contiguous(), dev(w[:, :80], torch.bfloat16).contiguous())
+    assert not ops.gemm_skinny_supported(dev(np.zeros((65, k)), torch.bfloat16), dev(w, torch.bfloat16))
+
+
 @pytest.mark.parametrize("dtype", DTYPES)
 def test_silu_mul(ops, dtype):
     rng = np.random.default_rng(4)
