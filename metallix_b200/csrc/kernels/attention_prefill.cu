@@ -49,6 +49,12 @@ __device__ __forceinline__ void mma_bf16_16816(float (&d)[4], const uint32_t (&a
                : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
                : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
+// 2^x on the special-function unit (relative error about 2^-22); -inf gives 0.
+__device__ __forceinline__ float fast_exp2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;\n" : "=f"(y) : "f"(x));
+  return y;
+}
 __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
   __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
   return *reinterpret_cast<uint32_t*>(&v);
@@ -62,7 +68,7 @@ template <int HD> __device__ __forceinline__ uint32_t tile_offset(int row, int c
 }
 
 template <int HD>
-__global__ void __launch_bounds__(kFlashThreads)
+__global__ void __launch_bounds__(kFlashThreads, 3)
 flash_prefill_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ cache,
                      __nv_bfloat16* __restrict__ out, const int* __restrict__ block_tables, int max_pages,
                      const int* __restrict__ tile_request, const int* __restrict__ tile_start,
@@ -71,11 +77,12 @@ flash_prefill_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* _
   constexpr int CHUNKS = HD / 8;                      // 16-byte chunks per row
   constexpr int TILE_BYTES = kFlashKeys * HD * 2;
   extern __shared__ __align__(128) unsigned char shared[];
-  unsigned char* sQ = shared;                          // [64][HD]
-  unsigned char* sK = sQ + kFlashQueries * HD * 2;     // 2 x [64][HD]
+  unsigned char* sK = shared;                          // 2 x [64][HD]
   unsigned char* sV = sK + 2 * TILE_BYTES;             // 2 x [64][HD]
+  unsigned char* sQ = sK + TILE_BYTES;                 // [64][HD]: the query tile borrows the second key
+                                                       // stage until its fragments sit in registers
 
-  const int tile = blockIdx.x, head = blockIdx.y;
+  const int head = blockIdx.x, tile = blockIdx.y;  // heads of one tile run side by side and share its keys in L2
   const int kv = head / (heads / kv_heads);
   const int t0 = tile_start[tile], n = tile_length[tile];
   const int pos0 = positions[t0];
@@ -96,26 +103,29 @@ flash_prefill_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* _
   }
   copy_async_commit();
 
+  // Two threads per key row: one block-table lookup each, then their half of
+  // the row's 16-byte chunks of K and of V.
   auto load_keys = [&](int key_tile, int stage) {
-    const int key0 = key_tile * kFlashKeys;
-    for (int i = tid; i < kFlashKeys * CHUNKS; i += kFlashThreads) {
-      const int row = i / CHUNKS, chunk = i - row * CHUNKS;
-      const int key = key0 + row;
-      bool valid = key >= first_key && key <= last_pos;
-      int page = 0;
-      if (valid) {
-        page = table[key / page_tokens];
-        if (page < 0 || page >= num_pages) {
-          atomicOr(status, kStatusBadPage);
-          valid = false;
-          page = 0;
-        }
+    const int row = tid >> 1, half = tid & 1;
+    const int key = key_tile * kFlashKeys + row;
+    bool valid = key >= first_key && key <= last_pos;
+    int page = 0;
+    if (valid) {
+      page = table[key / page_tokens];
+      if (page < 0 || page >= num_pages) {
+        atomicOr(status, kStatusBadPage);
+        valid = false;
+        page = 0;
       }
-      const __nv_bfloat16* src = head_base + page * page_stride +
-                                 static_cast<size_t>(valid ? key % page_tokens : 0) * HD + chunk * 8;
+    }
+    const __nv_bfloat16* src = head_base + page * page_stride + static_cast<size_t>(valid ? key % page_tokens : 0) * HD;
+    const int bytes = valid ? 16 : 0;
+#pragma unroll
+    for (int c = 0; c < CHUNKS / 2; ++c) {
+      const int chunk = half * (CHUNKS / 2) + c;
       const uint32_t offset = stage * TILE_BYTES + tile_offset<HD>(row, chunk);
-      copy_async_16(smem_address(sK + offset), src, valid ? 16 : 0);
-      copy_async_16(smem_address(sV + offset), src + v_offset, valid ? 16 : 0);
+      copy_async_16(smem_address(sK + offset), src + chunk * 8, bytes);
+      copy_async_16(smem_address(sV + offset), src + v_offset + chunk * 8, bytes);
     }
     copy_async_commit();
   };
@@ -136,6 +146,16 @@ flash_prefill_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* _
   for (int i = 0; i < HD / 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.0f;
   uint32_t qf[HD / 16][4];
 
+  // The query fragments move to registers before the second stage is filled.
+  copy_async_wait<1>();  // the query tile (the first group) has landed
+  __syncthreads();
+#pragma unroll
+  for (int ks = 0; ks < HD / 16; ++ks) {
+    const int row = warp * 16 + (lane & 7) + ((lane >> 3) & 1) * 8;
+    ldmatrix_x4(qf[ks], smem_address(sQ + tile_offset<HD>(row, ks * 2 + (lane >> 4))));
+  }
+  __syncthreads();
+
   for (int kt = tile_begin; kt <= tile_end; ++kt) {
     const int stage = (kt - tile_begin) & 1;
     if (kt < tile_end) {
@@ -145,13 +165,6 @@ flash_prefill_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* _
       copy_async_wait<0>();
     }
     __syncthreads();
-    if (kt == tile_begin) {
-#pragma unroll
-      for (int ks = 0; ks < HD / 16; ++ks) {
-        const int row = warp * 16 + (lane & 7) + ((lane >> 3) & 1) * 8;
-        ldmatrix_x4(qf[ks], smem_address(sQ + tile_offset<HD>(row, ks * 2 + (lane >> 4))));
-      }
-    }
     const unsigned char* k_tile = sK + stage * TILE_BYTES;
     const unsigned char* v_tile = sV + stage * TILE_BYTES;
 
@@ -171,37 +184,46 @@ flash_prefill_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* _
       }
     }
 
-    // ---- mask, running maximum and sum (float32)
+    // ---- mask, running maximum and sum (float32). m_* hold the running
+    // maximum already multiplied by scale * log2(e).
     const int key0 = kt * kFlashKeys;
-    float max_lo = m_lo, max_hi = m_hi;
+    const bool all_seen = window <= 0 && n == kFlashQueries && key0 + kFlashKeys - 1 <= pos0;
+    if (!all_seen) {
+#pragma unroll
+      for (int nb = 0; nb < kFlashKeys / 8; ++nb) {
+#pragma unroll
+        for (int j = 0; j < 2; ++j) {
+          const int key = key0 + nb * 8 + 2 * t + j;
+          const bool seen_lo = valid_lo && key <= pos_lo && key >= first_key && (window <= 0 || key > pos_lo - window);
+          const bool seen_hi = valid_hi && key <= pos_hi && key >= first_key && (window <= 0 || key > pos_hi - window);
+          if (!seen_lo) s[nb][j] = -INFINITY;
+          if (!seen_hi) s[nb][2 + j] = -INFINITY;
+        }
+      }
+    }
+    float max_lo = -INFINITY, max_hi = -INFINITY;
 #pragma unroll
     for (int nb = 0; nb < kFlashKeys / 8; ++nb) {
-#pragma unroll
-      for (int j = 0; j < 2; ++j) {
-        const int key = key0 + nb * 8 + 2 * t + j;
-        const bool seen_lo = valid_lo && key <= pos_lo && key >= first_key && (window <= 0 || key > pos_lo - window);
-        const bool seen_hi = valid_hi && key <= pos_hi && key >= first_key && (window <= 0 || key > pos_hi - window);
-        s[nb][j] = seen_lo ? s[nb][j] * scale_log2 : -INFINITY;
-        s[nb][2 + j] = seen_hi ? s[nb][2 + j] * scale_log2 : -INFINITY;
-        max_lo = fmaxf(max_lo, s[nb][j]);
-        max_hi = fmaxf(max_hi, s[nb][2 + j]);
-      }
+      max_lo = fmaxf(max_lo, fmaxf(s[nb][0], s[nb][1]));
+      max_hi = fmaxf(max_hi, fmaxf(s[nb][2], s[nb][3]));
     }
     max_lo = fmaxf(max_lo, __shfl_xor_sync(0xffffffffu, max_lo, 1));
     max_lo = fmaxf(max_lo, __shfl_xor_sync(0xffffffffu, max_lo, 2));
     max_hi = fmaxf(max_hi, __shfl_xor_sync(0xffffffffu, max_hi, 1));
     max_hi = fmaxf(max_hi, __shfl_xor_sync(0xffffffffu, max_hi, 2));
+    max_lo = fmaxf(m_lo, max_lo * scale_log2);  // scale > 0 keeps the order
+    max_hi = fmaxf(m_hi, max_hi * scale_log2);
     // A row that has seen no key yet keeps a finite reference so that no
     // inf - inf appears.
     const float ref_lo = max_lo == -INFINITY ? 0.0f : max_lo;
     const float ref_hi = max_hi == -INFINITY ? 0.0f : max_hi;
-    const float alpha_lo = exp2f(m_lo - ref_lo), alpha_hi = exp2f(m_hi - ref_hi);
+    const float alpha_lo = fast_exp2(m_lo - ref_lo), alpha_hi = fast_exp2(m_hi - ref_hi);
     float sum_lo = 0.0f, sum_hi = 0.0f;
     uint32_t pf[kFlashKeys / 16][4];
 #pragma unroll
     for (int nb = 0; nb < kFlashKeys / 8; ++nb) {
-      const float p0 = exp2f(s[nb][0] - ref_lo), p1 = exp2f(s[nb][1] - ref_lo);
-      const float p2 = exp2f(s[nb][2] - ref_hi), p3 = exp2f(s[nb][3] - ref_hi);
+      const float p0 = fast_exp2(fmaf(s[nb][0], scale_log2, -ref_lo)), p1 = fast_exp2(fmaf(s[nb][1], scale_log2, -ref_lo));
+      const float p2 = fast_exp2(fmaf(s[nb][2], scale_log2, -ref_hi)), p3 = fast_exp2(fmaf(s[nb][3], scale_log2, -ref_hi));
       sum_lo += p0 + p1;
       sum_hi += p2 + p3;
       pf[nb >> 1][(nb & 1) * 2] = pack_bf16(p0, p1);
@@ -252,11 +274,11 @@ static int launch_flash(const void* q, const void* cache, void* out, const int* 
                         const int* tile_request, const int* tile_start, const int* tile_length,
                         const int* positions, int tiles, int heads, int kv_heads, int page_tokens,
                         int num_pages, int window, float scale, int* status, cudaStream_t stream) {
-  const int shared = kFlashQueries * HD * 2 + 4 * kFlashKeys * HD * 2;
+  const int shared = 4 * kFlashKeys * HD * 2;
   auto kernel = flash_prefill_kernel<HD>;
   cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, shared);
   if (e != cudaSuccess) return static_cast<int>(e);
-  dim3 grid(tiles, heads);
+  dim3 grid(heads, tiles);
   kernel<<<grid, kFlashThreads, shared, stream>>>(
       static_cast<const __nv_bfloat16*>(q), static_cast<const __nv_bfloat16*>(cache),
       static_cast<__nv_bfloat16*>(out), block_tables, max_pages, tile_request, tile_start, tile_length,

@@ -63,6 +63,54 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ x, const TDelta* __restri
     y[base + i] = from_float<TOut>(x[base + i] * scale * w[i]);
 }
 
+// Four values per thread at a time (rows whose width is a multiple of 4 and
+// that start on 16-byte boundaries).
+__device__ __forceinline__ float4 load4(const float* p) { return *reinterpret_cast<const float4*>(p); }
+__device__ __forceinline__ float4 load4(const __nv_bfloat16* p) {
+  const uint2 raw = *reinterpret_cast<const uint2*>(p);
+  return make_float4(__uint_as_float(raw.x << 16), __uint_as_float(raw.x & 0xffff0000u),
+                     __uint_as_float(raw.y << 16), __uint_as_float(raw.y & 0xffff0000u));
+}
+__device__ __forceinline__ void store4(float* p, float4 v) { *reinterpret_cast<float4*>(p) = v; }
+__device__ __forceinline__ void store4(__nv_bfloat16* p, float4 v) {
+  __nv_bfloat162 lo = __floats2bfloat162_rn(v.x, v.y), hi = __floats2bfloat162_rn(v.z, v.w);
+  uint2 raw;
+  raw.x = *reinterpret_cast<uint32_t*>(&lo);
+  raw.y = *reinterpret_cast<uint32_t*>(&hi);
+  *reinterpret_cast<uint2*>(p) = raw;
+}
+
+// The same sums in the same order per thread as the scalar kernels would make
+// with a quarter of the threads: thread t owns elements 4t .. 4t + 3 of every
+// stride.
+template <typename TDelta, typename TOut, bool ADD>
+__global__ void add_rmsnorm_vec4_kernel(float* __restrict__ x, const TDelta* __restrict__ delta,
+                                        TOut* __restrict__ y, const float* __restrict__ w,
+                                        const int* __restrict__ rows_index, int size, float eps) {
+  __shared__ float scratch[33];
+  const size_t src = rows_index ? static_cast<size_t>(rows_index[blockIdx.x]) : static_cast<size_t>(blockIdx.x);
+  float* row = x + src * size;
+  float sum = 0.0f;
+  for (int i = threadIdx.x * 4; i < size; i += blockDim.x * 4) {
+    float4 v = load4(row + i);
+    if (ADD) {
+      const float4 d = load4(delta + src * size + i);
+      v.x += d.x; v.y += d.y; v.z += d.z; v.w += d.w;
+      store4(row + i, v);
+    }
+    sum += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+  }
+  sum = block_sum(sum, scratch);
+  const float scale = rsqrtf(sum / static_cast<float>(size) + eps);
+  TOut* dst = y + static_cast<size_t>(blockIdx.x) * size;
+  for (int i = threadIdx.x * 4; i < size; i += blockDim.x * 4) {
+    const float4 v = load4(row + i), g = load4(w + i);
+    store4(dst + i, make_float4(v.x * scale * g.x, v.y * scale * g.y, v.z * scale * g.z, v.w * scale * g.w));
+  }
+}
+
+static bool aligned16(const void* p) { return reinterpret_cast<uintptr_t>(p) % 16 == 0; }
+
 // x[r, :] += delta[r, :] alone (the last residual sum of a model).
 template <typename TDelta>
 __global__ void add_kernel(float* __restrict__ x, const TDelta* __restrict__ delta, size_t count) {
@@ -96,6 +144,17 @@ MXB_API int mxb_embed(float* out, const void* table, int table_dtype, const int*
 MXB_API int mxb_rmsnorm(void* y, int y_dtype, const void* x, int x_dtype, const float* w,
                         const int* rows_index, int rows, int size, float eps, cudaStream_t stream) {
   if (rows <= 0) return 0;
+  if (x_dtype == kF32 && size % 4 == 0 && aligned16(x) && aligned16(y) && aligned16(w)) {
+    const int vec_threads = norm_threads(size / 4);
+    float* xs = const_cast<float*>(static_cast<const float*>(x));  // read only: ADD is false
+    if (y_dtype == kF32)
+      add_rmsnorm_vec4_kernel<float, float, false><<<rows, vec_threads, 0, stream>>>(xs, nullptr, static_cast<float*>(y), w, rows_index, size, eps);
+    else if (y_dtype == kBF16)
+      add_rmsnorm_vec4_kernel<float, __nv_bfloat16, false><<<rows, vec_threads, 0, stream>>>(xs, nullptr, static_cast<__nv_bfloat16*>(y), w, rows_index, size, eps);
+    else
+      return static_cast<int>(cudaErrorInvalidValue);
+    return static_cast<int>(cudaGetLastError());
+  }
   const int threads = norm_threads(size);
 #define LAUNCH(TI, TO) rmsnorm_kernel<TI, TO><<<rows, threads, 0, stream>>>( \
       static_cast<TO*>(y), static_cast<const TI*>(x), w, rows_index, size, eps)
@@ -111,6 +170,19 @@ MXB_API int mxb_rmsnorm(void* y, int y_dtype, const void* x, int x_dtype, const 
 MXB_API int mxb_add_rmsnorm(float* x, const void* delta, int delta_dtype, void* y, int y_dtype,
                             const float* w, int rows, int size, float eps, cudaStream_t stream) {
   if (rows <= 0) return 0;
+  if (size % 4 == 0 && aligned16(x) && aligned16(y) && aligned16(w) && aligned16(delta) &&
+      (delta_dtype == kF32 || size % 8 == 0)) {
+    const int vec_threads = norm_threads(size / 4);
+#define VEC(TD, TO) add_rmsnorm_vec4_kernel<TD, TO, true><<<rows, vec_threads, 0, stream>>>( \
+        x, static_cast<const TD*>(delta), static_cast<TO*>(y), w, nullptr, size, eps)
+    if (delta_dtype == kF32 && y_dtype == kF32) VEC(float, float);
+    else if (delta_dtype == kBF16 && y_dtype == kBF16) VEC(__nv_bfloat16, __nv_bfloat16);
+    else if (delta_dtype == kF32 && y_dtype == kBF16) VEC(float, __nv_bfloat16);
+    else if (delta_dtype == kBF16 && y_dtype == kF32) VEC(__nv_bfloat16, float);
+    else return static_cast<int>(cudaErrorInvalidValue);
+#undef VEC
+    return static_cast<int>(cudaGetLastError());
+  }
   const int threads = norm_threads(size);
 #define LAUNCH(TD, TO) add_rmsnorm_kernel<TD, TO><<<rows, threads, 0, stream>>>( \
       x, static_cast<const TD*>(delta), static_cast<TO*>(y), w, size, eps)

@@ -92,6 +92,86 @@ __global__ void qk_norm_rope_cache_kernel(
   }
 }
 
+// The same work with one warp per (token, head) and no shared memory, for
+// head sizes that are a multiple of 64 with the rotation over the whole head:
+// lane l holds elements l, l + 32, l + 64, ...; the rotation partner of
+// element i (i +- head_dim / 2) then sits in the same lane.
+template <typename T, int PER_LANE>
+__global__ void __launch_bounds__(256)
+qk_norm_rope_cache_warp_kernel(
+    const T* __restrict__ q_in, const T* __restrict__ k_in, const T* __restrict__ v_in,
+    long long q_stride, long long k_stride, long long v_stride, T* __restrict__ q_out,
+    T* __restrict__ cache, const int* __restrict__ slots, const int* __restrict__ positions,
+    const float* __restrict__ q_weight, const float* __restrict__ k_weight,
+    const float* __restrict__ cos_table, const float* __restrict__ sin_table, int table_positions,
+    int tokens, int heads, int kv_heads, int page_tokens, int num_pages, float eps, int* status) {
+  constexpr int HD = PER_LANE * 32;
+  constexpr int HALF = HD / 2;
+  const int lane = threadIdx.x & 31;
+  const int per_token = heads + 2 * kv_heads;
+  const long long item = static_cast<long long>(blockIdx.x) * 8 + (threadIdx.x >> 5);
+  if (item >= static_cast<long long>(tokens) * per_token) return;
+  const int t = static_cast<int>(item / per_token), h = static_cast<int>(item % per_token);
+  const bool is_q = h < heads;
+  const bool is_k = !is_q && h < heads + kv_heads;
+  const int kv = is_q ? 0 : (is_k ? h - heads : h - heads - kv_heads);
+  const T* src = is_q ? q_in + t * q_stride + static_cast<long long>(h) * HD
+               : is_k ? k_in + t * k_stride + static_cast<long long>(kv) * HD
+                      : v_in + t * v_stride + static_cast<long long>(kv) * HD;
+  T* dst = nullptr;
+  if (is_q) {
+    if (q_out == nullptr) return;
+    dst = q_out + (static_cast<size_t>(t) * heads + h) * HD;
+  } else {
+    if (slots == nullptr || cache == nullptr) return;
+    const int slot = slots[t];
+    if (slot < 0) return;
+    const int page = slot / page_tokens, row = slot - page * page_tokens;
+    if (page >= num_pages) {
+      if (lane == 0) atomicOr(status, kStatusBadSlot);
+      return;
+    }
+    dst = cache + (((static_cast<size_t>(page) * 2 + (is_k ? 0 : 1)) * kv_heads + kv) * page_tokens + row) * HD;
+  }
+  if (!is_q && !is_k) {
+#pragma unroll
+    for (int j = 0; j < PER_LANE; ++j) dst[lane + 32 * j] = src[lane + 32 * j];
+    return;
+  }
+  float x[PER_LANE];
+  float sum = 0.0f;
+#pragma unroll
+  for (int j = 0; j < PER_LANE; ++j) {
+    x[j] = to_float(src[lane + 32 * j]);
+    sum += x[j] * x[j];
+  }
+  const float* weight = is_q ? q_weight : k_weight;
+  if (weight != nullptr) {
+    sum = warp_sum(sum);
+    const float scale = rsqrtf(sum / static_cast<float>(HD) + eps);
+#pragma unroll
+    for (int j = 0; j < PER_LANE; ++j) x[j] = x[j] * scale * weight[lane + 32 * j];
+  }
+  if (cos_table != nullptr) {
+    int pos = positions[t];
+    if (pos < 0 || pos >= table_positions) {
+      if (lane == 0) atomicOr(status, kStatusBadSlot);
+      pos = 0;
+    }
+    const float* c = cos_table + static_cast<size_t>(pos) * HALF;
+    const float* sn = sin_table + static_cast<size_t>(pos) * HALF;
+#pragma unroll
+    for (int j = 0; j < PER_LANE / 2; ++j) {
+      const int i = lane + 32 * j;  // i < HALF; its partner is element i + HALF = x[j + PER_LANE / 2]
+      const float lo = x[j], hi = x[j + PER_LANE / 2];
+      x[j] = lo * c[i] - hi * sn[i];
+      x[j + PER_LANE / 2] = hi * c[i] + lo * sn[i];
+    }
+  }
+#pragma unroll
+  for (int j = 0; j < PER_LANE; ++j) dst[lane + 32 * j] = from_float<T>(x[j]);
+}
+
 }  // namespace mxb
 
 using namespace mxb;
@@ -104,6 +184,23 @@ MXB_API int mxb_qk_norm_rope_cache(
     int page_tokens, int num_pages, float eps, int dtype, int* status, cudaStream_t stream) {
   if (tokens <= 0) return 0;
   if (rotary_dim < 0 || rotary_dim > head_dim || (rotary_dim & 1)) return static_cast<int>(cudaErrorInvalidValue);
+  if ((head_dim == 64 || head_dim == 128 || head_dim == 256) && (cos_table == nullptr || rotary_dim == head_dim)) {
+    const long long items = static_cast<long long>(tokens) * (heads + 2 * kv_heads);
+    const unsigned blocks = static_cast<unsigned>((items + 7) / 8);
+#define WARP_LAUNCH(T, PL) qk_norm_rope_cache_warp_kernel<T, PL><<<blocks, 256, 0, stream>>>( \
+        static_cast<const T*>(q_in), static_cast<const T*>(k_in), static_cast<const T*>(v_in), q_stride, k_stride, \
+        v_stride, static_cast<T*>(q_out), static_cast<T*>(cache), slots, positions, q_weight, k_weight, cos_table, \
+        sin_table, table_positions, tokens, heads, kv_heads, page_tokens, num_pages, eps, status)
+    if (dtype == kF32) {
+      if (head_dim == 64) WARP_LAUNCH(float, 2); else if (head_dim == 128) WARP_LAUNCH(float, 4); else WARP_LAUNCH(float, 8);
+    } else if (dtype == kBF16) {
+      if (head_dim == 64) WARP_LAUNCH(__nv_bfloat16, 2); else if (head_dim == 128) WARP_LAUNCH(__nv_bfloat16, 4); else WARP_LAUNCH(__nv_bfloat16, 8);
+    } else {
+      return static_cast<int>(cudaErrorInvalidValue);
+    }
+#undef WARP_LAUNCH
+    return static_cast<int>(cudaGetLastError());
+  }
   int threads = 32;
   while (threads < head_dim && threads < 256) threads <<= 1;
   dim3 grid(tokens, heads + 2 * kv_heads);

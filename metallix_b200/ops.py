@@ -420,6 +420,11 @@ def gemm_simple(a: torch.Tensor, w: torch.Tensor, out_dtype: Optional[torch.dtyp
     return out
 
 
+# Up to this many rows "auto" takes the weight-streaming kernel; beyond it every
+# block would re-read too much of x and the library product is faster.
+SKINNY_ROWS = 16
+
+
 def gemm_skinny_supported(a: torch.Tensor, w: torch.Tensor) -> bool:
     """Whether the weight-streaming kernel takes a [m, k] times w [n, k]
     transposed: bfloat16, at most 64 rows, k a multiple of 32, rows on 16-byte
@@ -467,7 +472,7 @@ def gemm_bf16(a: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype = torch.b
     _need(out_dtype in (torch.bfloat16, torch.float32), "out_dtype must be bfloat16 or float32")
     if backend == "simple":
         return gemm_simple(a, w, out_dtype=out_dtype, out=out)
-    if backend in ("auto", "skinny") and a.shape[0] <= 64 and gemm_skinny_supported(a, w):
+    if (backend == "skinny" or (backend == "auto" and a.shape[0] <= SKINNY_ROWS)) and gemm_skinny_supported(a, w):
         return gemm_skinny(a, w, out_dtype=out_dtype, out=out)
     _need(backend != "skinny", "the weight-streaming kernel does not take this shape")
     if backend in ("auto", "tcgen05"):

@@ -28,7 +28,7 @@ class SwiGLU:
         self.intermediate_size = inter
 
     def forward(self, x: torch.Tensor, ctx: StepContext) -> torch.Tensor:
-        if (x.shape[0] <= 64 and self.gate_up.backend in ("auto", "skinny")
+        if (x.shape[0] <= ops.SKINNY_ROWS and self.gate_up.backend in ("auto", "skinny")
                 and ops.gemm_skinny_supported(x, self.gate_up.weight)):
             # A decode step: gate, up and the activation in one pass over the weights.
             return self.down.forward(ops.gemm_skinny(x, self.gate_up.weight, swiglu=True))
