@@ -208,6 +208,210 @@ paged_attention_decode_kernel(const T* __restrict__ q, const T* __restrict__ cac
   }
 }
 
+// ---------------------------------------------------------------------------
+// The bfloat16 split on the tensor cores. The scalar kernel above spends more
+// issue slots on unpacking, multiply-adds and shuffles than the memory system
+// needs time to deliver the keys; here the query heads of one key/value head
+// (at most 8) form the rows of a 16-row tensor-core tile, so q k^T and p v
+// cost a few hundred instructions per split. Each of the four warps takes 32
+// of the split's 128 keys with softmax statistics of its own; the warps'
+// results are merged in warp order, then written as one partial.
+__device__ __forceinline__ uint32_t decode_smem_address(const void* p) {
+  return static_cast<uint32_t>(__cvta_generic_to_shared(p));
+}
+__device__ __forceinline__ void decode_ldmatrix_x4(uint32_t (&r)[4], uint32_t address) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];\n"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(address));
+}
+__device__ __forceinline__ void decode_ldmatrix_x4_trans(uint32_t (&r)[4], uint32_t address) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0, %1, %2, %3}, [%4];\n"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(address));
+}
+__device__ __forceinline__ void decode_mma(float (&d)[4], uint32_t a0, uint32_t a2, uint32_t b0, uint32_t b1) {
+  // Rows 8..15 of the 16-row operand are zero: a1 = a3 = 0.
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};\n"
+               : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+               : "r"(a0), "r"(0u), "r"(a2), "r"(0u), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ float decode_exp2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;\n" : "=f"(y) : "f"(x));
+  return y;
+}
+template <int HD> __device__ __forceinline__ uint32_t decode_tile_offset(int row, int chunk) {
+  return static_cast<uint32_t>(row * (HD * 2) + ((chunk ^ (row & 7)) << 4));  // XOR swizzle, as in the prompt kernel
+}
+
+template <int HD>
+__global__ void __launch_bounds__(kDecodeThreads)
+paged_attention_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ cache,
+                                  float* __restrict__ partial, const int* __restrict__ block_tables,
+                                  int max_pages, const int* __restrict__ row_token,
+                                  const int* __restrict__ row_request, const int* __restrict__ positions,
+                                  int heads, int kv_heads, int page_tokens, int num_pages, int max_splits,
+                                  int window, float scale, int* status) {
+  constexpr int CHUNKS = HD / 8;
+  constexpr int TILE_BYTES = kSplitKeys * HD * 2;
+  extern __shared__ __align__(128) unsigned char mma_shared[];
+  unsigned char* sK = mma_shared;                 // [128][HD], swizzled
+  unsigned char* sV = sK + TILE_BYTES;            // [128][HD], swizzled
+  float* s_merge = reinterpret_cast<float*>(mma_shared);  // [4 warps][8 heads][HD + 2], over K once the scores exist
+
+  const int split = blockIdx.x, kv = blockIdx.y, row = blockIdx.z;
+  const int token = row_token[row];
+  if (token < 0) return;
+  const int pos = positions[token];
+  const int group = heads / kv_heads;  // <= 8
+  const int first_key = window > 0 ? max(0, pos - window + 1) : 0;
+  const int begin = max(split * kSplitKeys, first_key);
+  const int end = min((split + 1) * kSplitKeys, pos + 1);
+  if (begin >= end) return;
+  const int count = end - begin;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int g = lane >> 2, t = lane & 3;
+
+  // ---- one thread per key row: a block-table lookup, then the row's chunks
+  {
+    const int* table = block_tables + static_cast<size_t>(row_request[row]) * max_pages;
+    const size_t page_stride = static_cast<size_t>(2) * kv_heads * page_tokens * HD;
+    const size_t v_offset = static_cast<size_t>(kv_heads) * page_tokens * HD;
+    const int kk = tid;  // kSplitKeys == kDecodeThreads
+    const int key = begin + kk;
+    bool ok = kk < count;
+    int page = 0;
+    if (ok) {
+      page = table[key / page_tokens];
+      if (page < 0 || page >= num_pages) {
+        atomicOr(status, kStatusBadPage);
+        ok = false;
+        page = 0;
+      }
+    }
+    const __nv_bfloat16* src = cache + page * page_stride + static_cast<size_t>(kv) * page_tokens * HD +
+                               static_cast<size_t>(ok ? key % page_tokens : 0) * HD;
+    const int bytes = ok ? 16 : 0;
+#pragma unroll
+    for (int c = 0; c < CHUNKS; ++c)
+      decode_copy_async_16(sK + decode_tile_offset<HD>(kk, c), src + c * 8, bytes);
+    asm volatile("cp.async.commit_group;\n" ::);
+#pragma unroll
+    for (int c = 0; c < CHUNKS; ++c)
+      decode_copy_async_16(sV + decode_tile_offset<HD>(kk, c), src + v_offset + c * 8, bytes);
+    asm volatile("cp.async.commit_group;\n" ::);
+  }
+
+  // ---- the query heads of this key/value head as rows 0..group-1 of the 16-row operand
+  uint32_t qa0[HD / 16], qa2[HD / 16];
+  {
+    const __nv_bfloat16* qrow = q + (static_cast<size_t>(token) * heads + kv * group + (g < group ? g : 0)) * HD;
+#pragma unroll
+    for (int ks = 0; ks < HD / 16; ++ks) {
+      qa0[ks] = g < group ? *reinterpret_cast<const uint32_t*>(qrow + ks * 16 + 2 * t) : 0u;
+      qa2[ks] = g < group ? *reinterpret_cast<const uint32_t*>(qrow + ks * 16 + 8 + 2 * t) : 0u;
+    }
+  }
+  asm volatile("cp.async.wait_group 1;\n" ::);
+  __syncthreads();
+
+  // ---- scores of this warp's 32 keys
+  const int key_base = warp * 32;
+  float sc[4][4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) sc[i][0] = sc[i][1] = sc[i][2] = sc[i][3] = 0.0f;
+  if (key_base < count) {
+#pragma unroll
+    for (int ks = 0; ks < HD / 16; ++ks) {
+#pragma unroll
+      for (int nb = 0; nb < 2; ++nb) {
+        uint32_t kf[4];
+        const int krow = key_base + nb * 16 + (lane & 7) + (lane >> 4) * 8;
+        decode_ldmatrix_x4(kf, decode_smem_address(sK + decode_tile_offset<HD>(krow, ks * 2 + ((lane >> 3) & 1))));
+        decode_mma(sc[2 * nb], qa0[ks], qa2[ks], kf[0], kf[1]);
+        decode_mma(sc[2 * nb + 1], qa0[ks], qa2[ks], kf[2], kf[3]);
+      }
+    }
+  }
+  // Row g of the tile is query head g; this thread holds keys nb * 8 + 2t, 2t + 1.
+  const float scale_log2 = scale * 1.4426950408889634f;
+  float m_w = -INFINITY;
+#pragma unroll
+  for (int nb = 0; nb < 4; ++nb) {
+#pragma unroll
+    for (int j = 0; j < 2; ++j) {
+      const int kk = key_base + nb * 8 + 2 * t + j;
+      sc[nb][j] = kk < count ? sc[nb][j] * scale_log2 : -INFINITY;
+      m_w = fmaxf(m_w, sc[nb][j]);
+    }
+  }
+  m_w = fmaxf(m_w, __shfl_xor_sync(0xffffffffu, m_w, 1));
+  m_w = fmaxf(m_w, __shfl_xor_sync(0xffffffffu, m_w, 2));
+  const float ref = m_w == -INFINITY ? 0.0f : m_w;
+  float l_w = 0.0f;
+  uint32_t pa0[2], pa2[2];
+#pragma unroll
+  for (int nb = 0; nb < 4; ++nb) {
+    const float p0 = decode_exp2(sc[nb][0] - ref), p1 = decode_exp2(sc[nb][1] - ref);
+    l_w += p0 + p1;
+    __nv_bfloat162 packed = __floats2bfloat162_rn(p0, p1);
+    const uint32_t word = *reinterpret_cast<uint32_t*>(&packed);
+    if (nb & 1) pa2[nb >> 1] = word; else pa0[nb >> 1] = word;
+  }
+  l_w += __shfl_xor_sync(0xffffffffu, l_w, 1);
+  l_w += __shfl_xor_sync(0xffffffffu, l_w, 2);
+
+  asm volatile("cp.async.wait_group 0;\n" ::);
+  __syncthreads();
+
+  // ---- o = p v over this warp's 32 keys
+  float o[HD / 8][4];
+#pragma unroll
+  for (int i = 0; i < HD / 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.0f;
+  if (key_base < count) {
+#pragma unroll
+    for (int ks = 0; ks < 2; ++ks) {
+#pragma unroll
+      for (int nb = 0; nb < HD / 16; ++nb) {
+        uint32_t vf[4];
+        const int vrow = key_base + ks * 16 + (lane & 7) + ((lane >> 3) & 1) * 8;
+        decode_ldmatrix_x4_trans(vf, decode_smem_address(sV + decode_tile_offset<HD>(vrow, nb * 2 + (lane >> 4))));
+        decode_mma(o[2 * nb], pa0[ks], pa2[ks], vf[0], vf[1]);
+        decode_mma(o[2 * nb + 1], pa0[ks], pa2[ks], vf[2], vf[3]);
+      }
+    }
+  }
+  __syncthreads();  // every warp is done with K and V: the merge area lies over K
+
+  // ---- merge the four warps in warp order
+  if (g < group) {
+    float* mine = s_merge + (warp * 8 + g) * (HD + 2);
+#pragma unroll
+    for (int i = 0; i < HD / 8; ++i) {
+      mine[i * 8 + 2 * t] = o[i][0];
+      mine[i * 8 + 2 * t + 1] = o[i][1];
+    }
+    if (t == 0) { mine[HD] = m_w; mine[HD + 1] = l_w; }
+  }
+  __syncthreads();
+  for (int i = tid; i < group * HD; i += kDecodeThreads) {
+    const int h = i / HD, d = i - h * HD;
+    float m_all = -INFINITY;
+#pragma unroll
+    for (int wp = 0; wp < 4; ++wp) m_all = fmaxf(m_all, s_merge[(wp * 8 + h) * (HD + 2) + HD]);
+    float sum = 0.0f, l_all = 0.0f;
+#pragma unroll
+    for (int wp = 0; wp < 4; ++wp) {
+      const float* theirs = s_merge + (wp * 8 + h) * (HD + 2);
+      const float weight = decode_exp2(theirs[HD] - m_all);  // a warp without keys has m = -inf: weight 0
+      sum += weight * theirs[d];
+      l_all += weight * theirs[HD + 1];
+    }
+    const int head = kv * group + h;
+    float* dst = partial + ((static_cast<size_t>(row) * heads + head) * max_splits + split) * (HD + 2);
+    dst[d] = sum;
+    if (d == 0) { dst[HD] = m_all * 0.6931471805599453f; dst[HD + 1] = l_all; }  // the merge kernel works in natural units
+  }
+}
+
 // out[token, head, :] = sum_s exp(m_s - M) acc_s / sum_s exp(m_s - M) l_s over
 // the splits that hold keys of this token, in ascending order.
 template <typename T>
@@ -269,6 +473,31 @@ static int launch_decode(const void* q, const void* cache, void* out, float* par
   return static_cast<int>(cudaGetLastError());
 }
 
+template <int HD>
+static int launch_decode_mma(const void* q, const void* cache, void* out, float* partial,
+                             const int* block_tables, int max_pages, const int* row_token,
+                             const int* row_request, const int* positions, int rows, int heads,
+                             int kv_heads, int page_tokens, int num_pages, int max_splits, int window,
+                             float scale, int* status, cudaStream_t stream) {
+  static_assert(kSplitKeys == kDecodeThreads, "one thread per key row of a split");
+  static_assert(4 * 8 * (HD + 2) * sizeof(float) <= kSplitKeys * HD * 2, "the merge area must fit over the keys");
+  dim3 grid(max_splits, kv_heads, rows);
+  const int shared = 2 * kSplitKeys * HD * 2;
+  auto kernel = paged_attention_decode_mma_kernel<HD>;
+  cudaError_t attribute = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, shared);
+  if (attribute != cudaSuccess) return static_cast<int>(attribute);
+  kernel<<<grid, kDecodeThreads, shared, stream>>>(
+      static_cast<const __nv_bfloat16*>(q), static_cast<const __nv_bfloat16*>(cache), partial, block_tables,
+      max_pages, row_token, row_request, positions, heads, kv_heads, page_tokens, num_pages, max_splits,
+      window, scale, status);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return static_cast<int>(e);
+  dim3 merge_grid(rows, heads);
+  paged_attention_merge_kernel<__nv_bfloat16><<<merge_grid, HD >= 128 ? 128 : 64, 0, stream>>>(
+      partial, static_cast<__nv_bfloat16*>(out), row_token, positions, heads, HD, max_splits, window);
+  return static_cast<int>(cudaGetLastError());
+}
+
 }  // namespace mxb
 
 using namespace mxb;
@@ -304,9 +533,10 @@ MXB_API int mxb_paged_attention_decode(const void* q, const void* cache, void* o
   if (group == 2) return launch_decode<T, HD, 2>(ARGS);        \
   if (group <= 4) return launch_decode<T, HD, 4>(ARGS);        \
   return launch_decode<T, HD, 8>(ARGS);
+  if (dtype == kBF16 && (head_dim == 64 || head_dim == 128)) {
+    return head_dim == 64 ? launch_decode_mma<64>(ARGS) : launch_decode_mma<128>(ARGS);
+  }
   if (dtype == kBF16) {
-    if (head_dim == 64) { BY_GROUP(__nv_bfloat16, 64) }
-    if (head_dim == 128) { BY_GROUP(__nv_bfloat16, 128) }
     if (head_dim == 256) { BY_GROUP(__nv_bfloat16, 256) }
   } else {
     if (head_dim == 64) { BY_GROUP(float, 64) }

@@ -35,16 +35,19 @@ __device__ __forceinline__ void mma_16816(float (&d)[4], uint32_t a0, uint32_t a
 template <typename TOut> __device__ __forceinline__ void store_out(TOut* p, float v) { *p = from_float<TOut>(v); }
 
 // MB: 8-row blocks of x (M <= 8 * MB). SWIGLU: gate/up pairs, see above.
-template <int MB, bool SWIGLU, typename TOut>
+// WROWS: rows of W per block, 16 or 8. With 8 the upper half of the 16-row
+// operand is zero; narrow matrices then still spread over enough blocks to
+// keep every SM reading.
+template <int MB, bool SWIGLU, typename TOut, int WROWS>
 __global__ void __launch_bounds__(kSkinnyThreads)
 gemm_skinny_kernel(TOut* __restrict__ out, const __nv_bfloat16* __restrict__ x,
                    const __nv_bfloat16* __restrict__ w, int m, int n, int k, long long ldx, long long ldw,
                    long long ldo, int inter) {
   constexpr int SETS = SWIGLU ? 2 : 1;
-  __shared__ float s_part[kSkinnyWarps][kSkinnyRows][MB * 8 + 1];
+  __shared__ float s_part[kSkinnyWarps][WROWS][MB * 8 + 1];
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int g = lane >> 2, t = lane & 3;
-  const int n0 = blockIdx.x * kSkinnyRows;
+  const int n0 = blockIdx.x * WROWS;
   const int columns = SWIGLU ? inter : n;  // output columns
   // Rows of W this lane reads (clamped; rows beyond the end are masked at the store).
   const int row_lo = min(n0 + g, columns - 1), row_hi = min(n0 + g + 8, columns - 1);
@@ -76,7 +79,7 @@ gemm_skinny_kernel(TOut* __restrict__ out, const __nv_bfloat16* __restrict__ x,
 #pragma unroll
     for (int s = 0; s < SETS; ++s) {
       a_lo[s] = __ldg(reinterpret_cast<const uint4*>(w_lo[s] + k0));
-      a_hi[s] = __ldg(reinterpret_cast<const uint4*>(w_hi[s] + k0));
+      a_hi[s] = WROWS == 16 ? __ldg(reinterpret_cast<const uint4*>(w_hi[s] + k0)) : make_uint4(0u, 0u, 0u, 0u);
     }
     uint4 b[MB];
 #pragma unroll
@@ -91,7 +94,7 @@ gemm_skinny_kernel(TOut* __restrict__ out, const __nv_bfloat16* __restrict__ x,
       }
   }
   // c0, c1: W row g, x rows 8j + 2t, 8j + 2t + 1; c2, c3: W row g + 8.
-  constexpr int ITEMS = (kSkinnyRows * MB * 8 + kSkinnyThreads - 1) / kSkinnyThreads;
+  constexpr int ITEMS = (WROWS * MB * 8 + kSkinnyThreads - 1) / kSkinnyThreads;
   float sums[SETS][ITEMS];
 #pragma unroll
   for (int s = 0; s < SETS; ++s) {
@@ -100,14 +103,16 @@ gemm_skinny_kernel(TOut* __restrict__ out, const __nv_bfloat16* __restrict__ x,
     for (int j = 0; j < MB; ++j) {
       s_part[warp][g][j * 8 + 2 * t] = acc[s][j][0];
       s_part[warp][g][j * 8 + 2 * t + 1] = acc[s][j][1];
-      s_part[warp][g + 8][j * 8 + 2 * t] = acc[s][j][2];
-      s_part[warp][g + 8][j * 8 + 2 * t + 1] = acc[s][j][3];
+      if (WROWS == 16) {
+        s_part[warp][g + 8][j * 8 + 2 * t] = acc[s][j][2];
+        s_part[warp][g + 8][j * 8 + 2 * t + 1] = acc[s][j][3];
+      }
     }
     __syncthreads();
 #pragma unroll
     for (int item = 0; item < ITEMS; ++item) {
       const int i = tid + item * kSkinnyThreads;
-      const int r = i % kSkinnyRows, row_m = i / kSkinnyRows;
+      const int r = i % WROWS, row_m = i / WROWS;
       float sum = 0.0f;
       if (row_m < MB * 8) {
 #pragma unroll
@@ -119,7 +124,7 @@ gemm_skinny_kernel(TOut* __restrict__ out, const __nv_bfloat16* __restrict__ x,
 #pragma unroll
   for (int item = 0; item < ITEMS; ++item) {
     const int i = tid + item * kSkinnyThreads;
-    const int r = i % kSkinnyRows, row_m = i / kSkinnyRows;  // consecutive threads: consecutive columns
+    const int r = i % WROWS, row_m = i / WROWS;  // consecutive threads: consecutive columns
     const int column = n0 + r;
     if (row_m >= m || column >= columns) continue;
     float value = sums[0][item];
@@ -138,15 +143,15 @@ template <int MB, bool SWIGLU>
 static int launch_skinny(void* out, int out_dtype, const void* x, const void* w, int m, int n, int k,
                          long long ldx, long long ldw, long long ldo, int inter, cudaStream_t stream) {
   const int columns = SWIGLU ? inter : n;
-  dim3 grid((columns + kSkinnyRows - 1) / kSkinnyRows);
-  if (out_dtype == kBF16)
-    gemm_skinny_kernel<MB, SWIGLU, __nv_bfloat16><<<grid, kSkinnyThreads, 0, stream>>>(
-        static_cast<__nv_bfloat16*>(out), static_cast<const __nv_bfloat16*>(x),
-        static_cast<const __nv_bfloat16*>(w), m, n, k, ldx, ldw, ldo, inter);
-  else
-    gemm_skinny_kernel<MB, SWIGLU, float><<<grid, kSkinnyThreads, 0, stream>>>(
-        static_cast<float*>(out), static_cast<const __nv_bfloat16*>(x),
-        static_cast<const __nv_bfloat16*>(w), m, n, k, ldx, ldw, ldo, inter);
+  // Narrow outputs take 8 rows of W per block so that at least ~2 blocks per SM exist.
+  const bool narrow = columns <= 2048;
+  dim3 grid((columns + (narrow ? 8 : 16) - 1) / (narrow ? 8 : 16));
+#define GO(TOUT, WROWS) gemm_skinny_kernel<MB, SWIGLU, TOUT, WROWS><<<grid, kSkinnyThreads, 0, stream>>>( \
+      static_cast<TOUT*>(out), static_cast<const __nv_bfloat16*>(x), static_cast<const __nv_bfloat16*>(w), \
+      m, n, k, ldx, ldw, ldo, inter)
+  if (out_dtype == kBF16) { if (narrow) GO(__nv_bfloat16, 8); else GO(__nv_bfloat16, 16); }
+  else { if (narrow) GO(float, 8); else GO(float, 16); }
+#undef GO
   return static_cast<int>(cudaGetLastError());
 }
 
