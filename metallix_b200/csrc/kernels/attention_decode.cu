@@ -13,6 +13,7 @@
 // Replaces the reference's per-step gather of every row's whole context into
 // [rows, kv_heads, longest, head_dim] plus a masked SDPA call
 // (crates/models/qwen/src/forward/paged.rs:189-219, :1067-1076, :1216-1232).
+#include "async_copy.cuh"
 #include "common.cuh"
 
 namespace mxb {
@@ -238,8 +239,11 @@ __device__ __forceinline__ float decode_exp2(float x) {
   asm("ex2.approx.ftz.f32 %0, %1;\n" : "=f"(y) : "f"(x));
   return y;
 }
+// Key rows lie in shared memory as they lie in the cache, each followed by 16
+// bytes of padding: eight consecutive rows then start in eight different bank
+// groups, so ldmatrix meets no conflict, and a row is one bulk copy.
 template <int HD> __device__ __forceinline__ uint32_t decode_tile_offset(int row, int chunk) {
-  return static_cast<uint32_t>(row * (HD * 2) + ((chunk ^ (row & 7)) << 4));  // XOR swizzle, as in the prompt kernel
+  return static_cast<uint32_t>(row * (HD * 2 + 16) + (chunk << 4));
 }
 
 template <int HD>
@@ -250,13 +254,16 @@ paged_attention_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, const __n
                                   const int* __restrict__ row_request, const int* __restrict__ positions,
                                   int heads, int kv_heads, int page_tokens, int num_pages, int max_splits,
                                   int window, float scale, int* status) {
-  constexpr int CHUNKS = HD / 8;
-  constexpr int TILE_BYTES = kSplitKeys * HD * 2;
+  constexpr int ROW_BYTES = HD * 2;
+  constexpr int TILE_BYTES = kSplitKeys * (ROW_BYTES + 16);
   extern __shared__ __align__(128) unsigned char mma_shared[];
-  unsigned char* sK = mma_shared;                 // [128][HD], swizzled
-  unsigned char* sV = sK + TILE_BYTES;            // [128][HD], swizzled
+  unsigned char* sK = mma_shared;                 // [128] rows of HD values + 16 bytes
+  unsigned char* sV = sK + TILE_BYTES;            // the same for the values
   float* s_merge = reinterpret_cast<float*>(mma_shared);  // [4 warps][8 heads][HD + 2], over K once the scores exist
+  __shared__ __align__(8) uint64_t barriers[2];   // keys, values
 
+  chain_wait();
+  chain_release();
   const int split = blockIdx.x, kv = blockIdx.y, row = blockIdx.z;
   const int token = row_token[row];
   if (token < 0) return;
@@ -270,7 +277,15 @@ paged_attention_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, const __n
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int g = lane >> 2, t = lane & 3;
 
-  // ---- one thread per key row: a block-table lookup, then the row's chunks
+  // ---- one thread per key row: a block-table lookup, then one bulk copy for
+  // the row's keys and one for its values (the copy engine moves the bytes;
+  // the thread issues two instructions instead of one per 16 bytes).
+  if (tid == 0) {
+    barrier_init(&barriers[0], kDecodeThreads);
+    barrier_init(&barriers[1], kDecodeThreads);
+    barrier_init_fence();
+  }
+  __syncthreads();
   {
     const int* table = block_tables + static_cast<size_t>(row_request[row]) * max_pages;
     const size_t page_stride = static_cast<size_t>(2) * kv_heads * page_tokens * HD;
@@ -284,20 +299,24 @@ paged_attention_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, const __n
       if (page < 0 || page >= num_pages) {
         atomicOr(status, kStatusBadPage);
         ok = false;
-        page = 0;
       }
     }
-    const __nv_bfloat16* src = cache + page * page_stride + static_cast<size_t>(kv) * page_tokens * HD +
-                               static_cast<size_t>(ok ? key % page_tokens : 0) * HD;
-    const int bytes = ok ? 16 : 0;
+    if (ok) {
+      const __nv_bfloat16* src = cache + page * page_stride + static_cast<size_t>(kv) * page_tokens * HD +
+                                 static_cast<size_t>(key % page_tokens) * HD;
+      barrier_arrive_expect(&barriers[0], ROW_BYTES);
+      bulk_copy(sK + decode_tile_offset<HD>(kk, 0), src, ROW_BYTES, &barriers[0]);
+      barrier_arrive_expect(&barriers[1], ROW_BYTES);
+      bulk_copy(sV + decode_tile_offset<HD>(kk, 0), src + v_offset, ROW_BYTES, &barriers[1]);
+    } else {
+      // A row beyond the split's keys: zeros, written by the thread itself.
+      uint4* zk = reinterpret_cast<uint4*>(sK + decode_tile_offset<HD>(kk, 0));
+      uint4* zv = reinterpret_cast<uint4*>(sV + decode_tile_offset<HD>(kk, 0));
 #pragma unroll
-    for (int c = 0; c < CHUNKS; ++c)
-      decode_copy_async_16(sK + decode_tile_offset<HD>(kk, c), src + c * 8, bytes);
-    asm volatile("cp.async.commit_group;\n" ::);
-#pragma unroll
-    for (int c = 0; c < CHUNKS; ++c)
-      decode_copy_async_16(sV + decode_tile_offset<HD>(kk, c), src + v_offset + c * 8, bytes);
-    asm volatile("cp.async.commit_group;\n" ::);
+      for (int c = 0; c < ROW_BYTES / 16; ++c) zk[c] = zv[c] = make_uint4(0u, 0u, 0u, 0u);
+      barrier_arrive(&barriers[0]);
+      barrier_arrive(&barriers[1]);
+    }
   }
 
   // ---- the query heads of this key/value head as rows 0..group-1 of the 16-row operand
@@ -310,8 +329,8 @@ paged_attention_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, const __n
       qa2[ks] = g < group ? *reinterpret_cast<const uint32_t*>(qrow + ks * 16 + 8 + 2 * t) : 0u;
     }
   }
-  asm volatile("cp.async.wait_group 1;\n" ::);
-  __syncthreads();
+  const bool keys_landed = barrier_wait(&barriers[0], 0, status);
+  __syncthreads();  // also orders the zero rows written by other threads
 
   // ---- scores of this warp's 32 keys
   const int key_base = warp * 32;
@@ -359,8 +378,10 @@ paged_attention_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, const __n
   l_w += __shfl_xor_sync(0xffffffffu, l_w, 1);
   l_w += __shfl_xor_sync(0xffffffffu, l_w, 2);
 
-  asm volatile("cp.async.wait_group 0;\n" ::);
-  __syncthreads();
+  const bool values_landed = barrier_wait(&barriers[1], 0, status);
+  // One decision for the whole block; the status word says why, and both
+  // barriers were given their time, so no copy is left in flight.
+  if (__syncthreads_or(!keys_landed || !values_landed)) return;
 
   // ---- o = p v over this warp's 32 keys
   float o[HD / 8][4];
@@ -419,6 +440,8 @@ __global__ void paged_attention_merge_kernel(const float* __restrict__ partial, 
                                              const int* __restrict__ row_token,
                                              const int* __restrict__ positions, int heads, int head_dim,
                                              int max_splits, int window) {
+  chain_wait();
+  chain_release();
   const int row = blockIdx.x, head = blockIdx.y;
   const int token = row_token[row];
   if (token < 0) return;
@@ -482,20 +505,20 @@ static int launch_decode_mma(const void* q, const void* cache, void* out, float*
   static_assert(kSplitKeys == kDecodeThreads, "one thread per key row of a split");
   static_assert(4 * 8 * (HD + 2) * sizeof(float) <= kSplitKeys * HD * 2, "the merge area must fit over the keys");
   dim3 grid(max_splits, kv_heads, rows);
-  const int shared = 2 * kSplitKeys * HD * 2;
+  const int shared = 2 * kSplitKeys * (HD * 2 + 16);
   auto kernel = paged_attention_decode_mma_kernel<HD>;
   cudaError_t attribute = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, shared);
   if (attribute != cudaSuccess) return static_cast<int>(attribute);
-  kernel<<<grid, kDecodeThreads, shared, stream>>>(
-      static_cast<const __nv_bfloat16*>(q), static_cast<const __nv_bfloat16*>(cache), partial, block_tables,
-      max_pages, row_token, row_request, positions, heads, kv_heads, page_tokens, num_pages, max_splits,
-      window, scale, status);
-  cudaError_t e = cudaGetLastError();
+  cudaError_t e = launch_chained(kernel, grid, dim3(kDecodeThreads), shared, stream,
+                                 static_cast<const __nv_bfloat16*>(q), static_cast<const __nv_bfloat16*>(cache),
+                                 partial, block_tables, max_pages, row_token, row_request, positions, heads,
+                                 kv_heads, page_tokens, num_pages, max_splits, window, scale, status);
   if (e != cudaSuccess) return static_cast<int>(e);
   dim3 merge_grid(rows, heads);
-  paged_attention_merge_kernel<__nv_bfloat16><<<merge_grid, HD >= 128 ? 128 : 64, 0, stream>>>(
-      partial, static_cast<__nv_bfloat16*>(out), row_token, positions, heads, HD, max_splits, window);
-  return static_cast<int>(cudaGetLastError());
+  return static_cast<int>(launch_chained(paged_attention_merge_kernel<__nv_bfloat16>, merge_grid,
+                                         dim3(HD >= 128 ? 128 : 64), 0, stream, static_cast<const float*>(partial),
+                                         static_cast<__nv_bfloat16*>(out), row_token, positions, heads, HD,
+                                         max_splits, window));
 }
 
 }  // namespace mxb

@@ -61,6 +61,34 @@ __device__ __forceinline__ float block_sum(float v, float* scratch /* >= 33 floa
 
 inline int ceil_div(int a, int b) { return (a + b - 1) / b; }
 
+// Programmatic dependent launch: a kernel launched through launch_chained()
+// may start while its predecessor in the stream is still running. It calls
+// chain_wait() before it touches anything the predecessor writes (the wait
+// returns once the predecessor has finished and its writes are visible), and
+// chain_release() as early as it likes to let its own successor start. What
+// runs before the wait (index arithmetic, fetching weights no kernel writes)
+// overlaps the predecessor. Without the launch attribute both are no-ops.
+__device__ __forceinline__ void chain_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void chain_release() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+bool chained_launches();  // whether launch_chained() asks for the overlap (csrc/kernels/embed_norm.cu)
+
+template <typename... KernelArgs, typename... Args>
+inline cudaError_t launch_chained(void (*kernel)(KernelArgs...), dim3 grid, dim3 block, size_t shared,
+                                  cudaStream_t stream, Args... args) {
+  cudaLaunchConfig_t config = {};
+  config.gridDim = grid;
+  config.blockDim = block;
+  config.dynamicSmemBytes = shared;
+  config.stream = stream;
+  cudaLaunchAttribute attribute[1];
+  attribute[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attribute[0].val.programmaticStreamSerializationAllowed = 1;
+  config.attrs = attribute;
+  config.numAttrs = chained_launches() ? 1 : 0;
+  return cudaLaunchKernelEx(&config, kernel, static_cast<KernelArgs>(args)...);
+}
+
 }  // namespace mxb
 
 #define MXB_API extern "C" __attribute__((visibility("default")))

@@ -8,11 +8,16 @@
 
 namespace mxb {
 
+static bool g_chained_launches = false;
+bool chained_launches() { return g_chained_launches; }
+
 // out[t, :] = table[ids[t], :] as float32. A bad id sets the status word and
 // writes zeros.
 template <typename T>
 __global__ void embed_kernel(float* __restrict__ out, const T* __restrict__ table,
                              const int* __restrict__ ids, int hidden, int vocab, int* status) {
+  chain_wait();
+  chain_release();
   const int t = blockIdx.x;
   const int id = ids[t];
   const bool ok = id >= 0 && id < vocab;
@@ -88,6 +93,8 @@ __global__ void add_rmsnorm_vec4_kernel(float* __restrict__ x, const TDelta* __r
                                         TOut* __restrict__ y, const float* __restrict__ w,
                                         const int* __restrict__ rows_index, int size, float eps) {
   __shared__ float scratch[33];
+  chain_wait();
+  chain_release();
   const size_t src = rows_index ? static_cast<size_t>(rows_index[blockIdx.x]) : static_cast<size_t>(blockIdx.x);
   float* row = x + src * size;
   float sum = 0.0f;
@@ -114,6 +121,8 @@ static bool aligned16(const void* p) { return reinterpret_cast<uintptr_t>(p) % 1
 // x[r, :] += delta[r, :] alone (the last residual sum of a model).
 template <typename TDelta>
 __global__ void add_kernel(float* __restrict__ x, const TDelta* __restrict__ delta, size_t count) {
+  chain_wait();
+  chain_release();
   const size_t i = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x;
   if (i < count) x[i] += to_float(delta[i]);
 }
@@ -135,10 +144,10 @@ MXB_API int mxb_embed(float* out, const void* table, int table_dtype, const int*
   if (tokens <= 0) return 0;
   const int threads = hidden >= 256 ? 256 : 128;
   if (table_dtype == kF32)
-    embed_kernel<float><<<tokens, threads, 0, stream>>>(out, static_cast<const float*>(table), ids, hidden, vocab, status);
-  else
-    embed_kernel<__nv_bfloat16><<<tokens, threads, 0, stream>>>(out, static_cast<const __nv_bfloat16*>(table), ids, hidden, vocab, status);
-  return static_cast<int>(cudaGetLastError());
+    return static_cast<int>(launch_chained(embed_kernel<float>, dim3(tokens), dim3(threads), 0, stream, out,
+                                           static_cast<const float*>(table), ids, hidden, vocab, status));
+  return static_cast<int>(launch_chained(embed_kernel<__nv_bfloat16>, dim3(tokens), dim3(threads), 0, stream, out,
+                                         static_cast<const __nv_bfloat16*>(table), ids, hidden, vocab, status));
 }
 
 MXB_API int mxb_rmsnorm(void* y, int y_dtype, const void* x, int x_dtype, const float* w,
@@ -148,12 +157,12 @@ MXB_API int mxb_rmsnorm(void* y, int y_dtype, const void* x, int x_dtype, const 
     const int vec_threads = norm_threads(size / 4);
     float* xs = const_cast<float*>(static_cast<const float*>(x));  // read only: ADD is false
     if (y_dtype == kF32)
-      add_rmsnorm_vec4_kernel<float, float, false><<<rows, vec_threads, 0, stream>>>(xs, nullptr, static_cast<float*>(y), w, rows_index, size, eps);
-    else if (y_dtype == kBF16)
-      add_rmsnorm_vec4_kernel<float, __nv_bfloat16, false><<<rows, vec_threads, 0, stream>>>(xs, nullptr, static_cast<__nv_bfloat16*>(y), w, rows_index, size, eps);
-    else
-      return static_cast<int>(cudaErrorInvalidValue);
-    return static_cast<int>(cudaGetLastError());
+      return static_cast<int>(launch_chained(add_rmsnorm_vec4_kernel<float, float, false>, dim3(rows), dim3(vec_threads), 0,
+                                             stream, xs, static_cast<const float*>(nullptr), static_cast<float*>(y), w, rows_index, size, eps));
+    if (y_dtype == kBF16)
+      return static_cast<int>(launch_chained(add_rmsnorm_vec4_kernel<float, __nv_bfloat16, false>, dim3(rows), dim3(vec_threads), 0,
+                                             stream, xs, static_cast<const float*>(nullptr), static_cast<__nv_bfloat16*>(y), w, rows_index, size, eps));
+    return static_cast<int>(cudaErrorInvalidValue);
   }
   const int threads = norm_threads(size);
 #define LAUNCH(TI, TO) rmsnorm_kernel<TI, TO><<<rows, threads, 0, stream>>>( \
@@ -173,15 +182,14 @@ MXB_API int mxb_add_rmsnorm(float* x, const void* delta, int delta_dtype, void* 
   if (size % 4 == 0 && aligned16(x) && aligned16(y) && aligned16(w) && aligned16(delta) &&
       (delta_dtype == kF32 || size % 8 == 0)) {
     const int vec_threads = norm_threads(size / 4);
-#define VEC(TD, TO) add_rmsnorm_vec4_kernel<TD, TO, true><<<rows, vec_threads, 0, stream>>>( \
-        x, static_cast<const TD*>(delta), static_cast<TO*>(y), w, nullptr, size, eps)
+#define VEC(TD, TO) return static_cast<int>(launch_chained(add_rmsnorm_vec4_kernel<TD, TO, true>, dim3(rows), dim3(vec_threads), \
+        0, stream, x, static_cast<const TD*>(delta), static_cast<TO*>(y), w, static_cast<const int*>(nullptr), size, eps))
     if (delta_dtype == kF32 && y_dtype == kF32) VEC(float, float);
-    else if (delta_dtype == kBF16 && y_dtype == kBF16) VEC(__nv_bfloat16, __nv_bfloat16);
-    else if (delta_dtype == kF32 && y_dtype == kBF16) VEC(float, __nv_bfloat16);
-    else if (delta_dtype == kBF16 && y_dtype == kF32) VEC(__nv_bfloat16, float);
-    else return static_cast<int>(cudaErrorInvalidValue);
+    if (delta_dtype == kBF16 && y_dtype == kBF16) VEC(__nv_bfloat16, __nv_bfloat16);
+    if (delta_dtype == kF32 && y_dtype == kBF16) VEC(float, __nv_bfloat16);
+    if (delta_dtype == kBF16 && y_dtype == kF32) VEC(__nv_bfloat16, float);
 #undef VEC
-    return static_cast<int>(cudaGetLastError());
+    return static_cast<int>(cudaErrorInvalidValue);
   }
   const int threads = norm_threads(size);
 #define LAUNCH(TD, TO) add_rmsnorm_kernel<TD, TO><<<rows, threads, 0, stream>>>( \
@@ -201,8 +209,12 @@ MXB_API int mxb_add(float* x, const void* delta, int delta_dtype, long long coun
   const int threads = 256;
   const unsigned blocks = static_cast<unsigned>((count + threads - 1) / threads);
   if (delta_dtype == kF32)
-    add_kernel<float><<<blocks, threads, 0, stream>>>(x, static_cast<const float*>(delta), static_cast<size_t>(count));
-  else
-    add_kernel<__nv_bfloat16><<<blocks, threads, 0, stream>>>(x, static_cast<const __nv_bfloat16*>(delta), static_cast<size_t>(count));
-  return static_cast<int>(cudaGetLastError());
+    return static_cast<int>(launch_chained(add_kernel<float>, dim3(blocks), dim3(threads), 0, stream, x,
+                                           static_cast<const float*>(delta), static_cast<size_t>(count)));
+  return static_cast<int>(launch_chained(add_kernel<__nv_bfloat16>, dim3(blocks), dim3(threads), 0, stream, x,
+                                         static_cast<const __nv_bfloat16*>(delta), static_cast<size_t>(count)));
 }
+
+// Turns the overlap of consecutive kernels (programmatic dependent launch) on
+// or off for every kernel of this library that supports it.
+MXB_API void mxb_set_chained_launches(int enabled) { mxb::g_chained_launches = enabled != 0; }

@@ -22,7 +22,8 @@ namespace mxb {
 
 constexpr int kSkinnyWarps = 8;
 constexpr int kSkinnyThreads = kSkinnyWarps * 32;
-constexpr int kSkinnyRows = 16;   // rows of W per block
+constexpr int kSkinnyRows = 16;   // rows of W per block (8 for narrow outputs)
+static_assert(kSkinnyRows == 16, "the tensor-core tile has 16 rows");
 constexpr int kSkinnySlice = 32;  // k per warp iteration
 
 __device__ __forceinline__ void mma_16816(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
@@ -72,8 +73,44 @@ gemm_skinny_kernel(TOut* __restrict__ out, const __nv_bfloat16* __restrict__ x,
     for (int j = 0; j < MB; ++j) acc[s][j][0] = acc[s][j][1] = acc[s][j][2] = acc[s][j][3] = 0.0f;
 
   const int slices = k / kSkinnySlice;
+  // The weights are never written by a kernel, so this warp's first slices of
+  // W are fetched before waiting for the kernel that produces x.
+  constexpr int PRE = MB <= 2 ? 4 : 0;
+  uint4 pre_lo[PRE > 0 ? PRE : 1][SETS], pre_hi[PRE > 0 ? PRE : 1][SETS];
+  chain_release();
+#pragma unroll
+  for (int i = 0; i < PRE; ++i) {
+    const int slice = warp + i * kSkinnyWarps;
+    if (slice < slices) {
+#pragma unroll
+      for (int s = 0; s < SETS; ++s) {
+        pre_lo[i][s] = __ldg(reinterpret_cast<const uint4*>(w_lo[s] + slice * kSkinnySlice));
+        pre_hi[i][s] = WROWS == 16 ? __ldg(reinterpret_cast<const uint4*>(w_hi[s] + slice * kSkinnySlice))
+                                   : make_uint4(0u, 0u, 0u, 0u);
+      }
+    }
+  }
+  chain_wait();
+#pragma unroll
+  for (int i = 0; i < PRE; ++i) {
+    const int slice = warp + i * kSkinnyWarps;
+    if (slice < slices) {
+      const int k0 = slice * kSkinnySlice;
+      uint4 b[MB];
+#pragma unroll
+      for (int j = 0; j < MB; ++j)
+        b[j] = x_ok[j] ? *reinterpret_cast<const uint4*>(x_row[j] + k0) : make_uint4(0u, 0u, 0u, 0u);
+#pragma unroll
+      for (int s = 0; s < SETS; ++s)
+#pragma unroll
+        for (int j = 0; j < MB; ++j) {
+          mma_16816(acc[s][j], pre_lo[i][s].x, pre_hi[i][s].x, pre_lo[i][s].y, pre_hi[i][s].y, b[j].x, b[j].y);
+          mma_16816(acc[s][j], pre_lo[i][s].z, pre_hi[i][s].z, pre_lo[i][s].w, pre_hi[i][s].w, b[j].z, b[j].w);
+        }
+    }
+  }
 #pragma unroll 4
-  for (int slice = warp; slice < slices; slice += kSkinnyWarps) {
+  for (int slice = warp + PRE * kSkinnyWarps; slice < slices; slice += kSkinnyWarps) {
     const int k0 = slice * kSkinnySlice;
     uint4 a_lo[SETS], a_hi[SETS];
 #pragma unroll
@@ -146,13 +183,12 @@ static int launch_skinny(void* out, int out_dtype, const void* x, const void* w,
   // Narrow outputs take 8 rows of W per block so that at least ~2 blocks per SM exist.
   const bool narrow = columns <= 2048;
   dim3 grid((columns + (narrow ? 8 : 16) - 1) / (narrow ? 8 : 16));
-#define GO(TOUT, WROWS) gemm_skinny_kernel<MB, SWIGLU, TOUT, WROWS><<<grid, kSkinnyThreads, 0, stream>>>( \
-      static_cast<TOUT*>(out), static_cast<const __nv_bfloat16*>(x), static_cast<const __nv_bfloat16*>(w), \
-      m, n, k, ldx, ldw, ldo, inter)
+#define GO(TOUT, WROWS) return static_cast<int>(launch_chained(gemm_skinny_kernel<MB, SWIGLU, TOUT, WROWS>, grid, \
+      dim3(kSkinnyThreads), 0, stream, static_cast<TOUT*>(out), static_cast<const __nv_bfloat16*>(x), \
+      static_cast<const __nv_bfloat16*>(w), m, n, k, ldx, ldw, ldo, inter))
   if (out_dtype == kBF16) { if (narrow) GO(__nv_bfloat16, 8); else GO(__nv_bfloat16, 16); }
   else { if (narrow) GO(float, 8); else GO(float, 16); }
 #undef GO
-  return static_cast<int>(cudaGetLastError());
 }
 
 }  // namespace mxb

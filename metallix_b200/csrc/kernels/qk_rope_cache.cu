@@ -107,6 +107,8 @@ qk_norm_rope_cache_warp_kernel(
     int tokens, int heads, int kv_heads, int page_tokens, int num_pages, float eps, int* status) {
   constexpr int HD = PER_LANE * 32;
   constexpr int HALF = HD / 2;
+  chain_wait();
+  chain_release();
   const int lane = threadIdx.x & 31;
   const int per_token = heads + 2 * kv_heads;
   const long long item = static_cast<long long>(blockIdx.x) * 8 + (threadIdx.x >> 5);
@@ -187,7 +189,8 @@ MXB_API int mxb_qk_norm_rope_cache(
   if ((head_dim == 64 || head_dim == 128 || head_dim == 256) && (cos_table == nullptr || rotary_dim == head_dim)) {
     const long long items = static_cast<long long>(tokens) * (heads + 2 * kv_heads);
     const unsigned blocks = static_cast<unsigned>((items + 7) / 8);
-#define WARP_LAUNCH(T, PL) qk_norm_rope_cache_warp_kernel<T, PL><<<blocks, 256, 0, stream>>>( \
+    cudaError_t launch_status = cudaSuccess;
+#define WARP_LAUNCH(T, PL) launch_status = launch_chained(qk_norm_rope_cache_warp_kernel<T, PL>, dim3(blocks), dim3(256), 0, stream, \
         static_cast<const T*>(q_in), static_cast<const T*>(k_in), static_cast<const T*>(v_in), q_stride, k_stride, \
         v_stride, static_cast<T*>(q_out), static_cast<T*>(cache), slots, positions, q_weight, k_weight, cos_table, \
         sin_table, table_positions, tokens, heads, kv_heads, page_tokens, num_pages, eps, status)
@@ -199,7 +202,7 @@ MXB_API int mxb_qk_norm_rope_cache(
       return static_cast<int>(cudaErrorInvalidValue);
     }
 #undef WARP_LAUNCH
-    return static_cast<int>(cudaGetLastError());
+    return static_cast<int>(launch_status);
   }
   int threads = 32;
   while (threads < head_dim && threads < 256) threads <<= 1;

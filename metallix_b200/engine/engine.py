@@ -63,8 +63,9 @@ class Engine:
                  page_tokens: int = 16, num_pages: Optional[int] = None,
                  max_tokens: Optional[int] = None, max_requests: int = 64,
                  max_context: Optional[int] = None, device="cuda:0", gemm_backend: str = "auto",
-                 spec=None, cuda_graphs: bool = True):
+                 spec=None, cuda_graphs: bool = True, chained_launches: bool = True):
         ops.require_cuda()
+        ops.set_chained_launches(chained_launches)
         self.config = config
         self.device = torch.device(device)
         self.dtype = resolve_dtype(dtype)

@@ -49,6 +49,7 @@ _SIGNATURES = {
     "mxb_argmax": [_P, _L, _I, _I, _P, _P, _P],
     "mxb_sample_icdf": [_P, _L, _I, _I, _P, _P, _P, _P, _P, _P, _P, _P],
     "mxb_sample_race": [_P, _L, _I, _I, _P, _P, _P, _P, _P, _P, _P],
+    "mxb_set_chained_launches": [_I],
     "mxb_nucleus_mask": [_P, _L, _I, _I, _P, _P, _P, _P, _P, _P],
 }
 _functions = {}
@@ -118,6 +119,13 @@ def require_cuda() -> None:
     if not torch.cuda.is_available():
         raise KernelError("no CUDA device: metallix_b200 runs on a B200 only and has no CPU path")
     build.kernels()
+
+
+def set_chained_launches(enabled: bool) -> None:
+    """Lets consecutive kernels of this library overlap (programmatic dependent
+    launch): a kernel may start, and fetch weights, while its predecessor is
+    still running, and waits for the predecessor before it reads its output."""
+    _fn("mxb_set_chained_launches")(1 if enabled else 0)
 
 
 def status_word(device) -> torch.Tensor:
