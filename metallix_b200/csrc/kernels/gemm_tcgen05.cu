@@ -1,0 +1,332 @@
+// C[M, N] = A[M, K] * W[N, K]^T in bfloat16 on the fifth-generation tensor
+// cores: tcgen05.mma issued by one thread, operands staged in shared memory by
+// TMA (cp.async.bulk.tensor with the 128-byte swizzle), the float32
+// accumulator of a 128 x BN tile in tensor memory, read back with tcgen05.ld
+// for the epilogue.
+//
+// One block computes one 128 x BN tile. Warp 0 feeds the pipeline (one lane
+// issues the TMA loads), warp 1 owns tensor memory and issues the MMAs, warps
+// 2..5 run the epilogue: plain store (bfloat16 or float32), or SwiGLU, where
+// the B tile is made of 128 gate rows and the 128 up rows of the same columns
+// and the block writes silu(gate) * up, so gate and up never reach memory
+// (the reference does this as two products and three element-wise passes,
+// crates/models/qwen/src/forward.rs:1904-1917).
+//
+// Every wait on a barrier is bounded: if it runs out, the status word gets a
+// bit, the block stops issuing work, frees its tensor memory and leaves.
+#include <cuda.h>
+
+#include <map>
+#include <mutex>
+#include <tuple>
+
+#include "async_copy.cuh"
+#include "common.cuh"
+
+namespace mxb {
+
+constexpr int kTcM = 128;     // rows of a tile
+constexpr int kTcK = 64;      // k per stage: 64 bfloat16 = one 128-byte swizzle row
+constexpr int kTcThreads = 192;
+
+enum TcEpilogue : int { kTcStoreBf16 = 0, kTcStoreF32 = 1, kTcSwiGLU = 2 };
+
+template <int BN> struct TcConfig {
+  static constexpr int kStageBytes = (kTcM + BN) * kTcK * 2;
+  static constexpr int kStages = BN >= 256 ? 4 : (BN >= 128 ? 6 : 8);
+  static constexpr int kSharedBytes = kStages * kStageBytes + 1024;  // + room to align the tiles to 1024 bytes
+};
+
+__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, int x, int y, uint64_t* barrier) {
+  asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];\n"
+               ::"r"(shared_address(dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(shared_address(barrier)),
+                 "r"(x), "r"(y) : "memory");
+}
+
+// Shared-memory matrix descriptor of a K-major tile with the 128-byte swizzle:
+// rows of 128 bytes, groups of 8 rows 1024 bytes apart.
+__device__ __forceinline__ uint64_t tc_smem_descriptor(uint32_t address) {
+  uint64_t d = 0;
+  d |= static_cast<uint64_t>((address >> 4) & 0x3FFF);  // start address, 16-byte units
+  d |= static_cast<uint64_t>(1) << 16;                   // leading byte offset (unused with a swizzle)
+  d |= static_cast<uint64_t>(1024 >> 4) << 32;           // stride between 8-row groups
+  d |= static_cast<uint64_t>(1) << 46;                   // descriptor version of sm_100
+  d |= static_cast<uint64_t>(2) << 61;                   // 128-byte swizzle
+  return d;
+}
+
+// Instruction descriptor: bfloat16 x bfloat16 -> float32, both operands K-major.
+__host__ __device__ constexpr uint32_t tc_instruction_descriptor(int m, int n) {
+  return (1u << 4) | (1u << 7) | (1u << 10) | (static_cast<uint32_t>(n >> 3) << 17) |
+         (static_cast<uint32_t>(m >> 4) << 24);
+}
+
+__device__ __forceinline__ void tc_mma(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc,
+                                       uint32_t accumulate) {
+  asm volatile(
+      "{\n"
+      ".reg .pred p;\n"
+      "setp.ne.b32 p, %4, 0;\n"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%5, %5, %5, %5}, p;\n"
+      "}\n"
+      ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate), "r"(0u) : "memory");
+}
+
+// The barrier gets one arrival when every MMA issued so far has finished.
+__device__ __forceinline__ void tc_commit(uint64_t* barrier) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n"
+               ::"r"(shared_address(barrier)) : "memory");
+}
+
+__device__ __forceinline__ void tc_load_32(uint32_t taddr, uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];\n"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+        "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+        "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr) : "memory");
+  asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
+}
+
+// EPI: see TcEpilogue. For kTcSwiGLU n is the output width (inter) and map_b
+// covers the [2 * inter, k] weight; BN must be 256.
+template <int BN, int EPI>
+__global__ void __launch_bounds__(kTcThreads)
+gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                    void* __restrict__ out, int m, int n, int k, long long ldo, int* status) {
+  using Config = TcConfig<BN>;
+  constexpr int STAGES = Config::kStages;
+  constexpr int OUT_COLUMNS = EPI == kTcSwiGLU ? BN / 2 : BN;  // output columns of a tile
+  extern __shared__ unsigned char tc_shared_raw[];
+  __shared__ __align__(8) uint64_t full_barrier[STAGES];
+  __shared__ __align__(8) uint64_t empty_barrier[STAGES];
+  __shared__ __align__(8) uint64_t accumulator_barrier;
+  __shared__ uint32_t tmem_base_slot;
+  __shared__ int failed;
+
+  unsigned char* tiles = tc_shared_raw + ((1024 - (shared_address(tc_shared_raw) & 1023)) & 1023);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int m0 = blockIdx.y * kTcM;
+  const int n0 = blockIdx.x * OUT_COLUMNS;
+  const int k_blocks = (k + kTcK - 1) / kTcK;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      barrier_init(&full_barrier[s], 1);
+      barrier_init(&empty_barrier[s], 1);
+    }
+    barrier_init(&accumulator_barrier, 1);
+    barrier_init_fence();
+    failed = 0;
+  }
+  if (warp == 1) {  // one warp allocates the accumulator's columns of tensor memory
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n"
+                 ::"r"(shared_address(&tmem_base_slot)), "r"(BN) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::: "memory");
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
+  __syncthreads();
+  asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+  const uint32_t tmem_base = tmem_base_slot;
+
+  if (warp == 0) {
+    // ---- producer: TMA loads of the A and B tiles of every k block
+    if (lane == 0) {
+      for (int kb = 0; kb < k_blocks; ++kb) {
+        const int stage = kb % STAGES;
+        const uint32_t parity = (kb / STAGES) & 1;
+        if (!barrier_wait(&empty_barrier[stage], parity ^ 1, status)) { failed = 1; break; }
+        unsigned char* a_tile = tiles + stage * Config::kStageBytes;
+        unsigned char* b_tile = a_tile + kTcM * kTcK * 2;
+        barrier_arrive_expect(&full_barrier[stage], Config::kStageBytes);
+        tma_load_2d(a_tile, &map_a, kb * kTcK, m0, &full_barrier[stage]);
+        if (EPI == kTcSwiGLU) {
+          tma_load_2d(b_tile, &map_b, kb * kTcK, n0, &full_barrier[stage]);                            // gate rows
+          tma_load_2d(b_tile + (BN / 2) * kTcK * 2, &map_b, kb * kTcK, n + n0, &full_barrier[stage]);  // up rows
+        } else {
+          tma_load_2d(b_tile, &map_b, kb * kTcK, n0, &full_barrier[stage]);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ---- one thread issues every MMA; completion frees the stage
+    if (lane == 0) {
+      constexpr uint32_t idesc = tc_instruction_descriptor(kTcM, BN);
+      bool ok = true;
+      for (int kb = 0; kb < k_blocks && ok; ++kb) {
+        const int stage = kb % STAGES;
+        const uint32_t parity = (kb / STAGES) & 1;
+        if (!barrier_wait(&full_barrier[stage], parity, status)) { failed = 1; ok = false; break; }
+        asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+        const uint32_t a_address = shared_address(tiles + stage * Config::kStageBytes);
+        const uint32_t b_address = a_address + kTcM * kTcK * 2;
+#pragma unroll
+        for (int kk = 0; kk < kTcK / 16; ++kk) {  // 16 k per instruction: 32 bytes further along the swizzled row
+          tc_mma(tmem_base, tc_smem_descriptor(a_address + kk * 32), tc_smem_descriptor(b_address + kk * 32),
+                 idesc, (kb > 0 || kk > 0) ? 1u : 0u);
+        }
+        tc_commit(&empty_barrier[stage]);
+      }
+      tc_commit(&accumulator_barrier);  // arrives when the whole accumulator is final
+    }
+  } else {
+    // ---- epilogue: warp w reads the 32 accumulator rows (lanes) (w % 4) * 32 ...
+    const int lane_base = (warp & 3) * 32;
+    const bool landed = barrier_wait(&accumulator_barrier, 0, status);
+    asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+    const int row = m0 + lane_base + lane;
+    if (landed && !failed) {
+#pragma unroll 1
+      for (int c = 0; c < OUT_COLUMNS; c += 32) {
+        uint32_t acc[32];
+        tc_load_32(tmem_base + (static_cast<uint32_t>(lane_base) << 16) + c, acc);
+        float values[32];
+        if (EPI == kTcSwiGLU) {
+          uint32_t up[32];
+          tc_load_32(tmem_base + (static_cast<uint32_t>(lane_base) << 16) + BN / 2 + c, up);
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            // gate and up take the rounding to bfloat16 they would get on their way through memory
+            const float gate = to_float(from_float<__nv_bfloat16>(__uint_as_float(acc[i])));
+            const float u = to_float(from_float<__nv_bfloat16>(__uint_as_float(up[i])));
+            values[i] = (1.0f / (1.0f + expf(-gate))) * gate * u;
+          }
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) values[i] = __uint_as_float(acc[i]);
+        }
+        if (row < m) {
+          const int column = n0 + c;
+          if (EPI == kTcStoreF32) {
+            float* dst = static_cast<float*>(out) + static_cast<long long>(row) * ldo + column;
+            if (column + 32 <= n && (reinterpret_cast<uintptr_t>(dst) & 15) == 0) {
+#pragma unroll
+              for (int i = 0; i < 32; i += 4)
+                *reinterpret_cast<float4*>(dst + i) = make_float4(values[i], values[i + 1], values[i + 2], values[i + 3]);
+            } else {
+              for (int i = 0; i < 32; ++i)
+                if (column + i < n) dst[i] = values[i];
+            }
+          } else {
+            __nv_bfloat16* dst = static_cast<__nv_bfloat16*>(out) + static_cast<long long>(row) * ldo + column;
+            if (column + 32 <= n && (reinterpret_cast<uintptr_t>(dst) & 15) == 0) {
+#pragma unroll
+              for (int i = 0; i < 32; i += 8) {
+                uint32_t packed[4];
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                  __nv_bfloat162 pair = __floats2bfloat162_rn(values[i + 2 * j], values[i + 2 * j + 1]);
+                  packed[j] = *reinterpret_cast<uint32_t*>(&pair);
+                }
+                *reinterpret_cast<uint4*>(dst + i) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+              }
+            } else {
+              for (int i = 0; i < 32; ++i)
+                if (column + i < n) dst[i] = from_float<__nv_bfloat16>(values[i]);
+            }
+          }
+        }
+      }
+    }
+  }
+
+  asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
+  __syncthreads();
+  if (failed && threadIdx.x == 0) {
+    // A wait ran out somewhere. Give loads that may still be in flight a
+    // millisecond before the block's shared memory goes back.
+    for (int i = 0; i < 1000; ++i) __nanosleep(1000);
+  }
+  __syncthreads();
+  if (warp == 1) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_base), "r"(BN) : "memory");
+  }
+}
+
+// ------------------------------------------------------------------ host side
+typedef CUresult (*EncodeTiled)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiled encode_tiled() {
+  static EncodeTiled function = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* symbol = nullptr;
+    cudaDriverEntryPointQueryResult result;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &symbol, cudaEnableDefault, &result) == cudaSuccess &&
+        result == cudaDriverEntryPointSuccess)
+      function = reinterpret_cast<EncodeTiled>(symbol);
+  });
+  return function;
+}
+
+// A [rows, k] bfloat16 matrix with row stride ld (elements), read in boxes of
+// box_rows x 64 with the 128-byte swizzle; what lies outside reads as zero.
+static bool make_map(CUtensorMap* map, const void* base, int rows, int k, long long ld, int box_rows) {
+  EncodeTiled encode = encode_tiled();
+  if (encode == nullptr) return false;
+  const cuuint64_t dims[2] = {static_cast<cuuint64_t>(k), static_cast<cuuint64_t>(rows)};
+  const cuuint64_t strides[1] = {static_cast<cuuint64_t>(ld) * 2};
+  const cuuint32_t box[2] = {static_cast<cuuint32_t>(kTcK), static_cast<cuuint32_t>(box_rows)};
+  const cuuint32_t element_strides[2] = {1, 1};
+  return encode(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box,
+                element_strides, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+template <int BN, int EPI>
+static int launch_tc(const CUtensorMap& map_a, const CUtensorMap& map_b, void* out, int m, int n, int k,
+                     long long ldo, int* status, cudaStream_t stream) {
+  using Config = TcConfig<BN>;
+  auto kernel = gemm_tcgen05_kernel<BN, EPI>;
+  cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Config::kSharedBytes);
+  if (e != cudaSuccess) return static_cast<int>(e);
+  constexpr int out_columns = EPI == kTcSwiGLU ? BN / 2 : BN;
+  dim3 grid((n + out_columns - 1) / out_columns, (m + kTcM - 1) / kTcM);
+  kernel<<<grid, kTcThreads, Config::kSharedBytes, stream>>>(map_a, map_b, out, m, n, k, ldo, status);
+  return static_cast<int>(cudaGetLastError());
+}
+
+}  // namespace mxb
+
+using namespace mxb;
+
+// Shapes the kernel takes: k a multiple of 8 (row strides on 16-byte
+// boundaries), rows of a and w contiguous, bases 16-byte aligned.
+MXB_API int mxb_gemm_tcgen05_supported(int m, int n, int k, long long lda, long long ldw) {
+  return m >= 1 && n >= 1 && k >= 8 && k % 8 == 0 && lda % 8 == 0 && ldw % 8 == 0 ? 1 : 0;
+}
+
+// epilogue: 0 bfloat16 out[m, n], 1 float32 out[m, n], 2 SwiGLU: w is
+// [2 * n, k] (gate rows, then up rows) and out is bfloat16 [m, n].
+MXB_API int mxb_gemm_tcgen05(void* out, const void* a, const void* w, int m, int n, int k, long long lda,
+                             long long ldw, long long ldo, int epilogue, int* status, cudaStream_t stream) {
+  if (!mxb_gemm_tcgen05_supported(m, n, k, lda, ldw)) return static_cast<int>(cudaErrorInvalidValue);
+  if ((reinterpret_cast<uintptr_t>(a) & 15) || (reinterpret_cast<uintptr_t>(w) & 15)) return static_cast<int>(cudaErrorInvalidValue);
+  const int w_rows = epilogue == kTcSwiGLU ? 2 * n : n;
+  // Narrow outputs take narrower tiles so that the grid still covers the GPU.
+  const int m_tiles = (m + kTcM - 1) / kTcM;
+  int bn = 256;
+  if (epilogue != kTcSwiGLU) {
+    if (m_tiles * ((n + 255) / 256) < 148) bn = 128;
+    if (bn == 128 && m_tiles * ((n + 127) / 128) < 148) bn = 64;
+  }
+  CUtensorMap map_a, map_b;
+  const int b_box = epilogue == kTcSwiGLU ? bn / 2 : bn;
+  if (!make_map(&map_a, a, m, k, lda, kTcM) || !make_map(&map_b, w, w_rows, k, ldw, b_box))
+    return static_cast<int>(cudaErrorInvalidValue);
+  if (epilogue == kTcSwiGLU) return launch_tc<256, kTcSwiGLU>(map_a, map_b, out, m, n, k, ldo, status, stream);
+  if (epilogue == kTcStoreF32) {
+    if (bn == 256) return launch_tc<256, kTcStoreF32>(map_a, map_b, out, m, n, k, ldo, status, stream);
+    if (bn == 128) return launch_tc<128, kTcStoreF32>(map_a, map_b, out, m, n, k, ldo, status, stream);
+    return launch_tc<64, kTcStoreF32>(map_a, map_b, out, m, n, k, ldo, status, stream);
+  }
+  if (epilogue != kTcStoreBf16) return static_cast<int>(cudaErrorInvalidValue);
+  if (bn == 256) return launch_tc<256, kTcStoreBf16>(map_a, map_b, out, m, n, k, ldo, status, stream);
+  if (bn == 128) return launch_tc<128, kTcStoreBf16>(map_a, map_b, out, m, n, k, ldo, status, stream);
+  return launch_tc<64, kTcStoreBf16>(map_a, map_b, out, m, n, k, ldo, status, stream);
+}
