@@ -170,7 +170,7 @@ gemm_skinny_kernel(TOut* __restrict__ out, const __nv_bfloat16* __restrict__ x,
       // keep the same rounding points so both paths agree.
       const float gate = to_float(from_float<__nv_bfloat16>(sums[0][item]));
       const float up = to_float(from_float<__nv_bfloat16>(sums[SETS - 1][item]));
-      value = (1.0f / (1.0f + expf(-gate))) * gate * up;
+      value = __fdividef(gate, 1.0f + __expf(-gate)) * up;  // the result is rounded to bfloat16 anyway
     }
     store_out(out + static_cast<long long>(row_m) * ldo + column, value);
   }

@@ -31,9 +31,9 @@ constexpr int kTcThreads = 192;
 
 enum TcEpilogue : int { kTcStoreBf16 = 0, kTcStoreF32 = 1, kTcSwiGLU = 2 };
 
-template <int BN> struct TcConfig {
+template <int BN, int STAGES_> struct TcConfig {
   static constexpr int kStageBytes = (kTcM + BN) * kTcK * 2;
-  static constexpr int kStages = BN >= 256 ? 4 : (BN >= 128 ? 6 : 8);
+  static constexpr int kStages = STAGES_;
   static constexpr int kSharedBytes = kStages * kStageBytes + 1024;  // + room to align the tiles to 1024 bytes
 };
 
@@ -93,24 +93,32 @@ __device__ __forceinline__ void tc_load_32(uint32_t taddr, uint32_t (&r)[32]) {
 
 // EPI: see TcEpilogue. For kTcSwiGLU n is the output width (inter) and map_b
 // covers the [2 * inter, k] weight; BN must be 256.
-template <int BN, int EPI>
+//
+// The kernel is persistent: a block walks over tiles (tile, tile + gridDim.x,
+// ...), with two accumulators in tensor memory, so the epilogue of one tile
+// runs while the MMAs of the next fill the other accumulator and the TMA
+// loads run ahead of both. Tiles are numbered with the row tile fastest:
+// blocks working side by side share a tile of W.
+template <int BN, int EPI, int STAGES_>
 __global__ void __launch_bounds__(kTcThreads)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                     void* __restrict__ out, int m, int n, int k, long long ldo, int* status) {
-  using Config = TcConfig<BN>;
+  using Config = TcConfig<BN, STAGES_>;
   constexpr int STAGES = Config::kStages;
   constexpr int OUT_COLUMNS = EPI == kTcSwiGLU ? BN / 2 : BN;  // output columns of a tile
   extern __shared__ unsigned char tc_shared_raw[];
   __shared__ __align__(8) uint64_t full_barrier[STAGES];
   __shared__ __align__(8) uint64_t empty_barrier[STAGES];
-  __shared__ __align__(8) uint64_t accumulator_barrier;
+  __shared__ __align__(8) uint64_t accumulator_full[2];
+  __shared__ __align__(8) uint64_t accumulator_empty[2];
   __shared__ uint32_t tmem_base_slot;
   __shared__ int failed;
 
   unsigned char* tiles = tc_shared_raw + ((1024 - (shared_address(tc_shared_raw) & 1023)) & 1023);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int m0 = blockIdx.y * kTcM;
-  const int n0 = blockIdx.x * OUT_COLUMNS;
+  const int m_tiles = (m + kTcM - 1) / kTcM;
+  const int n_tiles = (n + OUT_COLUMNS - 1) / OUT_COLUMNS;
+  const int total_tiles = m_tiles * n_tiles;
   const int k_blocks = (k + kTcK - 1) / kTcK;
 
   if (threadIdx.x == 0) {
@@ -118,13 +126,16 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
       barrier_init(&full_barrier[s], 1);
       barrier_init(&empty_barrier[s], 1);
     }
-    barrier_init(&accumulator_barrier, 1);
+    for (int b = 0; b < 2; ++b) {
+      barrier_init(&accumulator_full[b], 1);
+      barrier_init(&accumulator_empty[b], kTcThreads - 64);  // every epilogue thread arrives
+    }
     barrier_init_fence();
     failed = 0;
   }
-  if (warp == 1) {  // one warp allocates the accumulator's columns of tensor memory
+  if (warp == 1) {  // one warp allocates both accumulators' columns of tensor memory
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n"
-                 ::"r"(shared_address(&tmem_base_slot)), "r"(BN) : "memory");
+                 ::"r"(shared_address(&tmem_base_slot)), "r"(2 * BN) : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::: "memory");
   }
   asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
@@ -133,21 +144,25 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
   const uint32_t tmem_base = tmem_base_slot;
 
   if (warp == 0) {
-    // ---- producer: TMA loads of the A and B tiles of every k block
+    // ---- producer: TMA loads of the A and B tiles of every k block of every tile
     if (lane == 0) {
-      for (int kb = 0; kb < k_blocks; ++kb) {
-        const int stage = kb % STAGES;
-        const uint32_t parity = (kb / STAGES) & 1;
-        if (!barrier_wait(&empty_barrier[stage], parity ^ 1, status)) { failed = 1; break; }
-        unsigned char* a_tile = tiles + stage * Config::kStageBytes;
-        unsigned char* b_tile = a_tile + kTcM * kTcK * 2;
-        barrier_arrive_expect(&full_barrier[stage], Config::kStageBytes);
-        tma_load_2d(a_tile, &map_a, kb * kTcK, m0, &full_barrier[stage]);
-        if (EPI == kTcSwiGLU) {
-          tma_load_2d(b_tile, &map_b, kb * kTcK, n0, &full_barrier[stage]);                            // gate rows
-          tma_load_2d(b_tile + (BN / 2) * kTcK * 2, &map_b, kb * kTcK, n + n0, &full_barrier[stage]);  // up rows
-        } else {
-          tma_load_2d(b_tile, &map_b, kb * kTcK, n0, &full_barrier[stage]);
+      int step = 0;  // k blocks issued so far, over all tiles
+      for (int tile = blockIdx.x; tile < total_tiles && !failed; tile += gridDim.x) {
+        const int m0 = (tile % m_tiles) * kTcM, n0 = (tile / m_tiles) * OUT_COLUMNS;
+        for (int kb = 0; kb < k_blocks; ++kb, ++step) {
+          const int stage = step % STAGES;
+          const uint32_t parity = (step / STAGES) & 1;
+          if (!barrier_wait(&empty_barrier[stage], parity ^ 1, status)) { failed = 1; break; }
+          unsigned char* a_tile = tiles + stage * Config::kStageBytes;
+          unsigned char* b_tile = a_tile + kTcM * kTcK * 2;
+          barrier_arrive_expect(&full_barrier[stage], Config::kStageBytes);
+          tma_load_2d(a_tile, &map_a, kb * kTcK, m0, &full_barrier[stage]);
+          if (EPI == kTcSwiGLU) {
+            tma_load_2d(b_tile, &map_b, kb * kTcK, n0, &full_barrier[stage]);                            // gate rows
+            tma_load_2d(b_tile + (BN / 2) * kTcK * 2, &map_b, kb * kTcK, n + n0, &full_barrier[stage]);  // up rows
+          } else {
+            tma_load_2d(b_tile, &map_b, kb * kTcK, n0, &full_barrier[stage]);
+          }
         }
       }
     }
@@ -155,44 +170,56 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     // ---- one thread issues every MMA; completion frees the stage
     if (lane == 0) {
       constexpr uint32_t idesc = tc_instruction_descriptor(kTcM, BN);
-      bool ok = true;
-      for (int kb = 0; kb < k_blocks && ok; ++kb) {
-        const int stage = kb % STAGES;
-        const uint32_t parity = (kb / STAGES) & 1;
-        if (!barrier_wait(&full_barrier[stage], parity, status)) { failed = 1; ok = false; break; }
+      int step = 0, local = 0;
+      for (int tile = blockIdx.x; tile < total_tiles && !failed; tile += gridDim.x, ++local) {
+        const int buffer = local & 1;
+        // The epilogue must have drained this accumulator (two tiles ago).
+        if (!barrier_wait(&accumulator_empty[buffer], ((local >> 1) & 1) ^ 1, status)) { failed = 1; break; }
         asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
-        const uint32_t a_address = shared_address(tiles + stage * Config::kStageBytes);
-        const uint32_t b_address = a_address + kTcM * kTcK * 2;
+        const uint32_t tmem_d = tmem_base + buffer * BN;
+        for (int kb = 0; kb < k_blocks; ++kb, ++step) {
+          const int stage = step % STAGES;
+          const uint32_t parity = (step / STAGES) & 1;
+          if (!barrier_wait(&full_barrier[stage], parity, status)) { failed = 1; break; }
+          asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+          const uint32_t a_address = shared_address(tiles + stage * Config::kStageBytes);
+          const uint32_t b_address = a_address + kTcM * kTcK * 2;
 #pragma unroll
-        for (int kk = 0; kk < kTcK / 16; ++kk) {  // 16 k per instruction: 32 bytes further along the swizzled row
-          tc_mma(tmem_base, tc_smem_descriptor(a_address + kk * 32), tc_smem_descriptor(b_address + kk * 32),
-                 idesc, (kb > 0 || kk > 0) ? 1u : 0u);
+          for (int kk = 0; kk < kTcK / 16; ++kk) {  // 16 k per instruction: 32 bytes further along the swizzled row
+            tc_mma(tmem_d, tc_smem_descriptor(a_address + kk * 32), tc_smem_descriptor(b_address + kk * 32),
+                   idesc, (kb > 0 || kk > 0) ? 1u : 0u);
+          }
+          tc_commit(&empty_barrier[stage]);
         }
-        tc_commit(&empty_barrier[stage]);
+        tc_commit(&accumulator_full[buffer]);  // arrives when this tile's accumulator is final
       }
-      tc_commit(&accumulator_barrier);  // arrives when the whole accumulator is final
     }
   } else {
     // ---- epilogue: warp w reads the 32 accumulator rows (lanes) (w % 4) * 32 ...
     const int lane_base = (warp & 3) * 32;
-    const bool landed = barrier_wait(&accumulator_barrier, 0, status);
-    asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
-    const int row = m0 + lane_base + lane;
-    if (landed && !failed) {
+    int local = 0;
+    for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++local) {
+      const int buffer = local & 1;
+      const int m0 = (tile % m_tiles) * kTcM, n0 = (tile / m_tiles) * OUT_COLUMNS;
+      if (!barrier_wait(&accumulator_full[buffer], (local >> 1) & 1, status)) { failed = 1; break; }
+      if (failed) break;
+      asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+      const int row = m0 + lane_base + lane;
+      const uint32_t tmem_row = tmem_base + buffer * BN + (static_cast<uint32_t>(lane_base) << 16);
 #pragma unroll 1
       for (int c = 0; c < OUT_COLUMNS; c += 32) {
         uint32_t acc[32];
-        tc_load_32(tmem_base + (static_cast<uint32_t>(lane_base) << 16) + c, acc);
+        tc_load_32(tmem_row + c, acc);
         float values[32];
         if (EPI == kTcSwiGLU) {
           uint32_t up[32];
-          tc_load_32(tmem_base + (static_cast<uint32_t>(lane_base) << 16) + BN / 2 + c, up);
+          tc_load_32(tmem_row + BN / 2 + c, up);
 #pragma unroll
           for (int i = 0; i < 32; ++i) {
             // gate and up take the rounding to bfloat16 they would get on their way through memory
             const float gate = to_float(from_float<__nv_bfloat16>(__uint_as_float(acc[i])));
             const float u = to_float(from_float<__nv_bfloat16>(__uint_as_float(up[i])));
-            values[i] = (1.0f / (1.0f + expf(-gate))) * gate * u;
+            values[i] = __fdividef(gate, 1.0f + __expf(-gate)) * u;  // the result is rounded to bfloat16 anyway
           }
         } else {
 #pragma unroll
@@ -230,6 +257,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
           }
         }
       }
+      // This thread has read all it needs of the accumulator: hand it back.
+      asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
+      barrier_arrive(&accumulator_empty[buffer]);
     }
   }
 
@@ -242,7 +272,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
   }
   __syncthreads();
   if (warp == 1) {
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_base), "r"(BN) : "memory");
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_base), "r"(2 * BN) : "memory");
   }
 }
 
@@ -250,6 +280,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
 typedef CUresult (*EncodeTiled)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                 const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
                                 CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static bool encode_map(CUtensorMap* map, const void* base, int rows, int k, long long ld, int box_rows);
 
 static EncodeTiled encode_tiled() {
   static EncodeTiled function = nullptr;
@@ -266,7 +298,30 @@ static EncodeTiled encode_tiled() {
 
 // A [rows, k] bfloat16 matrix with row stride ld (elements), read in boxes of
 // box_rows x 64 with the 128-byte swizzle; what lies outside reads as zero.
+// Encoded maps are kept: weights never move and the allocator hands the same
+// activation buffers out again and again.
 static bool make_map(CUtensorMap* map, const void* base, int rows, int k, long long ld, int box_rows) {
+  using Key = std::tuple<const void*, int, int, long long, int>;
+  static std::map<Key, CUtensorMap> known;
+  static std::mutex guard;
+  const Key key(base, rows, k, ld, box_rows);
+  {
+    std::lock_guard<std::mutex> lock(guard);
+    auto found = known.find(key);
+    if (found != known.end()) {
+      *map = found->second;
+      return true;
+    }
+  }
+  if (!encode_map(map, base, rows, k, ld, box_rows)) return false;
+  std::lock_guard<std::mutex> lock(guard);
+  if (known.size() > 4096) known.clear();
+  known.emplace(key, *map);
+  return true;
+}
+
+
+static bool encode_map(CUtensorMap* map, const void* base, int rows, int k, long long ld, int box_rows) {
   EncodeTiled encode = encode_tiled();
   if (encode == nullptr) return false;
   const cuuint64_t dims[2] = {static_cast<cuuint64_t>(k), static_cast<cuuint64_t>(rows)};
@@ -278,17 +333,37 @@ static bool make_map(CUtensorMap* map, const void* base, int rows, int k, long l
                 CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
-template <int BN, int EPI>
-static int launch_tc(const CUtensorMap& map_a, const CUtensorMap& map_b, void* out, int m, int n, int k,
-                     long long ldo, int* status, cudaStream_t stream) {
-  using Config = TcConfig<BN>;
-  auto kernel = gemm_tcgen05_kernel<BN, EPI>;
+int g_tc_bn = 0, g_tc_deep = -1;  // tuning overrides: tile width, deep (1) or shallow (0) pipeline
+
+template <int BN, int EPI, int STAGES_>
+static int launch_tc_staged(const CUtensorMap& map_a, const CUtensorMap& map_b, void* out, int m, int n, int k,
+                            long long ldo, int* status, cudaStream_t stream) {
+  using Config = TcConfig<BN, STAGES_>;
+  auto kernel = gemm_tcgen05_kernel<BN, EPI, STAGES_>;
   cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Config::kSharedBytes);
   if (e != cudaSuccess) return static_cast<int>(e);
   constexpr int out_columns = EPI == kTcSwiGLU ? BN / 2 : BN;
-  dim3 grid((n + out_columns - 1) / out_columns, (m + kTcM - 1) / kTcM);
+  const int tiles = ((n + out_columns - 1) / out_columns) * ((m + kTcM - 1) / kTcM);
+  static int sm_count = 0;
+  if (sm_count == 0) {
+    int device = 0;
+    cudaGetDevice(&device);
+    cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, device);
+  }
+  dim3 grid(tiles < sm_count ? tiles : sm_count);  // one block per SM walks over the tiles
   kernel<<<grid, kTcThreads, Config::kSharedBytes, stream>>>(map_a, map_b, out, m, n, k, ldo, status);
   return static_cast<int>(cudaGetLastError());
+}
+
+// Deep: the whole shared memory as pipeline (the default; a block owns its SM
+// and tensor memory holds two accumulators). Shallow: half the stages.
+template <int BN, int EPI>
+static int launch_tc(const CUtensorMap& map_a, const CUtensorMap& map_b, void* out, int m, int n, int k,
+                     long long ldo, int* status, cudaStream_t stream) {
+  constexpr int deep = BN >= 256 ? 4 : (BN >= 128 ? 6 : 8);
+  const bool shallow = g_tc_deep == 0;
+  if (shallow) return launch_tc_staged<BN, EPI, deep / 2>(map_a, map_b, out, m, n, k, ldo, status, stream);
+  return launch_tc_staged<BN, EPI, deep>(map_a, map_b, out, m, n, k, ldo, status, stream);
 }
 
 }  // namespace mxb
@@ -312,9 +387,11 @@ MXB_API int mxb_gemm_tcgen05(void* out, const void* a, const void* w, int m, int
   const int m_tiles = (m + kTcM - 1) / kTcM;
   int bn = 256;
   if (epilogue != kTcSwiGLU) {
-    if (m_tiles * ((n + 255) / 256) < 148) bn = 128;
-    if (bn == 128 && m_tiles * ((n + 127) / 128) < 148) bn = 64;
+    // 118 tiles keep four fifths of the 148 SMs busy; below that, narrower tiles.
+    if (m_tiles * ((n + 255) / 256) < 118) bn = 128;
+    if (bn == 128 && m_tiles * ((n + 127) / 128) < 118) bn = 64;
   }
+  if (g_tc_bn != 0 && epilogue != kTcSwiGLU) bn = g_tc_bn;
   CUtensorMap map_a, map_b;
   const int b_box = epilogue == kTcSwiGLU ? bn / 2 : bn;
   if (!make_map(&map_a, a, m, k, lda, kTcM) || !make_map(&map_b, w, w_rows, k, ldw, b_box))
@@ -329,4 +406,11 @@ MXB_API int mxb_gemm_tcgen05(void* out, const void* a, const void* w, int m, int
   if (bn == 256) return launch_tc<256, kTcStoreBf16>(map_a, map_b, out, m, n, k, ldo, status, stream);
   if (bn == 128) return launch_tc<128, kTcStoreBf16>(map_a, map_b, out, m, n, k, ldo, status, stream);
   return launch_tc<64, kTcStoreBf16>(map_a, map_b, out, m, n, k, ldo, status, stream);
+}
+
+// Tuning hook: force the tile width (64, 128, 256; 0 = choose) and the
+// pipeline depth (1 deep, 0 shallow, -1 = choose).
+MXB_API void mxb_gemm_tcgen05_tune(int bn, int deep) {
+  mxb::g_tc_bn = bn;
+  mxb::g_tc_deep = deep;
 }

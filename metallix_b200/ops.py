@@ -474,8 +474,9 @@ def gemm_bf16(a: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype = torch.b
     ``backend``: "skinny" is the weight-streaming kernel for at most 64 rows,
     "tcgen05" the hand-written tensor-core kernel, "cublas" the library product
     (where the reference calls a library matmul too), "simple" the plain
-    CUDA-core kernel, "auto" the hand-written kernel whose shape rules hold and
-    the library otherwise."""
+    CUDA-core kernel. "auto": the weight-streaming kernel up to 16 rows, else
+    the library for a plain product (fused products pick the tcgen05 kernel
+    themselves, see ``parts/feed_forward.py``)."""
     _need(a.is_cuda and w.is_cuda, "operands must be on a CUDA device")
     _need(a.dtype == torch.bfloat16 and w.dtype == torch.bfloat16, "operands must be bfloat16")
     _need(a.dim() == 2 and w.dim() == 2 and a.shape[1] == w.shape[1], "shapes do not match a @ w.T")
@@ -485,14 +486,17 @@ def gemm_bf16(a: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype = torch.b
     if (backend == "skinny" or (backend == "auto" and a.shape[0] <= SKINNY_ROWS)) and gemm_skinny_supported(a, w):
         return gemm_skinny(a, w, out_dtype=out_dtype, out=out)
     _need(backend != "skinny", "the weight-streaming kernel does not take this shape")
-    if backend in ("auto", "tcgen05"):
+    if backend == "tcgen05":
         from . import tensor_core
-        if tensor_core.supports(a, w, out_dtype):
-            return tensor_core.gemm(a, w, out_dtype=out_dtype, out=out)
-        _need(backend == "auto", "the tcgen05 kernel does not take this shape: "
+        _need(tensor_core.supports(a, w, out_dtype), "the tcgen05 kernel does not take this call: "
               + tensor_core.why_not(a, w, out_dtype))
-    elif backend != "cublas":
+        return tensor_core.gemm(a, w, out_dtype=out_dtype, out=out)
+    if backend not in ("auto", "cublas"):
         raise KernelError(f"unknown gemm backend {backend!r}")
+    # "auto" beyond the few rows of a decode step: a plain product goes to the
+    # library, as in the reference (its 2-SM tiles beat the one-SM tcgen05
+    # kernel here by 1.2x to 2x on this model's shapes); the tcgen05 kernel runs
+    # where the product is fused with what follows it (SwiGLU).
     if out_dtype == torch.float32:
         result = torch.mm(a, w.t(), out_dtype=torch.float32)
     else:

@@ -32,6 +32,11 @@ class SwiGLU:
                 and ops.gemm_skinny_supported(x, self.gate_up.weight)):
             # A decode step: gate, up and the activation in one pass over the weights.
             return self.down.forward(ops.gemm_skinny(x, self.gate_up.weight, swiglu=True))
+        if self.gate_up.dtype == torch.bfloat16 and self.gate_up.backend in ("auto", "tcgen05"):
+            from .. import tensor_core
+            if tensor_core.supports(x, self.gate_up.weight, torch.bfloat16):
+                # gate, up and the activation in the product's epilogue
+                return self.down.forward(tensor_core.gemm_swiglu(x, self.gate_up.weight))
         return self.down.forward(ops.silu_mul(self.gate_up.forward(x)))
 
     def weight_bytes(self) -> int:

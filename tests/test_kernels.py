@@ -479,8 +479,9 @@ def test_gemm_simple_float32_is_true_32_bit(ops, m, n, k):
     assert torch.equal(one_row[0], out[3 if m > 3 else 0])   # a row does not depend on the batch
 
 
-@pytest.mark.parametrize("backend", ["simple", "cublas", "auto"])
-@pytest.mark.parametrize("m, n, k", [(1, 384, 96), (5, 200, 136), (64, 331, 80), (300, 448, 192)])
+@pytest.mark.parametrize("backend", ["simple", "cublas", "auto", "tcgen05"])
+@pytest.mark.parametrize("m, n, k", [(1, 384, 96), (5, 200, 136), (64, 331, 80), (300, 448, 192),
+                                     (129, 130, 72), (700, 1030, 520)])
 def test_gemm_bf16(ops, backend, m, n, k):
     rng = np.random.default_rng(n)
     a, w = rng.normal(size=(m, k)), rng.normal(size=(n, k))
@@ -526,6 +527,38 @@ def test_gemm_skinny_swiglu(ops, m):
     assert (error <= 3 * 2.0 ** -8 * (np.abs(ref) + np.abs(u) * 0.3 + np.abs(g) * 0.3) + 1e-4).all()
     assert not ops.gemm_skinny_supported(dev(a[:, :80], torch.bfloat16).contiguous(), dev(w[:, :80], torch.bfloat16).contiguous())
     assert not ops.gemm_skinny_supported(dev(np.zeros((65, k)), torch.bfloat16), dev(w, torch.bfloat16))
+
+
+@pytest.mark.parametrize("m, inter, k", [(1, 56, 96), (130, 200, 136), (513, 3072, 1024)])
+def test_tcgen05_swiglu_epilogue(ops, m, inter, k):
+    from metallix_b200 import tensor_core
+    rng = np.random.default_rng(m)
+    a, w = rng.normal(size=(m, k)), rng.normal(size=(2 * inter, k)) * 0.1
+    a_d, w_d = dev(a, torch.bfloat16), dev(w, torch.bfloat16)
+    out = tensor_core.gemm_swiglu(a_d, w_d)
+    ops.check_status("cuda")
+    separate = ops.silu_mul(tensor_core.gemm(a_d, w_d))        # the same product, activation as its own kernel
+    # the epilogue takes the fast exponential; the two may land one bfloat16 step apart
+    gap = (out.double() - separate.double()).abs()
+    assert bool((gap <= 2.0 ** -7 * separate.double().abs() + 1e-30).all())
+    assert float((gap > 0).double().mean()) < 0.02
+    gate_up = rounded(rounded(a, torch.bfloat16) @ rounded(w, torch.bfloat16).T, torch.bfloat16)
+    g, u = gate_up[:, :inter], gate_up[:, inter:]
+    ref = g / (1 + np.exp(-g)) * u
+    assert np.abs(out.cpu().double().numpy() - ref).max() < 3e-2 * np.abs(ref).max()
+
+
+def test_tcgen05_refuses_what_it_cannot_take(ops):
+    from metallix_b200 import tensor_core
+    a, w = dev(np.zeros((4, 100)), torch.bfloat16), dev(np.zeros((8, 100)), torch.bfloat16)
+    assert not tensor_core.supports(a, w, torch.bfloat16)        # k = 100: rows would not start on 16 bytes
+    with pytest.raises(ops.KernelError, match="multiples of 8"):
+        tensor_core.gemm(a, w)
+    with pytest.raises(ops.KernelError, match="does not take"):
+        ops.gemm_bf16(a, w, backend="tcgen05")
+    with pytest.raises(ops.KernelError, match="unknown gemm backend"):
+        ops.gemm_bf16(a, w, backend="cutlass")
+    assert ops.gemm_bf16(a, w, backend="auto").shape == (4, 8)   # auto falls back to the library
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
