@@ -434,36 +434,59 @@ paged_attention_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, const __n
 }
 
 // out[token, head, :] = sum_s exp(m_s - M) acc_s / sum_s exp(m_s - M) l_s over
-// the splits that hold keys of this token, in ascending order.
+// the splits that hold keys of this token, in ascending order. One warp per
+// (token, head): the lanes first take one split each to find M and the
+// weights, then every lane sums its share of the head's values over the
+// splits, always in split order.
 template <typename T>
 __global__ void paged_attention_merge_kernel(const float* __restrict__ partial, T* __restrict__ out,
                                              const int* __restrict__ row_token,
-                                             const int* __restrict__ positions, int heads, int head_dim,
-                                             int max_splits, int window) {
+                                             const int* __restrict__ positions, int rows, int heads,
+                                             int head_dim, int max_splits, int window) {
   chain_wait();
   chain_release();
-  const int row = blockIdx.x, head = blockIdx.y;
+  __shared__ float s_weight[4][64];  // four warps per block, up to 64 splits at a time
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int item = blockIdx.x * 4 + warp;
+  const int row = item / heads, head = item - row * heads;
+  if (row >= rows) return;
   const int token = row_token[row];
   if (token < 0) return;
   const int pos = positions[token];
   const int first_key = window > 0 ? max(0, pos - window + 1) : 0;
   const int first_split = first_key / kSplitKeys, last_split = pos / kSplitKeys;
-  const float* base = partial + (static_cast<size_t>(row) * heads + head) * max_splits * (head_dim + 2);
+  const int splits = last_split - first_split + 1;
+  const float* base = partial + ((static_cast<size_t>(row) * heads + head) * max_splits + first_split) * (head_dim + 2);
   float m = kDecodeMinusHuge;
-  for (int s = first_split; s <= last_split; ++s) m = fmaxf(m, base[static_cast<size_t>(s) * (head_dim + 2) + head_dim]);
+  for (int s = lane; s < splits; s += 32) m = fmaxf(m, base[static_cast<size_t>(s) * (head_dim + 2) + head_dim]);
+  m = warp_max(m);
+  float acc[8];  // head_dim <= 256: eight values per lane
+#pragma unroll
+  for (int j = 0; j < 8; ++j) acc[j] = 0.0f;
   float l = 0.0f;
-  for (int s = first_split; s <= last_split; ++s) {
-    const float* p = base + static_cast<size_t>(s) * (head_dim + 2);
-    l += expf(p[head_dim] - m) * p[head_dim + 1];
+  for (int chunk = 0; chunk < splits; chunk += 64) {
+    const int here = min(64, splits - chunk);
+    __syncwarp();
+    for (int s = lane; s < here; s += 32)
+      s_weight[warp][s] = expf(base[static_cast<size_t>(chunk + s) * (head_dim + 2) + head_dim] - m);
+    __syncwarp();
+    for (int s = 0; s < here; ++s) {
+      const float* p = base + static_cast<size_t>(chunk + s) * (head_dim + 2);
+      const float weight = s_weight[warp][s];
+      l += weight * p[head_dim + 1];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const int d = lane + 32 * j;
+        if (d < head_dim) acc[j] += weight * p[d];
+      }
+    }
   }
   const float inv = 1.0f / l;
-  for (int d = threadIdx.x; d < head_dim; d += blockDim.x) {
-    float sum = 0.0f;
-    for (int s = first_split; s <= last_split; ++s) {
-      const float* p = base + static_cast<size_t>(s) * (head_dim + 2);
-      sum += expf(p[head_dim] - m) * p[d];
-    }
-    out[(static_cast<size_t>(token) * heads + head) * head_dim + d] = from_float<T>(sum * inv);
+  T* dst = out + (static_cast<size_t>(token) * heads + head) * head_dim;
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+    const int d = lane + 32 * j;
+    if (d < head_dim) dst[d] = from_float<T>(acc[j] * inv);
   }
 }
 
@@ -490,10 +513,9 @@ static int launch_decode(const void* q, const void* cache, void* out, float* par
       scale, status);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return static_cast<int>(e);
-  dim3 merge_grid(rows, heads);
-  paged_attention_merge_kernel<T><<<merge_grid, HD >= 128 ? 128 : 64, 0, stream>>>(
-      partial, static_cast<T*>(out), row_token, positions, heads, HD, max_splits, window);
-  return static_cast<int>(cudaGetLastError());
+  return static_cast<int>(launch_chained(paged_attention_merge_kernel<T>, dim3((rows * heads + 3) / 4), dim3(128), 0,
+                                         stream, static_cast<const float*>(partial), static_cast<T*>(out),
+                                         row_token, positions, rows, heads, HD, max_splits, window));
 }
 
 template <int HD>
@@ -514,11 +536,10 @@ static int launch_decode_mma(const void* q, const void* cache, void* out, float*
                                  partial, block_tables, max_pages, row_token, row_request, positions, heads,
                                  kv_heads, page_tokens, num_pages, max_splits, window, scale, status);
   if (e != cudaSuccess) return static_cast<int>(e);
-  dim3 merge_grid(rows, heads);
-  return static_cast<int>(launch_chained(paged_attention_merge_kernel<__nv_bfloat16>, merge_grid,
-                                         dim3(HD >= 128 ? 128 : 64), 0, stream, static_cast<const float*>(partial),
-                                         static_cast<__nv_bfloat16*>(out), row_token, positions, heads, HD,
-                                         max_splits, window));
+  return static_cast<int>(launch_chained(paged_attention_merge_kernel<__nv_bfloat16>, dim3((rows * heads + 3) / 4),
+                                         dim3(128), 0, stream, static_cast<const float*>(partial),
+                                         static_cast<__nv_bfloat16*>(out), row_token, positions, rows, heads,
+                                         HD, max_splits, window));
 }
 
 }  // namespace mxb
