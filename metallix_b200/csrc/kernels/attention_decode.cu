@@ -262,8 +262,10 @@ paged_attention_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, const __n
   float* s_merge = reinterpret_cast<float*>(mma_shared);  // [4 warps][8 heads][HD + 2], over K once the scores exist
   __shared__ __align__(8) uint64_t barriers[2];   // keys, values
 
-  chain_wait();
   chain_release();
+  // What follows up to chain_wait() reads nothing a kernel of this step writes
+  // (the step's integers and the keys and values of earlier positions), so it
+  // runs, copies included, while the kernels before this one are still at work.
   const int split = blockIdx.x, kv = blockIdx.y, row = blockIdx.z;
   const int token = row_token[row];
   if (token < 0) return;
@@ -301,14 +303,25 @@ paged_attention_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, const __n
         ok = false;
       }
     }
-    if (ok) {
-      const __nv_bfloat16* src = cache + page * page_stride + static_cast<size_t>(kv) * page_tokens * HD +
-                                 static_cast<size_t>(key % page_tokens) * HD;
+    // The token's own key and value are written by the kernel before this
+    // one: that row waits for it; every other row is fetched right away.
+    const bool fresh = ok && key == pos;
+    const __nv_bfloat16* src = cache + page * page_stride + static_cast<size_t>(kv) * page_tokens * HD +
+                               static_cast<size_t>(ok ? key % page_tokens : 0) * HD;
+    if (ok && !fresh) {
       barrier_arrive_expect(&barriers[0], ROW_BYTES);
       bulk_copy(sK + decode_tile_offset<HD>(kk, 0), src, ROW_BYTES, &barriers[0]);
       barrier_arrive_expect(&barriers[1], ROW_BYTES);
       bulk_copy(sV + decode_tile_offset<HD>(kk, 0), src + v_offset, ROW_BYTES, &barriers[1]);
-    } else {
+    }
+    chain_wait();
+    if (fresh) {
+      barrier_arrive_expect(&barriers[0], ROW_BYTES);
+      bulk_copy(sK + decode_tile_offset<HD>(kk, 0), src, ROW_BYTES, &barriers[0]);
+      barrier_arrive_expect(&barriers[1], ROW_BYTES);
+      bulk_copy(sV + decode_tile_offset<HD>(kk, 0), src + v_offset, ROW_BYTES, &barriers[1]);
+    }
+    if (!ok) {
       // A row beyond the split's keys: zeros, written by the thread itself.
       uint4* zk = reinterpret_cast<uint4*>(sK + decode_tile_offset<HD>(kk, 0));
       uint4* zv = reinterpret_cast<uint4*>(sV + decode_tile_offset<HD>(kk, 0));
@@ -443,16 +456,16 @@ __global__ void paged_attention_merge_kernel(const float* __restrict__ partial, 
                                              const int* __restrict__ row_token,
                                              const int* __restrict__ positions, int rows, int heads,
                                              int head_dim, int max_splits, int window) {
-  chain_wait();
   chain_release();
   __shared__ float s_weight[4][64];  // four warps per block, up to 64 splits at a time
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int item = blockIdx.x * 4 + warp;
   const int row = item / heads, head = item - row * heads;
   if (row >= rows) return;
-  const int token = row_token[row];
+  const int token = row_token[row];  // the step's integers are not written by any kernel of the step
   if (token < 0) return;
   const int pos = positions[token];
+  chain_wait();
   const int first_key = window > 0 ? max(0, pos - window + 1) : 0;
   const int first_split = first_key / kSplitKeys, last_split = pos / kSplitKeys;
   const int splits = last_split - first_split + 1;

@@ -16,8 +16,8 @@ bool chained_launches() { return g_chained_launches; }
 template <typename T>
 __global__ void embed_kernel(float* __restrict__ out, const T* __restrict__ table,
                              const int* __restrict__ ids, int hidden, int vocab, int* status) {
-  chain_wait();
   chain_release();
+  chain_wait();
   const int t = blockIdx.x;
   const int id = ids[t];
   const bool ok = id >= 0 && id < vocab;
@@ -93,25 +93,33 @@ __global__ void add_rmsnorm_vec4_kernel(float* __restrict__ x, const TDelta* __r
                                         TOut* __restrict__ y, const float* __restrict__ w,
                                         const int* __restrict__ rows_index, int size, float eps) {
   __shared__ float scratch[33];
-  chain_wait();
   chain_release();
   const size_t src = rows_index ? static_cast<size_t>(rows_index[blockIdx.x]) : static_cast<size_t>(blockIdx.x);
   float* row = x + src * size;
+  const int first = threadIdx.x * 4;
+  // The thread's first four values stay in registers between the two passes
+  // (for rows up to 4 * blockDim.x wide that is all of them); the norm weights
+  // are fetched before waiting for the kernel that produces x.
+  float4 held = make_float4(0.0f, 0.0f, 0.0f, 0.0f), held_gain = held;
+  if (first < size) held_gain = load4(w + first);
+  chain_wait();
   float sum = 0.0f;
-  for (int i = threadIdx.x * 4; i < size; i += blockDim.x * 4) {
+  for (int i = first; i < size; i += blockDim.x * 4) {
     float4 v = load4(row + i);
     if (ADD) {
       const float4 d = load4(delta + src * size + i);
       v.x += d.x; v.y += d.y; v.z += d.z; v.w += d.w;
       store4(row + i, v);
     }
+    if (i == first) held = v;
     sum += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
   }
   sum = block_sum(sum, scratch);
   const float scale = rsqrtf(sum / static_cast<float>(size) + eps);
   TOut* dst = y + static_cast<size_t>(blockIdx.x) * size;
-  for (int i = threadIdx.x * 4; i < size; i += blockDim.x * 4) {
-    const float4 v = load4(row + i), g = load4(w + i);
+  for (int i = first; i < size; i += blockDim.x * 4) {
+    const float4 v = i == first ? held : load4(row + i);
+    const float4 g = i == first ? held_gain : load4(w + i);
     store4(dst + i, make_float4(v.x * scale * g.x, v.y * scale * g.y, v.z * scale * g.z, v.w * scale * g.w));
   }
 }
@@ -121,8 +129,8 @@ static bool aligned16(const void* p) { return reinterpret_cast<uintptr_t>(p) % 1
 // x[r, :] += delta[r, :] alone (the last residual sum of a model).
 template <typename TDelta>
 __global__ void add_kernel(float* __restrict__ x, const TDelta* __restrict__ delta, size_t count) {
-  chain_wait();
   chain_release();
+  chain_wait();
   const size_t i = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x;
   if (i < count) x[i] += to_float(delta[i]);
 }

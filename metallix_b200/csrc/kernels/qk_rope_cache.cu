@@ -107,8 +107,9 @@ qk_norm_rope_cache_warp_kernel(
     int tokens, int heads, int kv_heads, int page_tokens, int num_pages, float eps, int* status) {
   constexpr int HD = PER_LANE * 32;
   constexpr int HALF = HD / 2;
-  chain_wait();
   chain_release();
+  // Up to chain_wait(): only the step's integers, the norm weights and the
+  // cos/sin tables, none of which a kernel of this step writes.
   const int lane = threadIdx.x & 31;
   const int per_token = heads + 2 * kv_heads;
   const long long item = static_cast<long long>(blockIdx.x) * 8 + (threadIdx.x >> 5);
@@ -136,10 +137,28 @@ qk_norm_rope_cache_warp_kernel(
     dst = cache + (((static_cast<size_t>(page) * 2 + (is_k ? 0 : 1)) * kv_heads + kv) * page_tokens + row) * HD;
   }
   if (!is_q && !is_k) {
+    chain_wait();
 #pragma unroll
     for (int j = 0; j < PER_LANE; ++j) dst[lane + 32 * j] = src[lane + 32 * j];
     return;
   }
+  const float* weight = is_q ? q_weight : k_weight;
+  float gain[PER_LANE], c[PER_LANE / 2], sn[PER_LANE / 2];
+#pragma unroll
+  for (int j = 0; j < PER_LANE; ++j) gain[j] = weight != nullptr ? weight[lane + 32 * j] : 1.0f;
+  if (cos_table != nullptr) {
+    int pos = positions[t];
+    if (pos < 0 || pos >= table_positions) {
+      if (lane == 0) atomicOr(status, kStatusBadSlot);
+      pos = 0;
+    }
+#pragma unroll
+    for (int j = 0; j < PER_LANE / 2; ++j) {
+      c[j] = cos_table[static_cast<size_t>(pos) * HALF + lane + 32 * j];
+      sn[j] = sin_table[static_cast<size_t>(pos) * HALF + lane + 32 * j];
+    }
+  }
+  chain_wait();
   float x[PER_LANE];
   float sum = 0.0f;
 #pragma unroll
@@ -147,27 +166,19 @@ qk_norm_rope_cache_warp_kernel(
     x[j] = to_float(src[lane + 32 * j]);
     sum += x[j] * x[j];
   }
-  const float* weight = is_q ? q_weight : k_weight;
   if (weight != nullptr) {
     sum = warp_sum(sum);
     const float scale = rsqrtf(sum / static_cast<float>(HD) + eps);
 #pragma unroll
-    for (int j = 0; j < PER_LANE; ++j) x[j] = x[j] * scale * weight[lane + 32 * j];
+    for (int j = 0; j < PER_LANE; ++j) x[j] = x[j] * scale * gain[j];
   }
   if (cos_table != nullptr) {
-    int pos = positions[t];
-    if (pos < 0 || pos >= table_positions) {
-      if (lane == 0) atomicOr(status, kStatusBadSlot);
-      pos = 0;
-    }
-    const float* c = cos_table + static_cast<size_t>(pos) * HALF;
-    const float* sn = sin_table + static_cast<size_t>(pos) * HALF;
 #pragma unroll
     for (int j = 0; j < PER_LANE / 2; ++j) {
-      const int i = lane + 32 * j;  // i < HALF; its partner is element i + HALF = x[j + PER_LANE / 2]
+      // element lane + 32 j (below HALF) and its partner HALF further, x[j + PER_LANE / 2]
       const float lo = x[j], hi = x[j + PER_LANE / 2];
-      x[j] = lo * c[i] - hi * sn[i];
-      x[j + PER_LANE / 2] = hi * c[i] + lo * sn[i];
+      x[j] = lo * c[j] - hi * sn[j];
+      x[j + PER_LANE / 2] = hi * c[j] + lo * sn[j];
     }
   }
 #pragma unroll
