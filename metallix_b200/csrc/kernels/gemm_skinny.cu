@@ -75,7 +75,9 @@ gemm_skinny_kernel(TOut* __restrict__ out, const __nv_bfloat16* __restrict__ x,
   const int slices = k / kSkinnySlice;
   // The weights are never written by a kernel, so this warp's first slices of
   // W are fetched before waiting for the kernel that produces x.
-  constexpr int PRE = MB <= 2 ? 4 : 0;
+  // Narrow blocks read one row of W per lane and have registers to spare:
+  // they fetch up to 12 slices ahead (a k of 3072 is then wholly in flight).
+  constexpr int PRE = MB <= 2 ? (WROWS == 8 && !SWIGLU ? 12 : 4) : 0;
   uint4 pre_lo[PRE > 0 ? PRE : 1][SETS], pre_hi[PRE > 0 ? PRE : 1][SETS];
   chain_release();
 #pragma unroll
