@@ -118,17 +118,22 @@ def run_gen(args) -> int:
     started = time.perf_counter()
     options = dict(dtype=args.dtype, page_tokens=args.block_size, gemm_backend=args.gemm,
                    max_requests=max(args.max_num_seqs, 1) + 1)
+    if args.model:
+        from ..config import read_config
+        config = read_config(args.model)
+    else:
+        with open(args.config) as handle:
+            config = parse_config(json.load(handle))
     if args.num_pages:
         options["num_pages"] = args.num_pages
+    elif args.kv_pool_mib:
+        # The pool by bytes, as the reference's --kv-pool-mib (cli.rs:219-284): whole pages only.
+        per_page = config.kv_bytes_per_token(2 if args.dtype == "bfloat16" else 4) * args.block_size
+        options["num_pages"] = max(args.kv_pool_mib * 2 ** 20 // per_page, 1)
     if args.model:
         engine = Engine.from_folder(args.model, **options)
     else:
-        with open(args.config) as handle:
-            engine = Engine.from_random(parse_config(json.load(handle)), args.random_weights, **options)
-    if args.kv_pool_mib and not args.num_pages:
-        per_page = engine.cache.bytes_per_token() * args.block_size
-        raise SystemExit(f"--kv-pool-mib: pass --num-pages {args.kv_pool_mib * 2**20 // per_page} "
-                         f"({per_page} bytes a page)")
+        engine = Engine.from_random(config, args.random_weights, **options)
     load_ms = (time.perf_counter() - started) * 1e3
 
     results = generate(engine, prompts, max_new_tokens=args.max_tokens,

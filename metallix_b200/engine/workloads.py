@@ -1,0 +1,99 @@
+"""Small fixed workloads of the Qwen3-0.6B-shaped model for profilers.
+
+    python -m metallix_b200.engine.workloads decode --batch 8 --layers 4
+    python -m metallix_b200.engine.workloads prefill --layers 4
+    python -m metallix_b200.engine.workloads gemm --m 2048 --n 4096 --k 1024
+
+``decode``: ``--batch`` requests with ``--prompt-len`` tokens each, then a few
+decode steps (eagerly, so that a profiler sees every kernel; ``--graphs``
+replays captured graphs and prints the time per step instead). ``prefill``:
+one prompt of ``--prompt-len`` tokens, three times. ``gemm``: the tcgen05
+product against the library's on one shape. Random weights, random token ids;
+``--layers`` keeps captures small (a profiler replays every kernel many times).
+"""
+from __future__ import annotations
+
+import argparse
+import sys
+
+QWEN3_0_6B = dict(architectures=["Qwen3ForCausalLM"], model_type="qwen3", hidden_act="silu",
+                  num_hidden_layers=28, hidden_size=1024, num_attention_heads=16,
+                  num_key_value_heads=8, head_dim=128, intermediate_size=3072, vocab_size=151936,
+                  rope_theta=1000000.0, rms_norm_eps=1e-6, tie_word_embeddings=True,
+                  max_position_embeddings=40960)
+
+
+def main(argv=None) -> int:
+    parser = argparse.ArgumentParser(description=__doc__.split("\n\n")[0])
+    parser.add_argument("mode", choices=("decode", "prefill", "gemm"))
+    parser.add_argument("--batch", type=int, default=8)
+    parser.add_argument("--layers", type=int, default=4)
+    parser.add_argument("--prompt-len", type=int, default=2048)
+    parser.add_argument("--steps", type=int, default=4)
+    parser.add_argument("--graphs", action="store_true")
+    parser.add_argument("--m", type=int, default=2048)
+    parser.add_argument("--n", type=int, default=4096)
+    parser.add_argument("--k", type=int, default=1024)
+    parser.add_argument("--swiglu", action="store_true", help="gemm: the fused SwiGLU epilogue (n = 2 * inter)")
+    args = parser.parse_args(argv)
+
+    import numpy as np
+    import torch
+    from .. import Qwen3Config, ops
+    from .engine import Engine, StepEntry
+
+    if args.mode == "gemm":
+        from .. import tensor_core
+        ops.require_cuda()
+        a = torch.randn(args.m, args.k, device="cuda").bfloat16()
+        w = (torch.randn(args.n, args.k, device="cuda") * 0.05).bfloat16()
+        run = (lambda: tensor_core.gemm_swiglu(a, w)) if args.swiglu else (lambda: tensor_core.gemm(a, w))
+        for name, function in (("tcgen05", run), ("library", lambda: torch.mm(a, w.t()))):
+            for _ in range(3):
+                function()
+            start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            start.record()
+            for _ in range(10):
+                function()
+            end.record()
+            torch.cuda.synchronize()
+            microseconds = start.elapsed_time(end) * 100
+            print(f"{name}: {microseconds:.1f} us, {2 * args.m * args.n * args.k / microseconds / 1e6:.0f} TFLOP/s"
+                  " (launch overhead included)")
+        ops.check_status("cuda")
+        return 0
+
+    config = Qwen3Config.from_dict(dict(QWEN3_0_6B, num_hidden_layers=args.layers))
+    pages = args.batch * (-(-(args.prompt_len + 64) // 16)) + 64
+    engine = Engine.from_random(config, 0, dtype="bfloat16", page_tokens=16, num_pages=pages,
+                                max_requests=args.batch + 2, max_context=4096, cuda_graphs=args.graphs)
+    rng = np.random.default_rng(0)
+    if args.mode == "prefill":
+        ids = rng.integers(0, config.vocab_size, size=args.prompt_len).tolist()
+        for _ in range(3):
+            engine.step([StepEntry("p", ids, [args.prompt_len - 1])])
+            engine.release("p")
+        torch.cuda.synchronize()
+    else:
+        names = [f"r{i}" for i in range(args.batch)]
+        for first in range(0, args.batch, 4):
+            engine.step([StepEntry(name, rng.integers(0, config.vocab_size, size=args.prompt_len).tolist(), [])
+                         for name in names[first:first + 4]])
+        for _ in range(args.steps):
+            engine.step([StepEntry(name, [int(rng.integers(0, config.vocab_size))], [0]) for name in names])
+        torch.cuda.synchronize()
+        if args.graphs:
+            start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            start.record()
+            for _ in range(50):
+                engine.step([StepEntry(name, [5], [0]) for name in names])
+            end.record()
+            torch.cuda.synchronize()
+            print(f"{start.elapsed_time(end) / 50:.4f} ms per decode step")
+    engine.check()
+    print("ok")
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())
