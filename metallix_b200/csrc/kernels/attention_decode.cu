@@ -447,60 +447,57 @@ paged_attention_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, const __n
 }
 
 // out[token, head, :] = sum_s exp(m_s - M) acc_s / sum_s exp(m_s - M) l_s over
-// the splits that hold keys of this token, in ascending order. One warp per
-// (token, head): the lanes first take one split each to find M and the
-// weights, then every lane sums its share of the head's values over the
-// splits, always in split order.
+// the splits that hold keys of this token, in ascending order. One block per
+// (token, head): the first threads take one split each to find M and the
+// weights, then every thread sums one or two of the head's values over the
+// splits, always in split order, with all its loads in flight together.
+constexpr int kMergeThreads = 128;
+constexpr int kMergeSplits = 64;  // splits handled per round
+
 template <typename T>
-__global__ void paged_attention_merge_kernel(const float* __restrict__ partial, T* __restrict__ out,
-                                             const int* __restrict__ row_token,
-                                             const int* __restrict__ positions, int rows, int heads,
-                                             int head_dim, int max_splits, int window) {
+__global__ void __launch_bounds__(kMergeThreads)
+paged_attention_merge_kernel(const float* __restrict__ partial, T* __restrict__ out,
+                             const int* __restrict__ row_token, const int* __restrict__ positions,
+                             int rows, int heads, int head_dim, int max_splits, int window) {
   chain_release();
-  __shared__ float s_weight[4][64];  // four warps per block, up to 64 splits at a time
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int item = blockIdx.x * 4 + warp;
-  const int row = item / heads, head = item - row * heads;
-  if (row >= rows) return;
+  __shared__ float s_weight[kMergeSplits];
+  __shared__ float s_reduce[8];
+  const int row = blockIdx.x, head = blockIdx.y;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int token = row_token[row];  // the step's integers are not written by any kernel of the step
   if (token < 0) return;
   const int pos = positions[token];
-  chain_wait();
   const int first_key = window > 0 ? max(0, pos - window + 1) : 0;
   const int first_split = first_key / kSplitKeys, last_split = pos / kSplitKeys;
   const int splits = last_split - first_split + 1;
   const float* base = partial + ((static_cast<size_t>(row) * heads + head) * max_splits + first_split) * (head_dim + 2);
+  chain_wait();
+  // The maximum over all splits.
   float m = kDecodeMinusHuge;
-  for (int s = lane; s < splits; s += 32) m = fmaxf(m, base[static_cast<size_t>(s) * (head_dim + 2) + head_dim]);
+  for (int s = tid; s < splits; s += kMergeThreads) m = fmaxf(m, base[static_cast<size_t>(s) * (head_dim + 2) + head_dim]);
   m = warp_max(m);
-  float acc[8];  // head_dim <= 256: eight values per lane
-#pragma unroll
-  for (int j = 0; j < 8; ++j) acc[j] = 0.0f;
-  float l = 0.0f;
-  for (int chunk = 0; chunk < splits; chunk += 64) {
-    const int here = min(64, splits - chunk);
-    __syncwarp();
-    for (int s = lane; s < here; s += 32)
-      s_weight[warp][s] = expf(base[static_cast<size_t>(chunk + s) * (head_dim + 2) + head_dim] - m);
-    __syncwarp();
+  if (lane == 0) s_reduce[warp] = m;
+  __syncthreads();
+  m = fmaxf(fmaxf(s_reduce[0], s_reduce[1]), fmaxf(s_reduce[2], s_reduce[3]));
+  float acc0 = 0.0f, acc1 = 0.0f, l = 0.0f;  // head_dim <= 256: values tid and tid + 128
+  for (int chunk = 0; chunk < splits; chunk += kMergeSplits) {
+    const int here = min(kMergeSplits, splits - chunk);
+    __syncthreads();
+    if (tid < here) s_weight[tid] = expf(base[static_cast<size_t>(chunk + tid) * (head_dim + 2) + head_dim] - m);
+    __syncthreads();
+#pragma unroll 8
     for (int s = 0; s < here; ++s) {
       const float* p = base + static_cast<size_t>(chunk + s) * (head_dim + 2);
-      const float weight = s_weight[warp][s];
+      const float weight = s_weight[s];
+      if (tid < head_dim) acc0 += weight * p[tid];
+      if (tid + kMergeThreads < head_dim) acc1 += weight * p[tid + kMergeThreads];
       l += weight * p[head_dim + 1];
-#pragma unroll
-      for (int j = 0; j < 8; ++j) {
-        const int d = lane + 32 * j;
-        if (d < head_dim) acc[j] += weight * p[d];
-      }
     }
   }
   const float inv = 1.0f / l;
   T* dst = out + (static_cast<size_t>(token) * heads + head) * head_dim;
-#pragma unroll
-  for (int j = 0; j < 8; ++j) {
-    const int d = lane + 32 * j;
-    if (d < head_dim) dst[d] = from_float<T>(acc[j] * inv);
-  }
+  if (tid < head_dim) dst[tid] = from_float<T>(acc0 * inv);
+  if (tid + kMergeThreads < head_dim) dst[tid + kMergeThreads] = from_float<T>(acc1 * inv);
 }
 
 template <typename T, int HD, int G>
@@ -526,7 +523,7 @@ static int launch_decode(const void* q, const void* cache, void* out, float* par
       scale, status);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return static_cast<int>(e);
-  return static_cast<int>(launch_chained(paged_attention_merge_kernel<T>, dim3((rows * heads + 3) / 4), dim3(128), 0,
+  return static_cast<int>(launch_chained(paged_attention_merge_kernel<T>, dim3(rows, heads), dim3(kMergeThreads), 0,
                                          stream, static_cast<const float*>(partial), static_cast<T*>(out),
                                          row_token, positions, rows, heads, HD, max_splits, window));
 }
@@ -549,8 +546,8 @@ static int launch_decode_mma(const void* q, const void* cache, void* out, float*
                                  partial, block_tables, max_pages, row_token, row_request, positions, heads,
                                  kv_heads, page_tokens, num_pages, max_splits, window, scale, status);
   if (e != cudaSuccess) return static_cast<int>(e);
-  return static_cast<int>(launch_chained(paged_attention_merge_kernel<__nv_bfloat16>, dim3((rows * heads + 3) / 4),
-                                         dim3(128), 0, stream, static_cast<const float*>(partial),
+  return static_cast<int>(launch_chained(paged_attention_merge_kernel<__nv_bfloat16>, dim3(rows, heads),
+                                         dim3(kMergeThreads), 0, stream, static_cast<const float*>(partial),
                                          static_cast<__nv_bfloat16*>(out), row_token, positions, rows, heads,
                                          HD, max_splits, window));
 }
