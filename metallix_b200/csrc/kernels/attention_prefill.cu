@@ -2,7 +2,7 @@
 // the paged cache (which already holds this step's own keys and values).
 //
 // One block of four warps takes up to 64 consecutive query tokens of one
-// request and one query head. It walks the request's keys in tiles of 64
+// request and one query head (half a tile of the caller's list). It walks the request's keys in tiles of 64
 // absolute positions, fetched page by page through the block table with
 // 16-byte asynchronous copies into swizzled shared memory (two stages), forms
 // q k^T and p v on the tensor cores (mma.sync m16n8k16, bfloat16 in, float32
@@ -82,9 +82,12 @@ flash_prefill_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* _
   unsigned char* sQ = sK + TILE_BYTES;                 // [64][HD]: the query tile borrows the second key
                                                        // stage until its fragments sit in registers
 
-  const int head = blockIdx.x, tile = blockIdx.y;  // heads of one tile run side by side and share its keys in L2
+  // Tile lists hold up to 128 tokens a tile: two blocks take 64 each.
+  const int head = blockIdx.x, tile = blockIdx.y >> 1;  // heads of one tile run side by side and share its keys in L2
   const int kv = head / (heads / kv_heads);
-  const int t0 = tile_start[tile], n = tile_length[tile];
+  const int t0 = tile_start[tile] + (blockIdx.y & 1) * kFlashQueries;
+  const int n = min(kFlashQueries, tile_length[tile] - static_cast<int>(blockIdx.y & 1) * kFlashQueries);
+  if (n <= 0) return;
   const int pos0 = positions[t0];
   const int last_pos = pos0 + n - 1;
   const int first_key = window > 0 ? max(0, pos0 - window + 1) : 0;
@@ -278,7 +281,7 @@ static int launch_flash(const void* q, const void* cache, void* out, const int* 
   auto kernel = flash_prefill_kernel<HD>;
   cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, shared);
   if (e != cudaSuccess) return static_cast<int>(e);
-  dim3 grid(heads, tiles);
+  dim3 grid(heads, 2 * tiles);
   kernel<<<grid, kFlashThreads, shared, stream>>>(
       static_cast<const __nv_bfloat16*>(q), static_cast<const __nv_bfloat16*>(cache),
       static_cast<__nv_bfloat16*>(out), block_tables, max_pages, tile_request, tile_start, tile_length,
@@ -297,9 +300,9 @@ MXB_API int mxb_flash_prefill_supported(int head_dim, int heads, int kv_heads, i
   return head_dim == 64 || head_dim == 128 ? 1 : 0;
 }
 
-MXB_API int mxb_flash_prefill_tile() { return kFlashQueries; }
+MXB_API int mxb_flash_prefill_tile() { return 2 * kFlashQueries; }
 
-// Query tiles as for the general kernel, but up to 64 tokens each.
+// Query tiles as for the general kernel, but up to 128 tokens each.
 MXB_API int mxb_flash_prefill(const void* q, const void* cache, void* out, const int* block_tables,
                               int max_pages, const int* tile_request, const int* tile_start,
                               const int* tile_length, const int* positions, int tiles, int heads,

@@ -31,7 +31,7 @@ from .model import DecoderModel
 _DTYPES = {"bfloat16": torch.bfloat16, "bf16": torch.bfloat16, "float32": torch.float32,
            "fp32": torch.float32, torch.bfloat16: torch.bfloat16, torch.float32: torch.float32}
 ATTENTION_TILE = 16  # query tokens per tile of the general kernel (csrc/kernels/attention_tile.cu)
-WIDE_TILE = 64       # and of the tensor-core prompt kernel (csrc/kernels/attention_prefill.cu)
+WIDE_TILE = 128      # and of the tensor-core prompt kernels (csrc/kernels/attention_prefill*.cu)
 
 
 class StepError(ValueError):
@@ -253,7 +253,7 @@ class Engine:
         starts, wanted = [], []
         tile_request, tile_start, tile_length = [], [], []
         single_tiles, decode_token, decode_request, longest = [], [], [], 0
-        wide = []   # (keys to walk, row, first token, count) of 64-token tiles
+        wide = []   # (keys to walk, row, first token, count) of wide tiles
         group_tables = [[] for _ in cache.groups]
         for row, entry in enumerate(entries):
             rid = self._rid(entry)

@@ -42,6 +42,9 @@ _SIGNATURES = {
     "mxb_flash_prefill": [_P, _P, _P, _P, _I, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _F, _I, _P, _P],
     "mxb_flash_prefill_supported": [_I, _I, _I, _I],
     "mxb_flash_prefill_tile": [],
+    "mxb_flash_prefill_tcgen05": [_P, _P, _P, _P, _I, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _F, _I, _P, _P],
+    "mxb_flash_prefill_tcgen05_supported": [_I, _I, _I, _I, _I],
+    "mxb_flash_prefill_tcgen05_tile": [],
     "mxb_gemm_simple": [_P, _I, _P, _P, _I, _I, _I, _I, _L, _L, _L, _P],
     "mxb_gemm_skinny": [_P, _I, _P, _P, _I, _I, _I, _L, _L, _L, _I, _P],
     "mxb_gemm_skinny_supported": [_I, _I, _I, _L, _L],
@@ -331,12 +334,21 @@ def flash_prefill_tile() -> int:
     return _fn("mxb_flash_prefill_tile")()
 
 
+def flash_prefill_tcgen05_supported(head_dim: int, heads: int, kv_heads: int, page_tokens: int,
+                                    dtype: torch.dtype) -> bool:
+    """Whether the tcgen05 prompt kernel takes this head layout and page size."""
+    if dtype not in _CODES:
+        return False
+    return bool(_fn("mxb_flash_prefill_tcgen05_supported")(head_dim, heads, kv_heads, page_tokens, _CODES[dtype]))
+
+
 def flash_prefill(q: torch.Tensor, cache: torch.Tensor, out: torch.Tensor, block_tables: torch.Tensor,
                   tile_request: torch.Tensor, tile_start: torch.Tensor, tile_length: torch.Tensor,
-                  positions: torch.Tensor, scale: float, window: int = 0) -> torch.Tensor:
+                  positions: torch.Tensor, scale: float, window: int = 0, kernel: str = "auto") -> torch.Tensor:
     """Causal attention of prompt portions on the tensor cores (bfloat16,
-    float32 softmax and accumulation); tiles hold up to 64 consecutive tokens
-    of one request."""
+    float32 softmax and accumulation); tiles hold up to 128 consecutive tokens
+    of one request. ``kernel``: "tcgen05" (TMA, tensor memory), "mma" (the
+    warp-level kernel) or "auto" (tcgen05 where it takes the page size)."""
     _check(q, "q", (torch.bfloat16,), 3)
     _check(out, "out", (torch.bfloat16,), 3)
     _check(cache, "cache", (torch.bfloat16,), 5)
@@ -353,6 +365,18 @@ def flash_prefill(q: torch.Tensor, cache: torch.Tensor, out: torch.Tensor, block
     tiles = tile_request.numel()
     _need(tile_start.numel() == tiles and tile_length.numel() == tiles, "tile lists differ in length")
     _need(positions.numel() == tokens, "one position per token")
+    _need(kernel in ("auto", "tcgen05", "mma"), f"unknown prompt-attention kernel {kernel!r}")
+    tcgen05 = flash_prefill_tcgen05_supported(head_dim, heads, kv_heads, page_tokens, q.dtype)
+    _need(tcgen05 or kernel != "tcgen05",
+          f"the tcgen05 prompt kernel does not take head_dim {head_dim} with pages of {page_tokens} tokens")
+    if tcgen05 and kernel != "mma":
+        _need(q.is_contiguous() and cache.is_contiguous(), "q and cache must be contiguous")
+        _call("mxb_flash_prefill_tcgen05", q.data_ptr(), cache.data_ptr(), out.data_ptr(),
+              block_tables.data_ptr(), block_tables.shape[1], tile_request.data_ptr(), tile_start.data_ptr(),
+              tile_length.data_ptr(), positions.data_ptr(), tokens, tiles, heads, kv_heads, head_dim,
+              page_tokens, num_pages, int(window or 0), float(scale), _CODES[q.dtype],
+              status_word(q.device).data_ptr(), _stream())
+        return out
     _call("mxb_flash_prefill", q.data_ptr(), cache.data_ptr(), out.data_ptr(), block_tables.data_ptr(),
           block_tables.shape[1], tile_request.data_ptr(), tile_start.data_ptr(), tile_length.data_ptr(),
           positions.data_ptr(), tiles, heads, kv_heads, head_dim, page_tokens, num_pages,

@@ -278,9 +278,10 @@ def test_attention_does_not_depend_on_the_cut(ops):
     assert np.array_equal(part[37:], whole[total - 12:total - 9])
 
 
-def run_flash(ops, q, k, v, lengths, page_tokens, scale, window=0, seed=0):
-    """The tensor-core prompt kernel on requests whose last ``queries``
-    positions are the queries (bfloat16)."""
+def run_flash(ops, q, k, v, lengths, page_tokens, scale, window=0, seed=0, kernel="mma", tile=128):
+    """A tensor-core prompt kernel ("mma": warp-level, "tcgen05": TMA and
+    tensor memory) on requests whose last ``queries`` positions are the
+    queries (bfloat16), cut into tiles of up to ``tile`` tokens."""
     dtype = torch.bfloat16
     heads, head_dim, kv_heads = q[0].shape[1], q[0].shape[2], k[0].shape[1]
     rng = np.random.default_rng(seed)
@@ -299,30 +300,40 @@ def run_flash(ops, q, k, v, lengths, page_tokens, scale, window=0, seed=0):
         begin = len(positions)
         q_rows.append(q[r][total - queries:total])
         positions += list(range(total - queries, total))
-        for first in range(0, queries, 64):
-            tiles.append((r, begin + first, min(64, queries - first)))
+        for first in range(0, queries, tile):
+            tiles.append((r, begin + first, min(tile, queries - first)))
     q_all = dev(np.concatenate(q_rows), dtype)
     out = torch.full_like(q_all, float("nan"))
     ops.flash_prefill(q_all, dev(host_cache, dtype), out, dev(tables, torch.int32),
                       dev([t[0] for t in tiles], torch.int32), dev([t[1] for t in tiles], torch.int32),
-                      dev([t[2] for t in tiles], torch.int32), dev(positions, torch.int32), scale, window)
+                      dev([t[2] for t in tiles], torch.int32), dev(positions, torch.int32), scale, window,
+                      kernel=kernel)
     ops.check_status("cuda")
     return out.cpu().double().numpy()
 
 
+FLASH_KERNELS = ("mma", "tcgen05")
+
+
+@pytest.mark.parametrize("kernel", FLASH_KERNELS)
 @pytest.mark.parametrize("heads, kv_heads, head_dim, page_tokens", [(2, 2, 64, 16), (6, 2, 64, 4),
-                                                                   (4, 2, 128, 16), (3, 1, 128, 32)])
-def test_flash_prefill(ops, heads, kv_heads, head_dim, page_tokens):
+                                                                   (4, 2, 128, 16), (3, 1, 128, 32),
+                                                                   (5, 1, 128, 8), (2, 1, 64, 128)])
+def test_flash_prefill(ops, heads, kv_heads, head_dim, page_tokens, kernel):
     rng = np.random.default_rng(heads * head_dim + 1)
     dtype = torch.bfloat16
-    lengths = [(200, 200), (130, 2), (64, 64), (333, 70), (65, 65), (500, 129), (3, 3)]
+    if kernel == "tcgen05" and page_tokens == 4:
+        assert not ops.flash_prefill_tcgen05_supported(head_dim, heads, kv_heads, page_tokens, dtype)
+        pytest.skip("a page of 4 tokens does not fill a swizzle group: the warp-level kernel takes it")
+    lengths = [(200, 200), (130, 2), (64, 64), (333, 70), (65, 65), (500, 129), (3, 3), (1000, 300)]
     q = [rounded(rng.normal(size=(n, heads, head_dim)), dtype) for n, _ in lengths]
     k = [rounded(rng.normal(size=(n, kv_heads, head_dim)), dtype) for n, _ in lengths]
     v = [rounded(rng.normal(size=(n, kv_heads, head_dim)), dtype) for n, _ in lengths]
     scale = head_dim ** -0.5
     assert ops.flash_prefill_supported(head_dim, heads, kv_heads, dtype)
     for window in (0, 1, 50, 64, 200):
-        out = run_flash(ops, q, k, v, lengths, page_tokens, scale, window=window)
+        out = run_flash(ops, q, k, v, lengths, page_tokens, scale, window=window, kernel=kernel,
+                        tile=128 if window != 50 else 50)
         cursor = 0
         for r, (total, queries) in enumerate(lengths):
             ref = plain.causal_gqa_attention(q[r], k[r], v[r], scale, window=window or None)[total - queries:]
@@ -332,26 +343,27 @@ def test_flash_prefill(ops, heads, kv_heads, head_dim, page_tokens):
     assert not ops.flash_prefill_supported(48, 3, 1, dtype)
 
 
-def test_flash_prefill_one_far_key_and_cuts(ops):
+@pytest.mark.parametrize("kernel", FLASH_KERNELS)
+def test_flash_prefill_one_far_key_and_cuts(ops, kernel):
     heads, kv_heads, head_dim, total = 4, 2, 128, 700
     dtype = torch.bfloat16
     rng = np.random.default_rng(31)
-    for target in (0, 15, 16, 63, 64, 65, 511, 512, 640, 698, 699):
+    for target in (0, 15, 16, 63, 64, 65, 127, 128, 511, 512, 640, 698, 699):
         k = rounded(rng.normal(size=(total, kv_heads, head_dim)) * 0.1, dtype)
         v = rounded(rng.normal(size=(total, kv_heads, head_dim)), dtype)
         q = rounded(rng.normal(size=(total, heads, head_dim)) * 0.1, dtype)
         k[target, :, :] = 0.0
         k[target, :, 5] = 16.0
         q[-1, :, 5] = 16.0
-        out = run_flash(ops, [q], [k], [v], [(total, 40)], 16, head_dim ** -0.5, seed=target)
+        out = run_flash(ops, [q], [k], [v], [(total, 40)], 16, head_dim ** -0.5, seed=target, kernel=kernel)
         for head in range(heads):
             assert np.abs(out[-1, head] - v[target, head // 2]).max() < 1e-2, (target, head)
     # the same positions whole, as a portion after cached keys, and beside another request
     q = [rounded(rng.normal(size=(300, heads, head_dim)), dtype)]
     k = [rounded(rng.normal(size=(300, kv_heads, head_dim)), dtype)]
     v = [rounded(rng.normal(size=(300, kv_heads, head_dim)), dtype)]
-    whole = run_flash(ops, q, k, v, [(300, 300)], 16, 0.09)
-    part = run_flash(ops, q + q, k + k, v + v, [(300, 77), (250, 5)], 16, 0.09, seed=3)
+    whole = run_flash(ops, q, k, v, [(300, 300)], 16, 0.09, kernel=kernel)
+    part = run_flash(ops, q + q, k + k, v + v, [(300, 77), (250, 5)], 16, 0.09, seed=3, kernel=kernel)
     assert np.array_equal(part[:77], whole[-77:])
     assert np.array_equal(part[77:], whole[245:250])
 
