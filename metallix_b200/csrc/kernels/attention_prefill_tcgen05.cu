@@ -13,9 +13,11 @@
 //               two score buffers, and O_tile = P V into one of two output
 //               buffers, with P read from tensor memory where the softmax
 //               warps left it (over the scores it came from);
-//   warps 2..5  one thread per query row: mask, running maximum and sum in
-//               float32, P = exp2(...) back to tensor memory as bfloat16, and
-//               the row's output accumulator in registers: acc = acc * alpha +
+//   warps 2..17 four threads per query row, each with a quarter of the tile's
+//               keys and a quarter of the head's values: mask, running maximum
+//               (the four exchange their maxima once per tile) and sum in float32,
+//               P = exp2(...) back to tensor memory as bfloat16, and the
+//               row's output accumulator in registers: acc = acc * alpha +
 //               O_tile, read back with tcgen05.ld.
 // The MMAs of tile j + 1's scores run while the softmax of tile j does, and
 // the accumulation of tile j - 1 while P_j V_j runs.
@@ -37,15 +39,20 @@ namespace mxb {
 
 constexpr int kFaRows = 128;     // query rows of a block
 constexpr int kFaKeys = 128;     // keys of a tile
-constexpr int kFaThreads = 192;
+constexpr int kFaParts = 4;      // threads per query row
+constexpr int kFaSoftmaxThreads = kFaParts * kFaRows;
+constexpr int kFaThreads = 64 + kFaSoftmaxThreads;
 constexpr int kFaTmemColumns = 512;
 constexpr int kFaHalfBytes = 128 * kTmaColumns * 2;  // a [128 x 64] bfloat16 operand block: 16 KiB
 
 template <int HD> struct FaConfig {
   static constexpr int kHalves = HD / kTmaColumns;
   static constexpr int kTileBytes = kHalves * kFaHalfBytes;    // Q, a K stage or a V stage
-  static constexpr int kStages = HD == 64 ? 4 : 2;             // one block per SM either way
-  static constexpr int kSharedBytes = (1 + 2 * kStages) * kTileBytes + 1024;
+  static constexpr int kKeyStages = HD == 64 ? 4 : 3;          // at most; one block per SM either way
+  static constexpr int kValueStages = HD == 64 ? 4 : 2;
+  static constexpr int kSmallBytes = 512 + 2 * kFaParts * kFaRows * 4;  // barriers and the exchange of maxima, after the tiles
+  // Wanted: the tiles of every stage, the small area and room to align to 1024 bytes.
+  static constexpr int kSharedBytes = (1 + kKeyStages + kValueStages) * kTileBytes + kSmallBytes + 1024;
   static constexpr int kScoreColumns = kFaKeys;                // two buffers of 128 columns
   static constexpr int kOutputBase = 2 * kFaKeys;              // then two buffers of HD columns
 };
@@ -67,20 +74,42 @@ flash_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __
                              __nv_bfloat16* __restrict__ out, const int* __restrict__ block_tables, int max_pages,
                              const int* __restrict__ tile_request, const int* __restrict__ tile_start,
                              const int* __restrict__ tile_length, const int* __restrict__ positions, int heads,
-                             int kv_heads, int page_tokens, int num_pages, int window, float scale, int* status) {
+                             int kv_heads, int page_tokens, int num_pages, int window, float scale,
+                             int shared_bytes, int* status) {
   using Config = FaConfig<HD>;
-  constexpr int STAGES = Config::kStages;
+  constexpr int MAX_STAGES = Config::kKeyStages;
   constexpr int HALVES = Config::kHalves;
+  // All shared memory is dynamic: the block gets `shared_bytes` (up to the
+  // device's limit) and uses as many key stages as fit behind the 1024-byte
+  // boundary the swizzled tiles need.
   extern __shared__ unsigned char fa_shared_raw[];
-  __shared__ __align__(8) uint64_t q_full;
-  __shared__ __align__(8) uint64_t k_full[STAGES], k_empty[STAGES], v_full[STAGES], v_empty[STAGES];
-  __shared__ __align__(8) uint64_t s_full[2], p_full[2], o_full[2], o_empty[2];
-  __shared__ uint32_t tmem_base_slot;
-  __shared__ int failed;
-
-  unsigned char* q_tile = fa_shared_raw + ((1024 - (shared_address(fa_shared_raw) & 1023)) & 1023);
+  const int slack = (1024 - (shared_address(fa_shared_raw) & 1023)) & 1023;
+  const int VS = Config::kValueStages;
+  const int fitting = (shared_bytes - slack - Config::kSmallBytes) / Config::kTileBytes - 1 - VS;
+  const int KS = fitting < MAX_STAGES ? fitting : MAX_STAGES;
+  if (KS < 1) {  // the launcher asks for more than that
+    if (threadIdx.x == 0) atomicOr(status, kStatusWaitTimeout);
+    return;
+  }
+  unsigned char* q_tile = fa_shared_raw + slack;
   unsigned char* k_tiles = q_tile + Config::kTileBytes;
-  unsigned char* v_tiles = k_tiles + STAGES * Config::kTileBytes;
+  unsigned char* v_tiles = k_tiles + KS * Config::kTileBytes;
+  unsigned char* small = v_tiles + VS * Config::kTileBytes;
+  uint64_t* q_full = reinterpret_cast<uint64_t*>(small);
+  uint64_t* k_full = q_full + 1;
+  uint64_t* k_empty = k_full + MAX_STAGES;
+  uint64_t* v_full = k_empty + MAX_STAGES;
+  uint64_t* v_empty = v_full + MAX_STAGES;
+  uint64_t* s_full = v_empty + MAX_STAGES;
+  uint64_t* p_full = s_full + 2;
+  uint64_t* o_full = p_full + 2;
+  uint64_t* o_empty = o_full + 2;
+  uint64_t* row_ready = o_empty + 2;  // [4]: the softmax warps of a lane group meet here
+  uint32_t& tmem_base_slot = *reinterpret_cast<uint32_t*>(row_ready + 4);
+  volatile int& failed = *reinterpret_cast<volatile int*>(&tmem_base_slot + 1);
+  // [tile parity][part][row]: the threads of a row exchange maxima (and, at the end, sums)
+  float (*row_max)[kFaParts][kFaRows] = reinterpret_cast<float (*)[kFaParts][kFaRows]>(small + 512);
+  static_assert((1 + 4 * MAX_STAGES + 8 + 4) * 8 + 8 <= 512, "the barriers do not fit their area");
 
   const int head = blockIdx.x, tile = blockIdx.y;  // heads of one tile run side by side and share its keys in L2
   const int kv = head / (heads / kv_heads);
@@ -93,8 +122,8 @@ flash_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __
   const int key_tiles = tile_end - tile_begin + 1;
 
   if (threadIdx.x == 0) {
-    barrier_init(&q_full, 1);
-    for (int s = 0; s < STAGES; ++s) {
+    barrier_init(q_full, 1);
+    for (int s = 0; s < MAX_STAGES; ++s) {
       barrier_init(&k_full[s], 1);
       barrier_init(&k_empty[s], 1);
       barrier_init(&v_full[s], 1);
@@ -102,10 +131,11 @@ flash_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __
     }
     for (int b = 0; b < 2; ++b) {
       barrier_init(&s_full[b], 1);
-      barrier_init(&p_full[b], kFaRows);   // every softmax thread arrives
+      barrier_init(&p_full[b], kFaSoftmaxThreads);   // every softmax thread arrives
       barrier_init(&o_full[b], 1);
-      barrier_init(&o_empty[b], kFaRows);
+      barrier_init(&o_empty[b], kFaSoftmaxThreads);
     }
+    for (int g = 0; g < 4; ++g) barrier_init(&row_ready[g], kFaParts * 32);
     barrier_init_fence();
     failed = 0;
   }
@@ -123,44 +153,42 @@ flash_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __
     // ---- fetch: Q once, then K and V of every key tile, page by page
     const int* table = block_tables + static_cast<size_t>(tile_request[tile]) * max_pages;
     if (lane == 0) {
-      barrier_arrive_expect(&q_full, Config::kTileBytes);
+      barrier_arrive_expect(q_full, Config::kTileBytes);
       for (int half = 0; half < HALVES; ++half)
-        tma_load_2d(q_tile + half * kFaHalfBytes, &map_q, head * HD + half * kTmaColumns, t0, &q_full);
+        tma_load_2d(q_tile + half * kFaHalfBytes, &map_q, head * HD + half * kTmaColumns, t0, q_full);
     }
     const int pages_per_tile = kFaKeys / page_tokens;
-    const int copies = 2 * pages_per_tile * HALVES;  // K and V, every page, every 64-value half
+    const int copies = pages_per_tile * HALVES;  // every page, every 64-value half
     for (int i = 0; i < key_tiles && !failed; ++i) {
-      const int stage = i % STAGES;
-      const uint32_t parity = (i / STAGES) & 1;
+      const int k_stage = i % KS, v_stage = i % VS;
       const int key0 = (tile_begin + i) * kFaKeys;
-      bool ok = barrier_wait(&k_empty[stage], parity ^ 1, status);
-      ok = ok && barrier_wait(&v_empty[stage], parity ^ 1, status);
-      if (!ok) { failed = 1; break; }
-      if (lane == 0) {
-        barrier_arrive_expect(&k_full[stage], Config::kTileBytes);
-        barrier_arrive_expect(&v_full[stage], Config::kTileBytes);
-      }
-      __syncwarp();
-      for (int copy = lane; copy < copies; copy += 32) {
-        const int half = copy % HALVES;
-        const int which = (copy / HALVES) % 2;  // 0 K, 1 V
-        const int slot = copy / (2 * HALVES);   // page of the tile
-        const int page_key = key0 + slot * page_tokens;
-        // Pages no row of the tile can see are not looked up: page 0 stands
-        // in (its values are finite and every such key is masked).
-        int page = 0;
-        if (page_key <= last_pos && page_key + page_tokens > first_key && page_key / page_tokens < max_pages) {
-          page = table[page_key / page_tokens];
-          if (page < 0 || page >= num_pages) {
-            atomicOr(status, kStatusBadPage);
-            page = 0;
-          }
+      // Pages no row of the tile can see are not looked up: page 0 stands in
+      // (its values are finite and every such key is masked).
+      int page = 0;
+      const int slot = lane / HALVES, half = lane % HALVES;  // copies <= 32: one per lane
+      const int page_key = key0 + slot * page_tokens;
+      if (lane < copies && page_key <= last_pos && page_key + page_tokens > first_key &&
+          page_key / page_tokens < max_pages) {
+        page = table[page_key / page_tokens];
+        if (page < 0 || page >= num_pages) {
+          atomicOr(status, kStatusBadPage);
+          page = 0;
         }
-        const int row = ((page * 2 + which) * kv_heads + kv) * page_tokens;
-        unsigned char* dst = (which ? v_tiles : k_tiles) + stage * Config::kTileBytes + half * kFaHalfBytes +
-                             slot * page_tokens * (kTmaColumns * 2);
-        tma_load_2d(dst, &map_cache, half * kTmaColumns, row, which ? &v_full[stage] : &k_full[stage]);
       }
+      const uint32_t offset = half * kFaHalfBytes + slot * page_tokens * (kTmaColumns * 2);
+      // K as soon as the scores that read this stage last are done, V when the P V product is.
+      if (!barrier_wait(&k_empty[k_stage], ((i / KS) & 1) ^ 1, status)) { failed = 1; break; }
+      if (lane == 0) barrier_arrive_expect(&k_full[k_stage], Config::kTileBytes);
+      __syncwarp();
+      if (lane < copies)
+        tma_load_2d(k_tiles + k_stage * Config::kTileBytes + offset, &map_cache, half * kTmaColumns,
+                    ((page * 2) * kv_heads + kv) * page_tokens, &k_full[k_stage]);
+      if (!barrier_wait(&v_empty[v_stage], ((i / VS) & 1) ^ 1, status)) { failed = 1; break; }
+      if (lane == 0) barrier_arrive_expect(&v_full[v_stage], Config::kTileBytes);
+      __syncwarp();
+      if (lane < copies)
+        tma_load_2d(v_tiles + v_stage * Config::kTileBytes + offset, &map_cache, half * kTmaColumns,
+                    ((page * 2 + 1) * kv_heads + kv) * page_tokens, &v_full[v_stage]);
     }
   } else if (warp == 1) {
     // ---- one thread issues every MMA
@@ -168,10 +196,10 @@ flash_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __
       constexpr uint32_t idesc_s = tc_instruction_descriptor(kFaRows, kFaKeys);
       constexpr uint32_t idesc_o = tc_instruction_descriptor_b_mn(kFaRows, HD);
       const uint32_t q_address = shared_address(q_tile);
-      bool ok = barrier_wait(&q_full, 0, status);
+      bool ok = barrier_wait(q_full, 0, status);
       auto scores = [&](int i) {  // S_i = Q K_i^T
-        const int stage = i % STAGES;
-        if (!barrier_wait(&k_full[stage], (i / STAGES) & 1, status)) return false;
+        const int stage = i % KS;
+        if (!barrier_wait(&k_full[stage], (i / KS) & 1, status)) return false;
         tc_fence_after_sync();
         const uint32_t k_address = shared_address(k_tiles + stage * Config::kTileBytes);
         const uint32_t tmem_s = tmem_base + (i & 1) * Config::kScoreColumns;
@@ -186,8 +214,8 @@ flash_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __
         return true;
       };
       auto outputs = [&](int i) {  // O_tile_i = P_i V_i
-        const int stage = i % STAGES, buffer = i & 1;
-        if (!barrier_wait(&v_full[stage], (i / STAGES) & 1, status)) return false;
+        const int stage = i % VS, buffer = i & 1;
+        if (!barrier_wait(&v_full[stage], (i / VS) & 1, status)) return false;
         if (!barrier_wait(&o_empty[buffer], ((i >> 1) & 1) ^ 1, status)) return false;
         if (!barrier_wait(&p_full[buffer], (i >> 1) & 1, status)) return false;
         tc_fence_after_sync();
@@ -196,8 +224,9 @@ flash_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __
         const uint32_t tmem_o = tmem_base + Config::kOutputBase + buffer * HD;
 #pragma unroll
         for (int kk = 0; kk < kFaKeys / 16; ++kk) {  // 16 keys per instruction: two 8-row groups of V, 8 columns of P
-          tc_mma_ts(tmem_o, tmem_p + kk * 8, tc_smem_descriptor_mn(v_address + kk * 2048, kFaHalfBytes), idesc_o,
-                    kk > 0 ? 1u : 0u);
+          // P of the keys' quarter q lies over the first half of that quarter's score columns.
+          tc_mma_ts(tmem_o, tmem_p + (kk / 2) * (kFaKeys / kFaParts) + (kk % 2) * 8,
+                    tc_smem_descriptor_mn(v_address + kk * 2048, kFaHalfBytes), idesc_o, kk > 0 ? 1u : 0u);
         }
         tc_commit(&v_empty[stage]);
         tc_commit(&o_full[buffer]);
@@ -211,8 +240,13 @@ flash_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __
       if (!ok) failed = 1;
     }
   } else {
-    // ---- softmax and accumulation: one thread per query row
+    // ---- softmax and accumulation: four threads per query row. Warps w,
+    // w + 4, w + 8 and w + 12 reach the same 32 lanes of tensor memory; each
+    // takes 32 keys of a tile and HD / 4 values of the output.
+    constexpr int PART_KEYS = kFaKeys / kFaParts, PART_HD = HD / kFaParts;
+    static_assert(PART_KEYS == 32 && (PART_HD == 16 || PART_HD == 32), "the tensor-memory loads below take 16 or 32 columns");
     const int lane_base = (warp & 3) * 32;
+    const int part = (warp - 2) >> 2;
     const int row = lane_base + lane;
     const bool valid = row < n;
     const int pos = pos0 + row;
@@ -220,9 +254,10 @@ flash_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __
     const int key_lo = window > 0 ? max(0, pos - window + 1) : 0;          // first key this row sees
     const float scale_log2 = scale * 1.4426950408889634f;
     const uint32_t tmem_lane = tmem_base + (static_cast<uint32_t>(lane_base) << 16);
-    float acc[HD];
+    uint64_t* meet = &row_ready[warp & 3];
+    float acc[PART_HD];
 #pragma unroll
-    for (int i = 0; i < HD; ++i) acc[i] = 0.0f;
+    for (int i = 0; i < PART_HD; ++i) acc[i] = 0.0f;
     float m = -INFINITY, l = 0.0f, alpha_pending = 0.0f;
     bool ok = true;
 
@@ -230,83 +265,82 @@ flash_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __
       const int buffer = i & 1;
       if (!barrier_wait(&o_full[buffer], (i >> 1) & 1, status)) return false;
       tc_fence_after_sync();
-      const uint32_t tmem_o = tmem_lane + Config::kOutputBase + buffer * HD;
-#pragma unroll
-      for (int c = 0; c < HD; c += 32) {
-        uint32_t o[32];
-        tc_load_32(tmem_o + c, o);
-#pragma unroll
-        for (int j = 0; j < 32; ++j) acc[c + j] = fmaf(acc[c + j], alpha, __uint_as_float(o[j]));
-      }
+      uint32_t o[PART_HD];
+      tc_load(tmem_lane + Config::kOutputBase + buffer * HD + part * PART_HD, o);
       tc_fence_before_sync();
       barrier_arrive(&o_empty[buffer]);
+#pragma unroll
+      for (int j = 0; j < PART_HD; ++j) acc[j] = fmaf(acc[j], alpha, __uint_as_float(o[j]));
       return true;
     };
 
     for (int i = 0; i < key_tiles; ++i) {
       const int buffer = i & 1;
-      const int key0 = (tile_begin + i) * kFaKeys;
+      const int key0 = (tile_begin + i) * kFaKeys + part * PART_KEYS;  // first key of this thread's share
       if (!barrier_wait(&s_full[buffer], (i >> 1) & 1, status) || failed) { ok = false; break; }
       tc_fence_after_sync();
-      const uint32_t tmem_s = tmem_lane + buffer * Config::kScoreColumns;
-      const bool all_seen = key0 >= key_lo && key0 + kFaKeys - 1 <= key_hi;
-      // Running maximum, already multiplied by scale * log2(e) (scale > 0 keeps the order).
-      float tile_max = -INFINITY;
-#pragma unroll 1
-      for (int c = 0; c < kFaKeys; c += 32) {
-        uint32_t s[32];
-        tc_load_32(tmem_s + c, s);
-        if (all_seen) {
+      const uint32_t tmem_s = tmem_lane + buffer * Config::kScoreColumns + part * PART_KEYS;
+      const bool all_seen = key0 >= key_lo && key0 + PART_KEYS - 1 <= key_hi;
+      uint32_t raw[PART_KEYS];
+      tc_load_32(tmem_s, raw);
+      float s[PART_KEYS];
+      if (all_seen) {
 #pragma unroll
-          for (int j = 0; j < 32; ++j) tile_max = fmaxf(tile_max, __uint_as_float(s[j]));
-        } else {
+        for (int j = 0; j < PART_KEYS; ++j) s[j] = __uint_as_float(raw[j]);
+      } else {
 #pragma unroll
-          for (int j = 0; j < 32; ++j) {
-            const int key = key0 + c + j;
-            if (key >= key_lo && key <= key_hi) tile_max = fmaxf(tile_max, __uint_as_float(s[j]));
-          }
-        }
+        for (int j = 0; j < PART_KEYS; ++j)
+          s[j] = key0 + j >= key_lo && key0 + j <= key_hi ? __uint_as_float(raw[j]) : -INFINITY;
       }
+      // Running maximum, already multiplied by scale * log2(e) (scale > 0 keeps the order).
+      float max4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll
+      for (int j = 0; j < PART_KEYS; ++j) max4[j & 3] = fmaxf(max4[j & 3], s[j]);
+      row_max[buffer][part][row] = fmaxf(fmaxf(max4[0], max4[1]), fmaxf(max4[2], max4[3]));
+      barrier_arrive(meet);
+      if (!barrier_wait(meet, i & 1, status)) { ok = false; break; }
+      const float tile_max = fmaxf(fmaxf(row_max[buffer][0][row], row_max[buffer][1][row]),
+                                   fmaxf(row_max[buffer][2][row], row_max[buffer][3][row]));
       const float m_new = fmaxf(m, tile_max * scale_log2);
       // A row that has seen no key yet keeps a finite reference so that no inf - inf appears.
       const float ref = m_new == -INFINITY ? 0.0f : m_new;
       const float alpha = fa_exp2(m - ref);
-      float sum = 0.0f;
-#pragma unroll 1
-      for (int c = 0; c < kFaKeys; c += 32) {
-        uint32_t s[32];
-        tc_load_32(tmem_s + c, s);
-        uint32_t packed[16];
+      float sum4[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+      uint32_t packed[PART_KEYS / 2];
 #pragma unroll
-        for (int j = 0; j < 32; j += 2) {
-          float p0 = fa_exp2(fmaf(__uint_as_float(s[j]), scale_log2, -ref));
-          float p1 = fa_exp2(fmaf(__uint_as_float(s[j + 1]), scale_log2, -ref));
-          if (!all_seen) {
-            const int key = key0 + c + j;
-            if (key < key_lo || key > key_hi) p0 = 0.0f;
-            if (key + 1 < key_lo || key + 1 > key_hi) p1 = 0.0f;
-          }
-          sum += p0 + p1;
-          packed[j >> 1] = fa_pack(p0, p1);
-        }
-        // P lies over the scores it came from: columns this thread has already read.
-        tc_store_16(tmem_s + (c >> 1), packed);
+      for (int j = 0; j < PART_KEYS; j += 2) {
+        // A masked score is -inf here and gives exactly 0.
+        const float p0 = fa_exp2(fmaf(s[j], scale_log2, -ref));
+        const float p1 = fa_exp2(fmaf(s[j + 1], scale_log2, -ref));
+        sum4[(j >> 1) & 3] += p0 + p1;
+        packed[j >> 1] = fa_pack(p0, p1);
       }
+      // P lies over the scores it came from: columns only this thread reads.
+      tc_store_16(tmem_s, packed);
       tc_store_wait();
       tc_fence_before_sync();
       barrier_arrive(&p_full[buffer]);
-      l = fmaf(l, alpha, sum);
+      l = fmaf(l, alpha, (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]));
       m = m_new;
       if (i > 0 && !accumulate(i - 1, alpha_pending)) { ok = false; break; }
       alpha_pending = alpha;
     }
     if (ok && !failed) ok = accumulate(key_tiles - 1, alpha_pending);
     if (!ok) failed = 1;
+    // The row's sum: this thread's keys plus its partners' (all scaled to the
+    // same final maximum). The buffer of this parity was last read two
+    // exchanges ago.
+    row_max[key_tiles & 1][part][row] = l;
+    barrier_arrive(meet);
+    if (ok && !barrier_wait(meet, key_tiles & 1, status)) ok = false;
+    l = (row_max[key_tiles & 1][0][row] + row_max[key_tiles & 1][1][row]) +
+        (row_max[key_tiles & 1][2][row] + row_max[key_tiles & 1][3][row]);
+    if (!ok) failed = 1;
     if (ok && valid) {
       const float inv = 1.0f / l;
-      __nv_bfloat16* dst = out + (static_cast<size_t>(t0 + row) * heads + head) * HD;
+      __nv_bfloat16* dst = out + (static_cast<size_t>(t0 + row) * heads + head) * HD + part * PART_HD;
 #pragma unroll
-      for (int c = 0; c < HD; c += 8) {
+      for (int c = 0; c < PART_HD; c += 8) {
         *reinterpret_cast<uint4*>(dst + c) =
             make_uint4(fa_pack(acc[c] * inv, acc[c + 1] * inv), fa_pack(acc[c + 2] * inv, acc[c + 3] * inv),
                        fa_pack(acc[c + 4] * inv, acc[c + 5] * inv), fa_pack(acc[c + 6] * inv, acc[c + 7] * inv));
@@ -341,12 +375,19 @@ static int launch_flash_tc(const void* q, const void* cache, void* out, const in
       !make_map(&map_cache, cache, static_cast<int>(cache_rows), HD, HD, page_tokens))
     return static_cast<int>(cudaErrorInvalidValue);
   auto kernel = flash_prefill_tcgen05_kernel<HD>;
-  cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Config::kSharedBytes);
+  static int shared_limit = 0;
+  if (shared_limit == 0) {
+    int device = 0;
+    cudaGetDevice(&device);
+    cudaDeviceGetAttribute(&shared_limit, cudaDevAttrMaxSharedMemoryPerBlockOptin, device);
+  }
+  const int shared_bytes = Config::kSharedBytes < shared_limit ? Config::kSharedBytes : shared_limit;
+  cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, shared_bytes);
   if (e != cudaSuccess) return static_cast<int>(e);
   dim3 grid(heads, tiles);
-  kernel<<<grid, kFaThreads, Config::kSharedBytes, stream>>>(
+  kernel<<<grid, kFaThreads, shared_bytes, stream>>>(
       map_q, map_cache, static_cast<__nv_bfloat16*>(out), block_tables, max_pages, tile_request, tile_start,
-      tile_length, positions, heads, kv_heads, page_tokens, num_pages, window, scale, status);
+      tile_length, positions, heads, kv_heads, page_tokens, num_pages, window, scale, shared_bytes, status);
   return static_cast<int>(cudaGetLastError());
 }
 

@@ -71,6 +71,18 @@ __device__ __forceinline__ void tc_load_32(uint32_t taddr, uint32_t (&r)[32]) {
   asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
 }
 
+__device__ __forceinline__ void tc_load_16(uint32_t taddr, uint32_t (&r)[16]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];\n"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+      : "r"(taddr) : "memory");
+  asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
+}
+__device__ __forceinline__ void tc_load(uint32_t taddr, uint32_t (&r)[32]) { tc_load_32(taddr, r); }
+__device__ __forceinline__ void tc_load(uint32_t taddr, uint32_t (&r)[16]) { tc_load_16(taddr, r); }
+
 // The same for an MN-major tile (the contracted index runs over rows): rows of
 // 64 contiguous values of the free index (128 bytes), 8 rows to a 1024-byte
 // group, groups one after the other; the next 64 values of the free index lie

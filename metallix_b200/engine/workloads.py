@@ -3,12 +3,15 @@
     python -m metallix_b200.engine.workloads decode --batch 8 --layers 4
     python -m metallix_b200.engine.workloads prefill --layers 4
     python -m metallix_b200.engine.workloads gemm --m 2048 --n 4096 --k 1024
+    python -m metallix_b200.engine.workloads attention --prompt-len 2048
 
 ``decode``: ``--batch`` requests with ``--prompt-len`` tokens each, then a few
 decode steps (eagerly, so that a profiler sees every kernel; ``--graphs``
 replays captured graphs and prints the time per step instead). ``prefill``:
 one prompt of ``--prompt-len`` tokens, three times. ``gemm``: the tcgen05
-product against the library's on one shape. Random weights, random token ids;
+product against the library's on one shape. ``attention``: the two prompt
+attention kernels alone on one prompt of ``--prompt-len`` tokens over
+``--context`` cached ones. Random weights, random token ids;
 ``--layers`` keeps captures small (a profiler replays every kernel many times).
 """
 from __future__ import annotations
@@ -25,7 +28,7 @@ QWEN3_0_6B = dict(architectures=["Qwen3ForCausalLM"], model_type="qwen3", hidden
 
 def main(argv=None) -> int:
     parser = argparse.ArgumentParser(description=__doc__.split("\n\n")[0])
-    parser.add_argument("mode", choices=("decode", "prefill", "gemm"))
+    parser.add_argument("mode", choices=("decode", "prefill", "gemm", "attention"))
     parser.add_argument("--batch", type=int, default=8)
     parser.add_argument("--layers", type=int, default=4)
     parser.add_argument("--prompt-len", type=int, default=2048)
@@ -35,6 +38,8 @@ def main(argv=None) -> int:
     parser.add_argument("--n", type=int, default=4096)
     parser.add_argument("--k", type=int, default=1024)
     parser.add_argument("--swiglu", action="store_true", help="gemm: the fused SwiGLU epilogue (n = 2 * inter)")
+    parser.add_argument("--context", type=int, default=0, help="attention: keys already in the cache")
+    parser.add_argument("--kernel", default="both", choices=("both", "tcgen05", "mma"))
     args = parser.parse_args(argv)
 
     import numpy as np
@@ -60,6 +65,40 @@ def main(argv=None) -> int:
             microseconds = start.elapsed_time(end) * 100
             print(f"{name}: {microseconds:.1f} us, {2 * args.m * args.n * args.k / microseconds / 1e6:.0f} TFLOP/s"
                   " (launch overhead included)")
+        ops.check_status("cuda")
+        return 0
+
+    if args.mode == "attention":
+        ops.require_cuda()
+        heads, kv_heads, head_dim, page_tokens = (QWEN3_0_6B["num_attention_heads"], QWEN3_0_6B["num_key_value_heads"],
+                                                  QWEN3_0_6B["head_dim"], 16)
+        tokens, total = args.prompt_len, args.context + args.prompt_len
+        pages = -(-total // page_tokens)
+        generator = torch.Generator(device="cuda").manual_seed(0)
+        cache = torch.randn((pages, 2, kv_heads, page_tokens, head_dim), device="cuda", generator=generator).bfloat16()
+        q = torch.randn((tokens, heads, head_dim), device="cuda", generator=generator).bfloat16()
+        out = torch.empty_like(q)
+        table = torch.randperm(pages, device="cuda", generator=generator).int().view(1, pages)
+        tile = ops.flash_prefill_tile()
+        starts = list(range(0, tokens, tile))[::-1]   # the tiles with most keys first
+        ints = lambda values: torch.tensor(values, dtype=torch.int32, device="cuda")
+        tile_request, tile_start = ints([0] * len(starts)), ints(starts)
+        tile_length = ints([min(tile, tokens - s) for s in starts])
+        positions = torch.arange(args.context, total, dtype=torch.int32, device="cuda")
+        flops = 4.0 * head_dim * heads * sum(args.context + t + 1 for t in range(tokens))
+        for kernel in (("tcgen05", "mma") if args.kernel == "both" else (args.kernel,)):
+            run = lambda: ops.flash_prefill(q, cache, out, table, tile_request, tile_start, tile_length, positions,
+                                            head_dim ** -0.5, kernel=kernel)
+            for _ in range(3):
+                run()
+            start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            start.record()
+            for _ in range(10):
+                run()
+            end.record()
+            torch.cuda.synchronize()
+            microseconds = start.elapsed_time(end) * 100
+            print(f"{kernel}: {microseconds:.1f} us, {flops / microseconds / 1e6:.0f} TFLOP/s (causal flops)")
         ops.check_status("cuda")
         return 0
 

@@ -97,7 +97,13 @@ def _call(name: str, *args) -> None:
         raise KernelError(f"{name} failed to launch: CUDA error {code}")
 
 
+_raw_stream = getattr(torch._C, "_cuda_getCurrentRawStream", None)
+
+
 def _stream() -> int:
+    """The current stream's handle; this runs once per launch, so it takes the short way."""
+    if _raw_stream is not None:
+        return _raw_stream(torch.cuda.current_device())
     return torch.cuda.current_stream().cuda_stream
 
 
@@ -111,6 +117,9 @@ def _need(condition: bool, message: str) -> None:
 
 
 def _check(tensor: torch.Tensor, name: str, dtypes, dims: Optional[int] = None) -> None:
+    if (isinstance(tensor, torch.Tensor) and tensor.is_cuda and tensor.dtype in dtypes and tensor.is_contiguous()
+            and (dims is None or tensor.dim() == dims)):
+        return   # the messages below are built only for what fails
     _need(isinstance(tensor, torch.Tensor), f"{name} must be a tensor")
     _need(tensor.is_cuda, f"{name} must be on a CUDA device; there is no CPU path")
     _need(tensor.dtype in dtypes, f"{name} has dtype {tensor.dtype}, expected one of {dtypes}")
@@ -135,10 +144,13 @@ def set_chained_launches(enabled: bool) -> None:
 
 def status_word(device) -> torch.Tensor:
     """The int32 word kernels set bits in instead of trapping."""
-    key = torch.device(device).index or 0
-    if key not in _status:
-        _status[key] = torch.zeros(1, dtype=torch.int32, device=device)
-    return _status[key]
+    word = _status.get(device)
+    if word is None:
+        key = torch.device(device).index or 0
+        if key not in _status:
+            _status[key] = torch.zeros(1, dtype=torch.int32, device=device)
+        word = _status[device] = _status[key]   # torch.device objects and strings find it directly next time
+    return word
 
 
 def check_status(device) -> None:
