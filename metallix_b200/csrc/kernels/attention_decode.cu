@@ -335,7 +335,8 @@ paged_attention_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, const __n
   // ---- the query heads of this key/value head as rows 0..group-1 of the 16-row operand
   uint32_t qa0[HD / 16], qa2[HD / 16];
   {
-    const __nv_bfloat16* qrow = q + (static_cast<size_t>(token) * heads + kv * group + (g < group ? g : 0)) * HD;
+    // q is written by the kernel ahead of this one
+    const __nv_bfloat16* qrow = behind_wait(q) + (static_cast<size_t>(token) * heads + kv * group + (g < group ? g : 0)) * HD;
 #pragma unroll
     for (int ks = 0; ks < HD / 16; ++ks) {
       qa0[ks] = g < group ? *reinterpret_cast<const uint32_t*>(qrow + ks * 16 + 2 * t) : 0u;
@@ -472,9 +473,11 @@ paged_attention_merge_kernel(const float* __restrict__ partial, T* __restrict__ 
   const int splits = last_split - first_split + 1;
   const float* base = partial + ((static_cast<size_t>(row) * heads + head) * max_splits + first_split) * (head_dim + 2);
   chain_wait();
+  base = behind_wait(base);  // the partial results are written by the kernel ahead of this one
   // The maximum over all splits.
   float m = kDecodeMinusHuge;
-  for (int s = tid; s < splits; s += kMergeThreads) m = fmaxf(m, base[static_cast<size_t>(s) * (head_dim + 2) + head_dim]);
+  for (int s = tid; s < splits; s += kMergeThreads)
+    m = fmaxf(m, base[static_cast<size_t>(s) * (head_dim + 2) + head_dim]);
   m = warp_max(m);
   if (lane == 0) s_reduce[warp] = m;
   __syncthreads();
@@ -483,7 +486,8 @@ paged_attention_merge_kernel(const float* __restrict__ partial, T* __restrict__ 
   for (int chunk = 0; chunk < splits; chunk += kMergeSplits) {
     const int here = min(kMergeSplits, splits - chunk);
     __syncthreads();
-    if (tid < here) s_weight[tid] = expf(base[static_cast<size_t>(chunk + tid) * (head_dim + 2) + head_dim] - m);
+    if (tid < here)
+      s_weight[tid] = expf(base[static_cast<size_t>(chunk + tid) * (head_dim + 2) + head_dim] - m);
     __syncthreads();
 #pragma unroll 8
     for (int s = 0; s < here; ++s) {

@@ -71,6 +71,17 @@ inline int ceil_div(int a, int b) { return (a + b - 1) / b; }
 __device__ __forceinline__ void chain_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void chain_release() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 
+// A kernel that launch_chained() starts lives before the kernel ahead of it
+// has written its output, so the promise a const __restrict__ parameter makes
+// (nobody changes this memory while the kernel runs) does not hold for that
+// output, and the compiler, trusting it, may move a load above chain_wait().
+// behind_wait(), called after chain_wait(), gives the pointer back with that
+// promise taken off: loads through the result stay behind the wait.
+template <typename T> __device__ __forceinline__ T* behind_wait(T* p) {
+  asm volatile("" : "+l"(p));
+  return p;
+}
+
 bool chained_launches();  // whether launch_chained() asks for the overlap (csrc/kernels/embed_norm.cu)
 
 template <typename... KernelArgs, typename... Args>

@@ -103,6 +103,8 @@ __global__ void add_rmsnorm_vec4_kernel(float* __restrict__ x, const TDelta* __r
   float4 held = make_float4(0.0f, 0.0f, 0.0f, 0.0f), held_gain = held;
   if (first < size) held_gain = load4(w + first);
   chain_wait();
+  row = behind_wait(row);      // both written by kernels ahead of this one
+  delta = behind_wait(delta);
   float sum = 0.0f;
   for (int i = first; i < size; i += blockDim.x * 4) {
     float4 v = load4(row + i);
@@ -131,6 +133,8 @@ template <typename TDelta>
 __global__ void add_kernel(float* __restrict__ x, const TDelta* __restrict__ delta, size_t count) {
   chain_release();
   chain_wait();
+  x = behind_wait(x);
+  delta = behind_wait(delta);
   const size_t i = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x;
   if (i < count) x[i] += to_float(delta[i]);
 }

@@ -94,6 +94,8 @@ gemm_skinny_kernel(TOut* __restrict__ out, const __nv_bfloat16* __restrict__ x,
   }
   chain_wait();
 #pragma unroll
+  for (int j = 0; j < MB; ++j) x_row[j] = behind_wait(x_row[j]);  // x is written by the kernel ahead
+#pragma unroll
   for (int i = 0; i < PRE; ++i) {
     const int slice = warp + i * kSkinnyWarps;
     if (slice < slices) {

@@ -92,10 +92,15 @@ __global__ void qk_norm_rope_cache_kernel(
   }
 }
 
+// V values of type T moved as one access of V * sizeof(T) bytes.
+template <typename T, int V> struct alignas(sizeof(T) * V) Pack { T v[V]; };
+
 // The same work with one warp per (token, head) and no shared memory, for
-// head sizes that are a multiple of 64 with the rotation over the whole head:
-// lane l holds elements l, l + 32, l + 64, ...; the rotation partner of
-// element i (i +- head_dim / 2) then sits in the same lane.
+// head sizes 64, 128 and 256 with the rotation over the whole head: with
+// V = head_dim / 64, lane l holds elements V l .. V l + V - 1 of the lower
+// half and the same of the upper half, so the rotation partner of element i
+// (i +- head_dim / 2) sits in the same lane and every access is one of
+// V * sizeof(T) bytes, a warp covering whole contiguous lines.
 template <typename T, int PER_LANE>
 __global__ void __launch_bounds__(256)
 qk_norm_rope_cache_warp_kernel(
@@ -136,36 +141,58 @@ qk_norm_rope_cache_warp_kernel(
     }
     dst = cache + (((static_cast<size_t>(page) * 2 + (is_k ? 0 : 1)) * kv_heads + kv) * page_tokens + row) * HD;
   }
+  constexpr int V = PER_LANE / 2;
+  using Values = Pack<T, V>;
+  using Floats = Pack<float, V>;
+  const Values* src_lo = reinterpret_cast<const Values*>(src) + lane;
+  const Values* src_hi = reinterpret_cast<const Values*>(src + HALF) + lane;
+  Values* dst_lo = reinterpret_cast<Values*>(dst) + lane;
+  Values* dst_hi = reinterpret_cast<Values*>(dst + HALF) + lane;
   if (!is_q && !is_k) {
     chain_wait();
-#pragma unroll
-    for (int j = 0; j < PER_LANE; ++j) dst[lane + 32 * j] = src[lane + 32 * j];
+    const Values lo = *behind_wait(src_lo), hi = *behind_wait(src_hi);  // written by the kernel ahead of this one
+    *dst_lo = lo;
+    *dst_hi = hi;
     return;
   }
   const float* weight = is_q ? q_weight : k_weight;
-  float gain[PER_LANE], c[PER_LANE / 2], sn[PER_LANE / 2];
+  float gain[PER_LANE], c[V], sn[V];
 #pragma unroll
-  for (int j = 0; j < PER_LANE; ++j) gain[j] = weight != nullptr ? weight[lane + 32 * j] : 1.0f;
+  for (int j = 0; j < PER_LANE; ++j) gain[j] = 1.0f;
+  if (weight != nullptr) {
+    const Floats lo = reinterpret_cast<const Floats*>(weight)[lane];
+    const Floats hi = reinterpret_cast<const Floats*>(weight + HALF)[lane];
+#pragma unroll
+    for (int j = 0; j < V; ++j) {
+      gain[j] = lo.v[j];
+      gain[V + j] = hi.v[j];
+    }
+  }
   if (cos_table != nullptr) {
     int pos = positions[t];
     if (pos < 0 || pos >= table_positions) {
       if (lane == 0) atomicOr(status, kStatusBadSlot);
       pos = 0;
     }
+    const Floats cs = reinterpret_cast<const Floats*>(cos_table + static_cast<size_t>(pos) * HALF)[lane];
+    const Floats ss = reinterpret_cast<const Floats*>(sin_table + static_cast<size_t>(pos) * HALF)[lane];
 #pragma unroll
-    for (int j = 0; j < PER_LANE / 2; ++j) {
-      c[j] = cos_table[static_cast<size_t>(pos) * HALF + lane + 32 * j];
-      sn[j] = sin_table[static_cast<size_t>(pos) * HALF + lane + 32 * j];
+    for (int j = 0; j < V; ++j) {
+      c[j] = cs.v[j];
+      sn[j] = ss.v[j];
     }
   }
   chain_wait();
+  const Values in_lo = *behind_wait(src_lo), in_hi = *behind_wait(src_hi);  // written by the kernel ahead
   float x[PER_LANE];
   float sum = 0.0f;
 #pragma unroll
-  for (int j = 0; j < PER_LANE; ++j) {
-    x[j] = to_float(src[lane + 32 * j]);
-    sum += x[j] * x[j];
+  for (int j = 0; j < V; ++j) {
+    x[j] = to_float(in_lo.v[j]);
+    x[V + j] = to_float(in_hi.v[j]);
   }
+#pragma unroll
+  for (int j = 0; j < PER_LANE; ++j) sum += x[j] * x[j];
   if (weight != nullptr) {
     sum = warp_sum(sum);
     const float scale = rsqrtf(sum / static_cast<float>(HD) + eps);
@@ -174,15 +201,21 @@ qk_norm_rope_cache_warp_kernel(
   }
   if (cos_table != nullptr) {
 #pragma unroll
-    for (int j = 0; j < PER_LANE / 2; ++j) {
-      // element lane + 32 j (below HALF) and its partner HALF further, x[j + PER_LANE / 2]
-      const float lo = x[j], hi = x[j + PER_LANE / 2];
+    for (int j = 0; j < V; ++j) {
+      // element V lane + j (below HALF) and its partner HALF further, x[V + j]
+      const float lo = x[j], hi = x[V + j];
       x[j] = lo * c[j] - hi * sn[j];
-      x[j + PER_LANE / 2] = hi * c[j] + lo * sn[j];
+      x[V + j] = hi * c[j] + lo * sn[j];
     }
   }
+  Values out_lo, out_hi;
 #pragma unroll
-  for (int j = 0; j < PER_LANE; ++j) dst[lane + 32 * j] = from_float<T>(x[j]);
+  for (int j = 0; j < V; ++j) {
+    out_lo.v[j] = from_float<T>(x[j]);
+    out_hi.v[j] = from_float<T>(x[V + j]);
+  }
+  *dst_lo = out_lo;
+  *dst_hi = out_hi;
 }
 
 }  // namespace mxb
@@ -197,7 +230,20 @@ MXB_API int mxb_qk_norm_rope_cache(
     int page_tokens, int num_pages, float eps, int dtype, int* status, cudaStream_t stream) {
   if (tokens <= 0) return 0;
   if (rotary_dim < 0 || rotary_dim > head_dim || (rotary_dim & 1)) return static_cast<int>(cudaErrorInvalidValue);
-  if ((head_dim == 64 || head_dim == 128 || head_dim == 256) && (cos_table == nullptr || rotary_dim == head_dim)) {
+  // The warp kernel moves head_dim / 64 values per access: rows and bases must be aligned to that.
+  const int per_access = head_dim >= 64 ? head_dim / 64 : 1;
+  const size_t access = static_cast<size_t>(per_access) * (dtype == kF32 ? 4 : 2);
+  auto aligned = [&](const void* p, long long stride) {
+    return p == nullptr || (reinterpret_cast<uintptr_t>(p) % access == 0 && (stride * (dtype == kF32 ? 4 : 2)) % access == 0);
+  };
+  auto float_aligned = [&](const float* p) {  // tables are read head_dim / 64 floats at a time
+    return p == nullptr || reinterpret_cast<uintptr_t>(p) % (static_cast<size_t>(per_access) * 4) == 0;
+  };
+  const bool vector_ok = aligned(q_in, q_stride) && aligned(k_in, k_stride) && aligned(v_in, v_stride) &&
+                         aligned(q_out, 0) && aligned(cache, 0) && float_aligned(q_weight) &&
+                         float_aligned(k_weight) && float_aligned(cos_table) && float_aligned(sin_table);
+  if ((head_dim == 64 || head_dim == 128 || head_dim == 256) && (cos_table == nullptr || rotary_dim == head_dim) &&
+      vector_ok) {
     const long long items = static_cast<long long>(tokens) * (heads + 2 * kv_heads);
     const unsigned blocks = static_cast<unsigned>((items + 7) / 8);
     cudaError_t launch_status = cudaSuccess;

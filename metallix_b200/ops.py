@@ -346,6 +346,9 @@ def flash_prefill_tile() -> int:
     return _fn("mxb_flash_prefill_tile")()
 
 
+PROMPT_KERNEL = "auto"   # what flash_prefill's "auto" means: "auto", "tcgen05" or "mma" (for comparisons)
+
+
 def flash_prefill_tcgen05_supported(head_dim: int, heads: int, kv_heads: int, page_tokens: int,
                                     dtype: torch.dtype) -> bool:
     """Whether the tcgen05 prompt kernel takes this head layout and page size."""
@@ -377,6 +380,8 @@ def flash_prefill(q: torch.Tensor, cache: torch.Tensor, out: torch.Tensor, block
     tiles = tile_request.numel()
     _need(tile_start.numel() == tiles and tile_length.numel() == tiles, "tile lists differ in length")
     _need(positions.numel() == tokens, "one position per token")
+    if kernel == "auto":
+        kernel = PROMPT_KERNEL
     _need(kernel in ("auto", "tcgen05", "mma"), f"unknown prompt-attention kernel {kernel!r}")
     tcgen05 = flash_prefill_tcgen05_supported(head_dim, heads, kv_heads, page_tokens, q.dtype)
     _need(tcgen05 or kernel != "tcgen05",
