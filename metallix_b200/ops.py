@@ -48,6 +48,8 @@ _SIGNATURES = {
     "mxb_gemm_simple": [_P, _I, _P, _P, _I, _I, _I, _I, _L, _L, _L, _P],
     "mxb_gemm_skinny": [_P, _I, _P, _P, _I, _I, _I, _L, _L, _L, _I, _P],
     "mxb_gemm_skinny_supported": [_I, _I, _I, _L, _L],
+    "mxb_gemm_stream": [_P, _I, _P, _P, _I, _I, _I, _L, _L, _L, _I, _P, _P],
+    "mxb_gemm_stream_supported": [_I, _I, _I, _L, _L, _I],
     "mxb_gemm_tcgen05": [_P, _P, _P, _I, _I, _I, _L, _L, _L, _I, _P, _P],
     "mxb_gemm_tcgen05_supported": [_I, _I, _I, _L, _L],
     "mxb_silu_mul": [_P, _P, _I, _L, _I, _P],
@@ -487,14 +489,43 @@ def gemm_skinny_supported(a: torch.Tensor, w: torch.Tensor) -> bool:
     return bool(_fn("mxb_gemm_skinny_supported")(a.shape[0], w.shape[0], a.shape[1], a.stride(0), w.stride(0)))
 
 
+STREAM_COLUMNS = 16384   # wider outputs (the vocabulary) keep the load-based kernel: enough blocks hide its latency
+
+
+def gemm_stream_supported(a: torch.Tensor, w: torch.Tensor, swiglu: bool = False) -> bool:
+    """Whether the bulk-copy weight-streaming kernel takes a [m, k] times w
+    [n, k] transposed: bfloat16, at most 16 rows, k a multiple of 16, rows on
+    16-byte boundaries, a block's rows of w and a fitting shared memory."""
+    if a.dtype != torch.bfloat16 or w.dtype != torch.bfloat16 or a.dim() != 2 or w.dim() != 2:
+        return False
+    if a.stride(1) != 1 or w.stride(1) != 1 or a.data_ptr() % 16 or w.data_ptr() % 16:
+        return False
+    n = w.shape[0]
+    if swiglu and n % 2:
+        return False
+    return bool(_fn("mxb_gemm_stream_supported")(a.shape[0], n, a.shape[1], a.stride(0), w.stride(0),
+                                                 n // 2 if swiglu else 0))
+
+
+def gemm_skinny_takes(a: torch.Tensor, w: torch.Tensor, swiglu: bool = False) -> bool:
+    """Whether one of the two weight-streaming kernels takes the call."""
+    return gemm_stream_supported(a, w, swiglu) or gemm_skinny_supported(a, w)
+
+
 def gemm_skinny(a: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype = torch.bfloat16,
-                swiglu: bool = False, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+                swiglu: bool = False, out: Optional[torch.Tensor] = None, kernel: str = "auto") -> torch.Tensor:
     """a [m <= 64, k] times w [n, k] transposed, reading w once. With
     ``swiglu`` w holds gate rows then up rows and the result is
-    silu(gate) * up, [m, n / 2]."""
+    silu(gate) * up, [m, n / 2]. ``kernel``: "stream" (rows of w by bulk copy
+    into shared memory, m <= 16), "load" (16-byte loads into registers) or
+    "auto" (stream where it takes the shape and the output is not wider than
+    STREAM_COLUMNS)."""
     _need(a.is_cuda and w.is_cuda and a.shape[1] == w.shape[1], "operands do not fit a @ w.T on a CUDA device")
-    _need(gemm_skinny_supported(a, w), "the weight-streaming kernel takes bfloat16, at most 64 rows, "
-          "k a multiple of 32 and rows on 16-byte boundaries")
+    _need(kernel in ("auto", "stream", "load"), f"unknown weight-streaming kernel {kernel!r}")
+    streams = kernel != "load" and gemm_stream_supported(a, w, swiglu)
+    _need(streams or kernel != "stream", "the bulk-copy kernel does not take this shape")
+    _need(streams or gemm_skinny_supported(a, w), "the weight-streaming kernels take bfloat16, at most 64 rows, "
+          "k a multiple of 32 (16 up to 16 rows) and rows on 16-byte boundaries")
     _need(out_dtype in (torch.bfloat16, torch.float32), "out_dtype must be bfloat16 or float32")
     m, k = a.shape
     n = w.shape[0]
@@ -503,6 +534,11 @@ def gemm_skinny(a: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype = torch
     if out is None:
         out = torch.empty((m, columns), dtype=out_dtype, device=a.device)
     _need(out.shape == (m, columns) and out.dtype == out_dtype and out.stride(1) == 1, "out does not fit")
+    if streams and (kernel == "stream" or columns <= STREAM_COLUMNS or not gemm_skinny_supported(a, w)):
+        _call("mxb_gemm_stream", out.data_ptr(), _CODES[out_dtype], a.data_ptr(), w.data_ptr(), m, n, k,
+              a.stride(0), w.stride(0), out.stride(0), columns if swiglu else 0,
+              status_word(a.device).data_ptr(), _stream())
+        return out
     _call("mxb_gemm_skinny", out.data_ptr(), _CODES[out_dtype], a.data_ptr(), w.data_ptr(), m, n, k,
           a.stride(0), w.stride(0), out.stride(0), columns if swiglu else 0, _stream())
     return out
@@ -524,7 +560,7 @@ def gemm_bf16(a: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype = torch.b
     _need(out_dtype in (torch.bfloat16, torch.float32), "out_dtype must be bfloat16 or float32")
     if backend == "simple":
         return gemm_simple(a, w, out_dtype=out_dtype, out=out)
-    if (backend == "skinny" or (backend == "auto" and a.shape[0] <= SKINNY_ROWS)) and gemm_skinny_supported(a, w):
+    if (backend == "skinny" or (backend == "auto" and a.shape[0] <= SKINNY_ROWS)) and gemm_skinny_takes(a, w):
         return gemm_skinny(a, w, out_dtype=out_dtype, out=out)
     _need(backend != "skinny", "the weight-streaming kernel does not take this shape")
     if backend == "tcgen05":

@@ -29,7 +29,7 @@ class SwiGLU:
 
     def forward(self, x: torch.Tensor, ctx: StepContext) -> torch.Tensor:
         if (x.shape[0] <= ops.SKINNY_ROWS and self.gate_up.backend in ("auto", "skinny")
-                and ops.gemm_skinny_supported(x, self.gate_up.weight)):
+                and ops.gemm_skinny_takes(x, self.gate_up.weight, swiglu=True)):
             # A decode step: gate, up and the activation in one pass over the weights.
             return self.down.forward(ops.gemm_skinny(x, self.gate_up.weight, swiglu=True))
         if self.gate_up.dtype == torch.bfloat16 and self.gate_up.backend in ("auto", "tcgen05"):

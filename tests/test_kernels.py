@@ -505,32 +505,63 @@ def test_gemm_bf16(ops, backend, m, n, k):
     assert np.abs(out16.cpu().double().numpy() - ref).max() < 0.02 * np.abs(ref).max()
 
 
+@pytest.mark.parametrize("kernel", ["load", "stream"])
 @pytest.mark.parametrize("m", [1, 3, 8, 9, 16, 31, 64])
-@pytest.mark.parametrize("n, k", [(331, 96), (1024, 3072), (40, 32), (4096, 1024)])
-def test_gemm_skinny(ops, m, n, k):
+@pytest.mark.parametrize("n, k", [(331, 96), (1024, 3072), (40, 32), (4096, 1024), (200, 6144), (136, 48)])
+def test_gemm_skinny(ops, m, n, k, kernel):
+    """Both weight-streaming kernels: "load" (16-byte loads into registers, up
+    to 64 rows, k a multiple of 32) and "stream" (bulk copies into shared
+    memory, up to 16 rows, k a multiple of 16)."""
     rng = np.random.default_rng(m + n)
     a, w = rng.normal(size=(m, k)), rng.normal(size=(n, k)) * 0.05
     a_d, w_d = dev(a, torch.bfloat16), dev(w, torch.bfloat16)
-    assert ops.gemm_skinny_supported(a_d, w_d)
+    if kernel == "stream":
+        # at most 16 rows, and 8 rows of w beside the 8 or 16 rows of a within 200 KiB of shared memory
+        takes = m <= 16 and (8 + (8 if m <= 8 else 16)) * (2 * k + 16) <= 200 * 1024
+        assert ops.gemm_stream_supported(a_d, w_d) == takes
+        if not takes:
+            with pytest.raises(ops.KernelError, match="bulk-copy kernel"):
+                ops.gemm_skinny(a_d, w_d, kernel="stream")
+            return
+    else:
+        assert ops.gemm_skinny_supported(a_d, w_d) == (k % 32 == 0)
+        if k % 32:
+            return
     ref = rounded(a, torch.bfloat16) @ rounded(w, torch.bfloat16).T
-    out32 = ops.gemm_skinny(a_d, w_d, torch.float32)
+    out32 = ops.gemm_skinny(a_d, w_d, torch.float32, kernel=kernel)
+    ops.check_status("cuda")
     assert np.abs(out32.cpu().double().numpy() - ref).max() < 1e-4 * np.sqrt(k / 32)
-    out16 = ops.gemm_skinny(a_d, w_d, torch.bfloat16)
+    out16 = ops.gemm_skinny(a_d, w_d, torch.bfloat16, kernel=kernel)
     assert (np.abs(out16.cpu().double().numpy() - ref) <= 2.0 ** -8 * np.abs(ref) + 1e-4).all()
     # a row's result does not depend on how many other rows ride along
-    alone = ops.gemm_skinny(a_d[m - 1:m].contiguous(), w_d, torch.float32)
+    alone = ops.gemm_skinny(a_d[m - 1:m].contiguous(), w_d, torch.float32, kernel=kernel)
     assert torch.equal(alone[0], out32[m - 1])
-    assert torch.equal(ops.gemm_bf16(a_d, w_d, torch.float32, backend="skinny"), out32)
-    if m <= ops.SKINNY_ROWS:   # what "auto" picks for so few rows
-        assert torch.equal(ops.gemm_bf16(a_d, w_d, torch.float32, backend="auto"), out32)
+    # what gemm_bf16 picks: the bulk-copy kernel where it takes the call, else the other
+    picked = "stream" if ops.gemm_stream_supported(a_d, w_d) else "load"
+    if kernel == picked and ops.gemm_skinny_supported(a_d, w_d):
+        assert torch.equal(ops.gemm_bf16(a_d, w_d, torch.float32, backend="skinny"), out32)
+        if m <= ops.SKINNY_ROWS:   # what "auto" picks for so few rows
+            assert torch.equal(ops.gemm_bf16(a_d, w_d, torch.float32, backend="auto"), out32)
 
 
-@pytest.mark.parametrize("m", [1, 8, 24, 64])
-def test_gemm_skinny_swiglu(ops, m):
+def test_gemm_stream_refuses_what_does_not_fit(ops):
+    wide = dev(np.zeros((16, 6144)), torch.bfloat16)          # 16 rows of x and 8 of W at k = 6144 exceed shared memory
+    assert not ops.gemm_stream_supported(wide, dev(np.zeros((64, 6144)), torch.bfloat16))
+    assert ops.gemm_stream_supported(wide[:8].contiguous(), dev(np.zeros((64, 6144)), torch.bfloat16))
+    assert not ops.gemm_stream_supported(dev(np.zeros((4, 40)), torch.bfloat16), dev(np.zeros((8, 40)), torch.bfloat16))
+
+
+@pytest.mark.parametrize("kernel", ["load", "stream"])
+@pytest.mark.parametrize("m", [1, 8, 13, 24, 64])
+def test_gemm_skinny_swiglu(ops, m, kernel):
     rng = np.random.default_rng(m)
     inter, k = 3 * 56, 96
     a, w = rng.normal(size=(m, k)), rng.normal(size=(2 * inter, k)) * 0.3
-    out = ops.gemm_skinny(dev(a, torch.bfloat16), dev(w, torch.bfloat16), swiglu=True)
+    if kernel == "stream" and m > 16:
+        assert not ops.gemm_stream_supported(dev(a, torch.bfloat16), dev(w, torch.bfloat16), swiglu=True)
+        return
+    out = ops.gemm_skinny(dev(a, torch.bfloat16), dev(w, torch.bfloat16), swiglu=True, kernel=kernel)
+    ops.check_status("cuda")
     gate_up = rounded(rounded(a, torch.bfloat16) @ rounded(w, torch.bfloat16).T, torch.bfloat16)
     g, u = gate_up[:, :inter], gate_up[:, inter:]
     ref = g / (1 + np.exp(-g)) * u
