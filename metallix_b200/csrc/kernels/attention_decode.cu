@@ -449,59 +449,57 @@ paged_attention_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, const __n
 
 // out[token, head, :] = sum_s exp(m_s - M) acc_s / sum_s exp(m_s - M) l_s over
 // the splits that hold keys of this token, in ascending order. One block per
-// (token, head): the first threads take one split each to find M and the
-// weights, then every thread sums one or two of the head's values over the
-// splits, always in split order, with all its loads in flight together.
-constexpr int kMergeThreads = 128;
-constexpr int kMergeSplits = 64;  // splits handled per round
+// (token, head), one thread per value of the head. A thread fetches the
+// maxima, the sums and its own value of up to kMergeSplits splits in one go
+// (all loads in flight together: one trip to memory instead of one for the
+// maxima, one for the weights and one for the values) and finds the weights
+// itself; longer contexts take further rounds with the running maximum
+// carried along.
+constexpr int kMergeSplits = 32;  // splits per round: 4,096 keys
 
 template <typename T>
-__global__ void __launch_bounds__(kMergeThreads)
+__global__ void __launch_bounds__(256)
 paged_attention_merge_kernel(const float* __restrict__ partial, T* __restrict__ out,
                              const int* __restrict__ row_token, const int* __restrict__ positions,
                              int rows, int heads, int head_dim, int max_splits, int window) {
   chain_release();
-  __shared__ float s_weight[kMergeSplits];
-  __shared__ float s_reduce[8];
-  const int row = blockIdx.x, head = blockIdx.y;
-  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int row = blockIdx.x, head = blockIdx.y, d = threadIdx.x;
   const int token = row_token[row];  // the step's integers are not written by any kernel of the step
-  if (token < 0) return;
+  if (token < 0 || d >= head_dim) return;
   const int pos = positions[token];
   const int first_key = window > 0 ? max(0, pos - window + 1) : 0;
   const int first_split = first_key / kSplitKeys, last_split = pos / kSplitKeys;
   const int splits = last_split - first_split + 1;
-  const float* base = partial + ((static_cast<size_t>(row) * heads + head) * max_splits + first_split) * (head_dim + 2);
+  const int stride = head_dim + 2;
+  const float* base = partial + ((static_cast<size_t>(row) * heads + head) * max_splits + first_split) * stride;
   chain_wait();
   base = behind_wait(base);  // the partial results are written by the kernel ahead of this one
-  // The maximum over all splits.
-  float m = kDecodeMinusHuge;
-  for (int s = tid; s < splits; s += kMergeThreads)
-    m = fmaxf(m, base[static_cast<size_t>(s) * (head_dim + 2) + head_dim]);
-  m = warp_max(m);
-  if (lane == 0) s_reduce[warp] = m;
-  __syncthreads();
-  m = fmaxf(fmaxf(s_reduce[0], s_reduce[1]), fmaxf(s_reduce[2], s_reduce[3]));
-  float acc0 = 0.0f, acc1 = 0.0f, l = 0.0f;  // head_dim <= 256: values tid and tid + 128
+  float m = kDecodeMinusHuge, acc = 0.0f, l = 0.0f;
   for (int chunk = 0; chunk < splits; chunk += kMergeSplits) {
-    const int here = min(kMergeSplits, splits - chunk);
-    __syncthreads();
-    if (tid < here)
-      s_weight[tid] = expf(base[static_cast<size_t>(chunk + tid) * (head_dim + 2) + head_dim] - m);
-    __syncthreads();
-#pragma unroll 8
-    for (int s = 0; s < here; ++s) {
-      const float* p = base + static_cast<size_t>(chunk + s) * (head_dim + 2);
-      const float weight = s_weight[s];
-      if (tid < head_dim) acc0 += weight * p[tid];
-      if (tid + kMergeThreads < head_dim) acc1 += weight * p[tid + kMergeThreads];
-      l += weight * p[head_dim + 1];
+    float ms[kMergeSplits], ls[kMergeSplits], values[kMergeSplits];
+#pragma unroll
+    for (int j = 0; j < kMergeSplits; ++j) {
+      const bool live = chunk + j < splits;
+      const float* p = base + static_cast<size_t>(live ? chunk + j : 0) * stride;
+      ms[j] = live ? p[head_dim] : kDecodeMinusHuge;
+      ls[j] = live ? p[head_dim + 1] : 0.0f;
+      values[j] = live ? p[d] : 0.0f;
     }
+    float round_max = m;
+#pragma unroll
+    for (int j = 0; j < kMergeSplits; ++j) round_max = fmaxf(round_max, ms[j]);
+    const float carry = expf(m - round_max);  // what earlier rounds gathered, on the new maximum
+    acc *= carry;
+    l *= carry;
+#pragma unroll
+    for (int j = 0; j < kMergeSplits; ++j) {
+      const float weight = expf(ms[j] - round_max);
+      acc = fmaf(weight, values[j], acc);
+      l = fmaf(weight, ls[j], l);
+    }
+    m = round_max;
   }
-  const float inv = 1.0f / l;
-  T* dst = out + (static_cast<size_t>(token) * heads + head) * head_dim;
-  if (tid < head_dim) dst[tid] = from_float<T>(acc0 * inv);
-  if (tid + kMergeThreads < head_dim) dst[tid + kMergeThreads] = from_float<T>(acc1 * inv);
+  out[(static_cast<size_t>(token) * heads + head) * head_dim + d] = from_float<T>(acc / l);
 }
 
 template <typename T, int HD, int G>
@@ -527,7 +525,7 @@ static int launch_decode(const void* q, const void* cache, void* out, float* par
       scale, status);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return static_cast<int>(e);
-  return static_cast<int>(launch_chained(paged_attention_merge_kernel<T>, dim3(rows, heads), dim3(kMergeThreads), 0,
+  return static_cast<int>(launch_chained(paged_attention_merge_kernel<T>, dim3(rows, heads), dim3(HD <= 64 ? 64 : (HD <= 128 ? 128 : 256)), 0,
                                          stream, static_cast<const float*>(partial), static_cast<T*>(out),
                                          row_token, positions, rows, heads, HD, max_splits, window));
 }
@@ -551,7 +549,7 @@ static int launch_decode_mma(const void* q, const void* cache, void* out, float*
                                  kv_heads, page_tokens, num_pages, max_splits, window, scale, status);
   if (e != cudaSuccess) return static_cast<int>(e);
   return static_cast<int>(launch_chained(paged_attention_merge_kernel<__nv_bfloat16>, dim3(rows, heads),
-                                         dim3(kMergeThreads), 0, stream, static_cast<const float*>(partial),
+                                         dim3(HD <= 64 ? 64 : (HD <= 128 ? 128 : 256)), 0, stream, static_cast<const float*>(partial),
                                          static_cast<__nv_bfloat16*>(out), row_token, positions, rows, heads,
                                          HD, max_splits, window));
 }
