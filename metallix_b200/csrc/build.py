@@ -128,8 +128,11 @@ def _locked(path: str):
 def _build_kernels(out_dir: str) -> str:
     sources = _sources(_KERNEL_DIR, (".cu",))
     headers = _sources(_KERNEL_DIR, (".cuh", ".h"))
-    tag = _digest(sources + headers, NVCC_FLAGS)
-    library = os.path.join(out_dir, "_mxb_kernels.so")
+    timeline = os.environ.get("METALLIX_B200_TIMELINE", "") not in ("", "0")
+    flags = NVCC_FLAGS + (["-DMXB_TIMELINE"] if timeline else [])
+    tag = _digest(sources + headers, flags)
+    # the build that records the kernels' timeline is a library of its own
+    library = os.path.join(out_dir, "_mxb_kernels_timeline.so" if timeline else "_mxb_kernels.so")
     stamp = library + ".stamp"
     lock = _locked(library)
     try:
@@ -142,12 +145,12 @@ def _build_kernels(out_dir: str) -> str:
             def compile_one(source: str) -> str:
                 # Objects are keyed by their own source, so an edit of one
                 # file recompiles one file.
-                own = _digest([source] + headers, NVCC_FLAGS)[:16]
+                own = _digest([source] + headers, flags)[:16]
                 target = os.path.join(object_dir,
                                       os.path.basename(source)[:-3] + f".{own}.o")
                 if not os.path.exists(target):
                     partial = target + f".{os.getpid()}.tmp"
-                    _run([nvcc, *NVCC_FLAGS, "-I", _KERNEL_DIR, "-c", source, "-o", partial],
+                    _run([nvcc, *flags, "-I", _KERNEL_DIR, "-c", source, "-o", partial],
                          os.path.basename(source))
                     os.replace(partial, target)
                 return target

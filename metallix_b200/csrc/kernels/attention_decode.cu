@@ -669,3 +669,5 @@ MXB_API int mxb_paged_attention_decode_noalloc(const void* q, const void* cache,
                                     row_request, positions, rows, heads, kv_heads, head_dim, page_tokens,
                                     num_pages, splits, window, scale, dtype, status, stream);
 }
+
+MXB_TIMELINE_EXPORT(mxb_timeline_attention)

@@ -68,7 +68,44 @@ inline int ceil_div(int a, int b) { return (a + b - 1) / b; }
 // chain_release() as early as it likes to let its own successor start. What
 // runs before the wait (index arithmetic, fetching weights no kernel writes)
 // overlaps the predecessor. Without the launch attribute both are no-ops.
+#ifndef MXB_TIMELINE
 __device__ __forceinline__ void chain_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+#define MXB_TIMELINE_EXPORT(name)
+#else
+// A build with -DMXB_TIMELINE (METALLIX_B200_TIMELINE=1) records when the
+// first thread of the first block of every chained kernel got past its wait,
+// i.e. when the kernel ahead of it had finished: the differences are the time
+// each kernel holds the chain, measured on the device while the step runs as
+// it always does (captured graph, overlapped launches). Every source file has
+// counters of its own, read through the function MXB_TIMELINE_EXPORT defines.
+constexpr unsigned kTimelineSlots = 8192;
+static __device__ unsigned long long timeline_times[kTimelineSlots];
+static __device__ unsigned timeline_count;
+__device__ __forceinline__ void chain_wait() {
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+  if (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && threadIdx.x == 0) {
+    unsigned long long now;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(now));
+    const unsigned slot = atomicAdd(&timeline_count, 1u);
+    if (slot < kTimelineSlots) timeline_times[slot] = now;
+  }
+}
+// int name(unsigned long long* out, int reset): copies the recorded times (ns)
+// to `out` (room for 8192, may be null), optionally clears them, returns how many.
+#define MXB_TIMELINE_EXPORT(name)                                                                        \
+  extern "C" __attribute__((visibility("default"))) int name(unsigned long long* out, int reset) {       \
+    unsigned count = 0;                                                                                  \
+    cudaMemcpyFromSymbol(&count, mxb::timeline_count, sizeof(count));                                    \
+    if (count > mxb::kTimelineSlots) count = mxb::kTimelineSlots;                                        \
+    if (out != nullptr && count > 0)                                                                     \
+      cudaMemcpyFromSymbol(out, mxb::timeline_times, count * sizeof(unsigned long long));                \
+    if (reset) {                                                                                         \
+      const unsigned zero = 0;                                                                           \
+      cudaMemcpyToSymbol(mxb::timeline_count, &zero, sizeof(zero));                                      \
+    }                                                                                                    \
+    return static_cast<int>(count);                                                                      \
+  }
+#endif
 __device__ __forceinline__ void chain_release() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 
 // A kernel that launch_chained() starts lives before the kernel ahead of it

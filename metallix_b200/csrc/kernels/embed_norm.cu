@@ -230,3 +230,5 @@ MXB_API int mxb_add(float* x, const void* delta, int delta_dtype, long long coun
 // Turns the overlap of consecutive kernels (programmatic dependent launch) on
 // or off for every kernel of this library that supports it.
 MXB_API void mxb_set_chained_launches(int enabled) { mxb::g_chained_launches = enabled != 0; }
+
+MXB_TIMELINE_EXPORT(mxb_timeline_norms)

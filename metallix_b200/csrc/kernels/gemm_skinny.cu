@@ -222,3 +222,5 @@ MXB_API int mxb_gemm_skinny(void* out, int out_dtype, const void* x, const void*
   LAUNCH(8);
 #undef LAUNCH
 }
+
+MXB_TIMELINE_EXPORT(mxb_timeline_gemm_load)

@@ -233,3 +233,5 @@ MXB_API int mxb_gemm_stream(void* out, int out_dtype, const void* x, const void*
   LAUNCH(2);
 #undef LAUNCH
 }
+
+MXB_TIMELINE_EXPORT(mxb_timeline_gemm_stream)

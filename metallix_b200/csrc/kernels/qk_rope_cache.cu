@@ -282,3 +282,5 @@ MXB_API int mxb_qk_norm_rope_cache(
     return static_cast<int>(cudaErrorInvalidValue);
   return static_cast<int>(cudaGetLastError());
 }
+
+MXB_TIMELINE_EXPORT(mxb_timeline_qk_rope)

@@ -7,7 +7,9 @@
 
 ``decode``: ``--batch`` requests with ``--prompt-len`` tokens each, then a few
 decode steps (eagerly, so that a profiler sees every kernel; ``--graphs``
-replays captured graphs and prints the time per step instead). ``prefill``:
+replays captured graphs and prints the time per step instead; ``--timeline``,
+with METALLIX_B200_TIMELINE=1 in the environment, prints how long each kernel
+of a layer holds the chain of one replayed step). ``prefill``:
 one prompt of ``--prompt-len`` tokens, three times. ``gemm``: the tcgen05
 product against the library's on one shape. ``attention``: the two prompt
 attention kernels alone on one prompt of ``--prompt-len`` tokens over
@@ -34,6 +36,7 @@ def main(argv=None) -> int:
     parser.add_argument("--prompt-len", type=int, default=2048)
     parser.add_argument("--steps", type=int, default=4)
     parser.add_argument("--graphs", action="store_true")
+    parser.add_argument("--timeline", action="store_true")
     parser.add_argument("--m", type=int, default=2048)
     parser.add_argument("--n", type=int, default=4096)
     parser.add_argument("--k", type=int, default=1024)
@@ -105,7 +108,8 @@ def main(argv=None) -> int:
     config = Qwen3Config.from_dict(dict(QWEN3_0_6B, num_hidden_layers=args.layers))
     pages = args.batch * (-(-(args.prompt_len + 64) // 16)) + 64
     engine = Engine.from_random(config, 0, dtype="bfloat16", page_tokens=16, num_pages=pages,
-                                max_requests=args.batch + 2, max_context=4096, cuda_graphs=args.graphs)
+                                max_requests=args.batch + 2, max_context=4096,
+                                cuda_graphs=args.graphs or args.timeline)   # the timeline is of the step as it serves
     rng = np.random.default_rng(0)
     if args.mode == "prefill":
         ids = rng.integers(0, config.vocab_size, size=args.prompt_len).tolist()
@@ -121,6 +125,28 @@ def main(argv=None) -> int:
         for _ in range(args.steps):
             engine.step([StepEntry(name, [int(rng.integers(0, config.vocab_size))], [0]) for name in names])
         torch.cuda.synchronize()
+        if args.timeline:
+            ops.timeline(reset=True)
+            engine.step([StepEntry(name, [5], [0]) for name in names])
+            torch.cuda.synchronize()
+            events = ops.timeline()
+            print(f"{len(events)} chained kernels, {(events[-1][0] - events[0][0]) / 1e3:.1f} us from the first to the last")
+            # one layer is nine chained kernels: norm, qkv, q/k norm + rotation, attention, merge, o, norm, gate/up, down
+            period = 9
+            names_of_layer = ["norm", "qkv product", "q/k norm, rotation, cache", "attention (split keys)",
+                              "merge of splits", "o product", "norm", "gate/up product + SwiGLU", "down product"]
+            first = 1   # after the embedding
+            sums = [0.0] * period
+            layers = (len(events) - 1 - first) // period
+            for layer in range(layers):
+                for k in range(period):
+                    i = first + layer * period + k
+                    sums[k] += (events[i + 1][0] - events[i][0]) / 1e3
+            print("| kernel of a layer | source | us until the next kernel may go on (mean over layers) |")
+            print("|---|---|---|")
+            for k in range(period):
+                print(f"| {names_of_layer[k]} | {events[first + k][1]} | {sums[k] / max(layers, 1):.2f} |")
+            print(f"| a layer | | {sum(sums) / max(layers, 1):.2f} |")
         if args.graphs:
             start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             start.record()

@@ -144,6 +144,28 @@ def set_chained_launches(enabled: bool) -> None:
     _fn("mxb_set_chained_launches")(1 if enabled else 0)
 
 
+TIMELINE_SOURCES = ("norms", "gemm_load", "gemm_stream", "qk_rope", "attention")
+
+
+def timeline(reset: bool = True):
+    """[(nanoseconds, source)] in time order: when each chained kernel
+    launched since the last reset got past the wait for the kernel ahead of
+    it. Needs the library built with METALLIX_B200_TIMELINE=1 in the
+    environment (a build of its own, next to the usual one)."""
+    library = build.kernels()
+    events = []
+    for source in TIMELINE_SOURCES:
+        function = getattr(library, f"mxb_timeline_{source}", None)
+        if function is None:
+            raise KernelError("this build records no timeline: set METALLIX_B200_TIMELINE=1 before the first use")
+        function.argtypes = [ctypes.c_void_p, ctypes.c_int]
+        function.restype = ctypes.c_int
+        buffer = (ctypes.c_ulonglong * 8192)()
+        count = function(buffer, 1 if reset else 0)
+        events.extend((int(buffer[i]), source) for i in range(count))
+    return sorted(events)
+
+
 def status_word(device) -> torch.Tensor:
     """The int32 word kernels set bits in instead of trapping."""
     word = _status.get(device)

@@ -697,3 +697,9 @@ def test_nucleus_mask(ops, top_p, top_k):
     for r in range(6):
         ref = plain.nucleus_mask(logits[r], float(temperature[r]), top_p, top_k or None)
         assert np.array_equal(mask[r], ref), (r, mask[r].sum(), ref.sum())
+
+
+def test_timeline_needs_a_build_of_its_own(ops):
+    """The usual library records no timeline and says how to get one."""
+    with pytest.raises(ops.KernelError, match="METALLIX_B200_TIMELINE"):
+        ops.timeline()
