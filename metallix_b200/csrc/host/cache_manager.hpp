@@ -167,15 +167,18 @@ class CacheManager {
   // Drops positions that were reserved but not committed (a failed step).
   void rollback(int64_t id) {
     Request& r = get(id);
+    bool shrank = false;
     for (size_t g = 0; g < groups_.size(); ++g) {
       int64_t keep = ceil_div(r.computed, groups_[g].page_tokens);
       while (static_cast<int64_t>(r.tables[g].size()) > keep) {
         int page = r.tables[g].back();
         r.tables[g].pop_back();
         if (page >= 0) give_back(static_cast<int>(g), page, id);
+        shrank = true;
       }
     }
     r.reserved = r.computed;
+    if (shrank) r.epoch = ++admissions_;  // a mirror of the longer table is stale now
   }
 
   // Everything the request holds goes back: pages last-first, then the slot

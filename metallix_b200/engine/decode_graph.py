@@ -34,6 +34,8 @@ class _Bucket:
         self.logits: Optional[torch.Tensor] = None
         self.layout: Dict[str, slice] = {}
         self.kernels = 0                              # our kernel launches inside the graph
+        self.staging: List[dict] = []                 # pinned host buffers for the step's integers
+        self.turn = 0
 
 
 class DecodeGraphs:
@@ -100,28 +102,40 @@ class DecodeGraphs:
         slots = {g.index: s[bucket.layout[f"slots{g.index}"]] for g in cache.groups}
         return lambda entry, write: cache.view(entry, write, tables, slots)
 
-    def _host_fill(self, bucket: _Bucket, rows: Sequence, out: np.ndarray) -> None:
+    def _host_constants(self, bucket: _Bucket, out: np.ndarray) -> None:
+        """What never changes in a bucket's integers, with every row padding."""
+        size, layout, cache = bucket.size, bucket.layout, self.engine.cache
+        index = np.arange(size, dtype=np.int32)
+        out[:] = 0
+        for name in ("token_request", "tile_request", "tile_start", "wanted", "decode_request"):
+            out[layout[name]] = index
+        out[layout["decode_token"]] = -1
+        for g in cache.groups:
+            out[layout[f"slots{g.index}"]] = -1
+            out[layout[f"table{g.index}"]] = -1
+
+    def _host_fill(self, bucket: _Bucket, rows: Sequence, out: np.ndarray, held_rows: Optional[list] = None,
+                   filled: int = 0) -> None:
         """rows: (manager id, token id, position, state slot) of the live
-        requests; fills one step's integers."""
+        requests; fills one step's integers into ``out``, which holds the
+        constants and, in its first ``filled`` rows, an earlier step.
+        ``held_rows[row]`` remembers whose block table a row of ``out`` holds,
+        so that a table is copied again only when it has changed."""
         size, layout, cache = bucket.size, bucket.layout, self.engine.cache
         manager, page_tokens = self.engine.manager, cache.page_tokens
         live = len(rows)
-        index = np.arange(size, dtype=np.int32)
-        out[layout["ids"]] = 0
-        out[layout["positions"]] = 0
-        out[layout["token_request"]] = index
-        out[layout["request_slots"]] = 0
-        out[layout["tile_request"]] = index
-        out[layout["tile_start"]] = index
-        out[layout["tile_length"]] = 0
-        out[layout["tile_length"]][:live] = 1
-        out[layout["wanted"]] = index
-        out[layout["decode_token"]] = -1
-        out[layout["decode_token"]][:live] = index[:live]
-        out[layout["decode_request"]] = index
-        ids, positions, request_slots = (out[layout[k]] for k in ("ids", "positions", "request_slots"))
-        for g in cache.groups:
-            out[layout[f"slots{g.index}"]] = -1
+        ids, positions, request_slots, tile_length, decode_token = (
+            out[layout[k]] for k in ("ids", "positions", "request_slots", "tile_length", "decode_token"))
+        tile_length[:live] = 1
+        decode_token[:live] = np.arange(live, dtype=np.int32)
+        if filled > live:   # rows an earlier, larger step left behind become padding again
+            tile_length[live:filled] = 0
+            decode_token[live:filled] = -1
+            ids[live:filled] = 0
+            positions[live:filled] = 0
+            request_slots[live:filled] = 0
+            for g in cache.groups:
+                out[layout[f"slots{g.index}"]][live:filled] = -1
         for row, (rid, token, position, slot) in enumerate(rows):
             ids[row], positions[row], request_slots[row] = token, position, slot
             pages = -(-(position + 1) // page_tokens)
@@ -136,12 +150,15 @@ class DecodeGraphs:
                     held.append(padded)
                 if len(self._host_tables) > 4 * manager.max_requests():
                     self._host_tables.clear()   # requests that left long ago
-                self._host_tables[rid] = (epoch, pages, held)
-            else:
-                held = mirror[2]
+                mirror = self._host_tables[rid] = (epoch, pages, held)
+            held = mirror[2]
+            copy_table = held_rows is None or held_rows[row] is not held
+            if held_rows is not None:
+                held_rows[row] = held
             for g in cache.groups:
-                table = out[layout[f"table{g.index}"]]
-                table[row * self.table_width:(row + 1) * self.table_width] = held[g.index]
+                if copy_table:
+                    table = out[layout[f"table{g.index}"]]
+                    table[row * self.table_width:(row + 1) * self.table_width] = held[g.index]
                 out[layout[f"slots{g.index}"]][row] = \
                     held[g.index][position // page_tokens] * page_tokens + position % page_tokens
 
@@ -153,8 +170,15 @@ class DecodeGraphs:
         bucket.layout = self._layout(size)
         total = bucket.layout["end"].start
         host = np.zeros(total, dtype=np.int32)
-        self._host_fill(bucket, [], host)   # all padding: nothing is read or written
+        self._host_constants(bucket, host)   # all padding: nothing is read or written
         bucket.static = torch.from_numpy(host).to(engine.device)
+        # Two pinned staging buffers taken in turn, each with the constants in
+        # place; an event says when the copy out of a buffer is done.
+        for _ in range(2):
+            pinned = torch.empty(total, dtype=torch.int32, pin_memory=True)
+            pinned.numpy()[:] = host
+            bucket.staging.append({"pinned": pinned, "array": pinned.numpy(), "copied": None,
+                                   "filled": 0, "held": [None] * size})
         ctx, views = self._context(bucket), self._views(bucket)
         ids, wanted = bucket.static[bucket.layout["ids"]], bucket.static[bucket.layout["wanted"]]
         stream = torch.cuda.Stream(device=engine.device)
@@ -184,19 +208,30 @@ class DecodeGraphs:
         return bucket
 
     # -------------------------------------------------------------------- run
-    def run(self, rows: Sequence) -> torch.Tensor:
+    def run(self, rows: Sequence, fed_ids: Optional[torch.Tensor] = None) -> torch.Tensor:
         """rows: (manager id, token id, position, state slot). Returns float32
         logits [len(rows), vocab]: a view of the graph's output that the next
-        replay of the same bucket overwrites."""
+        replay of the same bucket overwrites. ``fed_ids`` (int32, on the
+        device, one per row) replaces the rows' token ids without the host
+        ever seeing them: the tokens an earlier step picked."""
         from .. import ops
         size = self.bucket_for(len(rows))
         bucket = self.buckets.get(size)
         if bucket is None:
             bucket = self.buckets[size] = self._capture(size)
         total = bucket.layout["end"].start
-        packed = torch.empty(total, dtype=torch.int32, pin_memory=True)
-        self._host_fill(bucket, rows, packed.numpy())
-        bucket.static.copy_(packed, non_blocking=True)
+        stage = bucket.staging[bucket.turn]
+        bucket.turn ^= 1
+        if stage["copied"] is not None:
+            stage["copied"].synchronize()   # the copy of two steps ago out of this buffer (long done)
+        self._host_fill(bucket, rows, stage["array"], stage["held"], stage["filled"])
+        stage["filled"] = len(rows)
+        bucket.static.copy_(stage["pinned"], non_blocking=True)
+        if stage["copied"] is None:
+            stage["copied"] = torch.cuda.Event()
+        stage["copied"].record()
+        if fed_ids is not None:
+            bucket.static[bucket.layout["ids"]][:len(rows)].copy_(fed_ids[:len(rows)], non_blocking=True)
         bucket.graph.replay()
         ops.count_launches(bucket.kernels)
         self.h2d_bytes = total * 4

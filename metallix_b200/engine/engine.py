@@ -192,10 +192,68 @@ class Engine:
             return logits
         return logits[torch.tensor(wanted, device=self.device)]
 
+    # ------------------------------------------------- a decode step run ahead
+    def ahead_possible(self) -> bool:
+        """Whether a decode step may be launched before the tokens it runs on
+        have reached the host, to be confirmed or dropped afterwards: only
+        when dropping leaves no trace, i.e. every cache entry is pages without
+        a window (a page written in vain is simply written again) and no part
+        keeps state of its own."""
+        if self.graphs is None:
+            return False
+        return all(need is None or (need.kind == "kv_pages" and not need.window) or need.kind == "none"
+                   for need in self.cache.needs)
+
+    def launch_ahead(self, requests: Sequence[int], fed_ids: torch.Tensor) -> Optional[torch.Tensor]:
+        """One decoded token for each of the managed ``requests``, the token
+        ids taken from ``fed_ids`` on the device (int32, same order). Reserves
+        the positions and launches; commits nothing. Returns the logits, or
+        None (and changes nothing) where such a step cannot run now.
+        ``commit_ahead`` or ``drop_ahead`` must follow."""
+        manager = self.manager
+        if not self.ahead_possible() or self.graphs.bucket_for(len(requests)) is None:
+            return None
+        for rid in requests:
+            if (not manager.has(rid) or manager.computed(rid) == 0 or manager.reserved(rid) != manager.computed(rid)
+                    or manager.computed(rid) + 1 > self.max_context):
+                return None
+        if not manager.fits([(rid, 1) for rid in requests]):
+            return None
+        for rid in requests:
+            manager.reserve(rid, 1)
+        try:
+            rows = [(rid, 0, manager.computed(rid), manager.slot(rid)) for rid in requests]
+            return self.graphs.run(rows, fed_ids=fed_ids)
+        except BaseException:
+            self.drop_ahead(requests)
+            raise
+
+    def commit_ahead(self, requests: Sequence[int]) -> None:
+        for rid in requests:
+            self.manager.commit(rid, 1)
+        self.steps += 1
+
+    def drop_ahead(self, requests: Sequence[int]) -> None:
+        """The step launched ahead does not count: its positions are given
+        back (what it wrote is written again by the step that replaces it)."""
+        manager = self.manager
+        for rid in requests:
+            if manager.has(rid) and manager.reserved(rid) != manager.computed(rid):
+                manager.rollback(rid)
+
     def check(self) -> None:
         """Raises if any kernel since the last check refused its input
         (synchronises the device)."""
         ops.check_status(self.device)
+
+    def check_later(self) -> None:
+        """Queues the read of the kernels' status behind what has been
+        launched; ``check_now`` raises on it after the caller has synchronised
+        anyway (by reading tokens or logits)."""
+        ops.fetch_status(self.device)
+
+    def check_now(self) -> None:
+        ops.raise_status(self.device)
 
     # ------------------------------------------------------------------ pieces
     def _validate(self, entries: List[StepEntry]) -> None:
@@ -212,9 +270,14 @@ class Engine:
             count = len(entry.tokens)
             if count == 0:
                 raise StepError(f"request {entry.request!r} brings no tokens")
-            tokens = np.asarray(entry.tokens)
-            if tokens.dtype.kind not in "iu" or tokens.min() < 0 or tokens.max() >= vocab:
-                raise StepError(f"request {entry.request!r}: token ids must lie in 0..{vocab - 1}")
+            if count == 1:   # a decoded token: no array needed
+                token = entry.tokens[0]
+                if isinstance(token, bool) or not isinstance(token, (int, np.integer)) or not 0 <= token < vocab:
+                    raise StepError(f"request {entry.request!r}: token ids must lie in 0..{vocab - 1}")
+            else:
+                tokens = np.asarray(entry.tokens)
+                if tokens.dtype.kind not in "iu" or tokens.min() < 0 or tokens.max() >= vocab:
+                    raise StepError(f"request {entry.request!r}: token ids must lie in 0..{vocab - 1}")
             for index in entry.want:
                 if not 0 <= index < count:
                     raise StepError(f"request {entry.request!r}: want index {index} outside its {count} tokens")

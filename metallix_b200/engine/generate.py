@@ -40,6 +40,8 @@ class GenerationStats:
     decode_tokens: int = 0
     prefill_tokens: int = 0
     preemptions: int = 0
+    ahead_kept: int = 0       # steps launched before their tokens reached the host, and kept
+    ahead_dropped: int = 0    # ... and dropped because the scheduler decided otherwise
     step_ms: List[float] = field(default_factory=list)
 
 
@@ -47,7 +49,7 @@ class Generator:
     """Continuous batching over one engine."""
 
     def __init__(self, engine: Engine, max_num_seqs: int = 8, max_tokens_per_step: int = 8192,
-                 prefill_chunk: int = 0):
+                 prefill_chunk: int = 0, run_ahead: bool = True):
         host = build.host()
         self.engine = engine
         self.host = host
@@ -58,6 +60,12 @@ class Generator:
         self._params: Dict[int, SamplingParams] = {}
         self._started: Dict[int, float] = {}
         self._last: Dict[int, float] = {}
+        self._limits: Dict[int, int] = {}          # max_new_tokens by request
+        self.run_ahead = run_ahead
+        self._ahead = None                         # (plan, logits) of a step already launched
+        self._planned = None                       # a plan made but not yet run
+        self._host_tokens: Optional[torch.Tensor] = None
+        self._tokens_copied: Optional[torch.cuda.Event] = None
         self._timing: Dict[int, GenerationResult] = {}
 
     def add(self, prompt: Sequence[int], max_new_tokens: int, params: SamplingParams = SamplingParams(),
@@ -78,6 +86,7 @@ class Generator:
                                  self.host.SamplingParams(params.temperature, params.seed,
                                                           params.top_p, params.top_k, code))
         self._params[rid] = params
+        self._limits[rid] = int(max_new_tokens)
         self._timing[rid] = GenerationResult(input_ids=prompt, generated_ids=[], finish_reason="")
         self._started[rid] = time.perf_counter()
         return rid
@@ -90,32 +99,71 @@ class Generator:
 
     def step(self) -> List:
         """One scheduler iteration; returns the events (id, token, finished,
-        finish_reason) of this step."""
-        plan = self.scheduler.plan()
-        self.stats.preemptions += len(plan.preempted)
-        if not plan.entries:
-            return []
+        finish_reason) of this step.
+
+        While every running request is decoding, the next step is launched
+        *ahead*: right after this step's tokens have been picked on the device,
+        and before they have reached the host, the engine launches the step
+        the scheduler will most likely ask for next (the same requests, one
+        position further), fed with those tokens on the device. The host then
+        reads the tokens, lets the scheduler finish and plan, and keeps the
+        step launched ahead if the plan is the one foreseen; otherwise (a
+        request stopped at an end-of-sequence token, pages ran out, a request
+        arrived) it is dropped and the plan runs as usual. What a request
+        generates is the same either way; the device no longer waits for the
+        host between two steps."""
+        if self._ahead is not None:
+            plan, logits = self._ahead      # launched during the previous call
+            self._ahead = None
+        else:
+            if self._planned is not None:
+                plan, self._planned = self._planned, None
+            else:
+                plan = self.scheduler.plan()
+                self.stats.preemptions += len(plan.preempted)
+            if not plan.entries:
+                return []
+            logits = self._launch(plan)
         started = time.perf_counter()
-        entries, rows, positions = [], [], []
-        for entry in plan.entries:
-            count = len(entry.tokens)
-            entries.append(StepEntry(request=entry.id, tokens=entry.tokens,
-                                     want=(count - 1,) if entry.wants_token else (), managed=True))
-            if entry.wants_token:
-                rows.append(self._params[entry.id])
-                positions.append(entry.generated_position)
+        rows = [self._params[e.id] for e in plan.entries if e.wants_token]
+        positions = [e.generated_position for e in plan.entries if e.wants_token]
+        foreseen = None
         try:
-            logits = self.engine.step(entries)
             tokens: List[int] = []
             if logits is not None:
-                tokens = pick(logits, rows, positions).tolist()
-            self.engine.check()
+                picked = pick(logits, rows, positions)
+                self.engine.check_later()                       # the status word rides behind the tokens
+                host_tokens = self._token_buffer(len(rows))
+                host_tokens.copy_(picked, non_blocking=True)
+                self._tokens_copied.record()
+                foreseen = self._launch_ahead(plan, picked)     # the device goes on while the host reads
+                self._tokens_copied.synchronize()
+                tokens = host_tokens.tolist()
+                self.engine.check_now()
+            else:
+                self.engine.check()
             if any(t < 0 for t in tokens):
                 raise RuntimeError("non-finite logits")
         except Exception as error:  # the requests of this step leave with the error
+            if foreseen is not None:
+                self.engine.drop_ahead(foreseen[0])
             self.scheduler.fail_plan(plan, f"step failed: {error}")
             raise
         events = self.scheduler.update(plan, tokens)
+        if foreseen is not None:
+            requests, ahead_logits = foreseen
+            following = self.scheduler.plan()
+            self.stats.preemptions += len(following.preempted)
+            if (not following.preempted and not following.failed
+                    and [e.id for e in following.entries] == requests
+                    and all(len(e.tokens) == 1 and e.wants_token for e in following.entries)):
+                self.engine.commit_ahead(requests)
+                self._ahead = (following, ahead_logits)
+                self.stats.ahead_kept += 1
+            else:
+                self.engine.drop_ahead(requests)
+                self._planned = following                       # runs in the next call, the usual way
+                self.stats.ahead_dropped += 1
         now = time.perf_counter()
         self.stats.steps += 1
         self.stats.decode_tokens += plan.decode_tokens
@@ -129,6 +177,42 @@ class Generator:
                 result.decode_ms.append((now - self._last[event.id]) * 1e3)
             self._last[event.id] = now
         return events
+
+    def _launch(self, plan) -> Optional[torch.Tensor]:
+        entries = []
+        for entry in plan.entries:
+            count = len(entry.tokens)
+            entries.append(StepEntry(request=entry.id, tokens=entry.tokens,
+                                     want=(count - 1,) if entry.wants_token else (), managed=True))
+        try:
+            return self.engine.step(entries)
+        except Exception as error:
+            self.scheduler.fail_plan(plan, f"step failed: {error}")
+            raise
+
+    def _token_buffer(self, count: int) -> torch.Tensor:
+        if self._host_tokens is None or self._host_tokens.numel() < count:
+            self._host_tokens = torch.empty(max(count, 64), dtype=torch.int32, pin_memory=True)
+            self._tokens_copied = torch.cuda.Event()
+        return self._host_tokens[:count]
+
+    def _launch_ahead(self, plan, picked: torch.Tensor):
+        """Launches the step that follows ``plan`` if it can be foreseen: all
+        of the plan's requests decode, none of them reaches its token limit
+        with the token just picked, and nobody waits to be admitted. Returns
+        (requests, logits) or None."""
+        if not self.run_ahead or self.scheduler.num_waiting() or not self.engine.ahead_possible():
+            return None
+        requests = []
+        for entry in plan.entries:
+            if not entry.wants_token:
+                return None
+            # generated_position is the index of the token being picked now
+            if entry.generated_position + 1 >= self._limits[entry.id]:
+                return None
+            requests.append(entry.id)
+        logits = self.engine.launch_ahead(requests, picked)
+        return None if logits is None else (requests, logits)
 
     def result(self, rid: int) -> GenerationResult:
         info = self.scheduler.request(rid)
@@ -152,14 +236,15 @@ def generate(engine: Engine, prompts: Sequence[Sequence[int]], max_new_tokens: i
              temperature: float = 0.0, seed: int = 0, top_p: float = 1.0, top_k: int = 0,
              sampler: str = "icdf", eos_ids: Optional[Sequence[int]] = None,
              ignore_eos: bool = False, max_num_seqs: int = 8, max_tokens_per_step: int = 8192,
-             prefill_chunk: int = 0) -> List[GenerationResult]:
+             prefill_chunk: int = 0, run_ahead: bool = True) -> List[GenerationResult]:
     """Generates for every prompt (lists of token ids) and returns the results
     in the prompts' order. ``temperature`` 0 is greedy; otherwise request i
     draws from (seed, stream i). ``eos_ids`` defaults to the configuration's."""
     if eos_ids is None:
         eos_ids = tuple(getattr(engine.config, "eos_token_ids", ()) or ())
     generator = Generator(engine, max_num_seqs=max_num_seqs,
-                          max_tokens_per_step=max_tokens_per_step, prefill_chunk=prefill_chunk)
+                          max_tokens_per_step=max_tokens_per_step, prefill_chunk=prefill_chunk,
+                          run_ahead=run_ahead)
     ids = [generator.add(prompt, max_new_tokens,
                          SamplingParams(temperature=temperature, seed=seed, stream=index,
                                         top_p=top_p, top_k=top_k, sampler=sampler),

@@ -177,6 +177,32 @@ def status_word(device) -> torch.Tensor:
     return word
 
 
+_status_host = {}
+
+
+def fetch_status(device) -> None:
+    """Queues a copy of the status word to pinned host memory on the current
+    stream; ``raise_status`` reads it once the stream has been synchronised
+    (by reading the step's results, say), which saves a synchronisation of
+    its own."""
+    word = status_word(device)
+    host = _status_host.get(device)
+    if host is None:
+        host = _status_host[device] = torch.zeros(1, dtype=torch.int32, pin_memory=True)
+    host.copy_(word, non_blocking=True)
+
+
+def raise_status(device) -> None:
+    """Raises on what the last ``fetch_status`` copy brought (the caller has
+    synchronised since); clears the device word then."""
+    host = _status_host.get(device)
+    value = int(host[0]) if host is not None else 0
+    if value:
+        status_word(device).zero_()
+        reasons = [text for bit, text in STATUS_BITS.items() if value & bit]
+        raise KernelError("a kernel refused its input: " + "; ".join(reasons))
+
+
 def check_status(device) -> None:
     """Reads the status word (synchronises) and raises on any bit; clears it."""
     word = status_word(device)

@@ -86,9 +86,15 @@ def test_rollback_drops_uncommitted(host):
     m.commit(1, 6)
     m.reserve(1, 9)
     assert m.free_pages(0) == 12
+    epoch = m.epoch(1)
     m.rollback(1)
     assert m.reserved(1) == 6 and m.free_pages(0) == 14 and len(m.table(1, 0)) == 2
+    assert m.epoch(1) != epoch          # whoever mirrors the longer table must fetch it again
     m.check_invariants()
+    m.reserve(1, 1)                     # within the pages it holds: the table does not change
+    epoch = m.epoch(1)
+    m.rollback(1)
+    assert m.epoch(1) == epoch
 
 
 def test_window_gives_pages_back(host):

@@ -128,6 +128,67 @@ def test_eos_stops_and_is_reported(model_folders):
     assert ignored.generated_ids == free_run and ignored.finish_reason == "length"
 
 
+def test_steps_launched_ahead_change_nothing(model_folders):
+    """While all requests decode, the generator launches the next step before
+    the tokens of this one have reached the host. The tokens are those of a
+    generator that never does; a request that stops at an end-of-sequence
+    token, one that reaches its limit earlier than the others, one that
+    arrives later and a pool that runs out of pages each make it drop or skip
+    a step launched ahead."""
+    from metallix_b200.engine import Engine
+    from metallix_b200.engine.generate import Generator
+    from metallix_b200.sampling import SamplingParams
+    folder, config, tensors, page = model_folders["B"]
+    prompts = [random_ids(60 + i, n, config["vocab_size"]) for i, n in enumerate((9, 40, 21, 5))]
+    limits = (30, 17, 30, 24)
+
+    def run(run_ahead, num_pages, stop=(), late=False):
+        engine = Engine.from_folder(folder, dtype="bfloat16", page_tokens=page, num_pages=num_pages)
+        assert engine.ahead_possible()
+        generator = Generator(engine, max_num_seqs=4, run_ahead=run_ahead)
+        ids = []
+        for index, (prompt, limit) in enumerate(zip(prompts, limits)):
+            if late and index == 3:
+                continue
+            ids.append(generator.add(prompt, limit, SamplingParams(temperature=0.8, seed=3, stream=index),
+                                     eos_ids=stop))
+        steps = 0
+        while not generator.idle():
+            generator.step()
+            steps += 1
+            if late and steps == 9:
+                ids.append(generator.add(prompts[3], limits[3], SamplingParams(temperature=0.8, seed=3, stream=3),
+                                         eos_ids=stop))
+        engine.check()
+        assert engine.manager.live_requests() == 0 and engine.manager.free_pages(0) == num_pages
+        engine.manager.check_invariants()
+        return [generator.result(rid) for rid in ids], generator.stats
+
+    plain_run, plain_stats = run(False, 64)
+    assert plain_stats.ahead_kept == 0 and plain_stats.ahead_dropped == 0
+    ahead_run, stats = run(True, 64)
+    assert [r.generated_ids for r in ahead_run] == [r.generated_ids for r in plain_run]
+    assert stats.ahead_kept > 10 and stats.steps == plain_stats.steps
+    # an end-of-sequence token in the middle of a request: the step launched ahead is dropped
+    stop = (plain_run[0].generated_ids[11],)
+    stopped_plain, _ = run(False, 64, stop=stop)
+    stopped_ahead, stats = run(True, 64, stop=stop)
+    assert [(r.generated_ids, r.finish_reason) for r in stopped_ahead] == \
+           [(r.generated_ids, r.finish_reason) for r in stopped_plain]
+    assert any(r.finish_reason == "eos" for r in stopped_ahead) and stats.ahead_dropped >= 1
+    # a request that arrives while the others decode
+    late_plain, _ = run(False, 64, late=True)
+    late_ahead, stats = run(True, 64, late=True)
+    assert [r.generated_ids for r in late_ahead] == [r.generated_ids for r in late_plain]
+    assert stats.ahead_kept > 5
+    # so few pages that requests lose theirs while decoding and are computed again
+    tight_plain, tight_plain_stats = run(False, 14)
+    tight_ahead, stats = run(True, 14)
+    assert tight_plain_stats.preemptions > 0 and stats.preemptions > 0
+    assert [r.generated_ids for r in tight_ahead] == [r.generated_ids for r in plain_run]
+    assert [r.generated_ids for r in tight_plain] == [r.generated_ids for r in plain_run]
+
+
 def test_command_line(model_folders, tmp_path):
     folder, config, tensors, page = model_folders["A"]
     prompt = random_ids(51, 7, config["vocab_size"])
