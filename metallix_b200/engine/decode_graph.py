@@ -14,6 +14,7 @@ the width of the longest context the engine allows.
 """
 from __future__ import annotations
 
+import contextlib
 import gc
 import weakref
 from typing import Dict, List, Optional, Sequence
@@ -24,6 +25,21 @@ import torch
 from ..parts.registry import StepContext
 
 BUCKETS = (1, 2, 4, 8, 16, 24, 32, 48, 64, 96, 128, 192, 256)
+
+
+@contextlib.contextmanager
+def capture_quietly(graph: torch.cuda.CUDAGraph, pool):
+    """Captures into ``graph`` with the garbage collector off: freeing another
+    engine's graph or device memory in the middle would invalidate the capture."""
+    collecting = gc.isenabled()
+    gc.collect()
+    gc.disable()
+    try:
+        with torch.cuda.graph(graph, pool=pool):
+            yield
+    finally:
+        if collecting:
+            gc.enable()
 
 
 class _Bucket:
@@ -190,17 +206,8 @@ class DecodeGraphs:
         torch.cuda.synchronize(engine.device)
         graph = torch.cuda.CUDAGraph()
         before = ops.launch_count()
-        # No garbage collection while the stream captures: freeing another
-        # engine's graph or device memory in the middle would invalidate it.
-        collecting = gc.isenabled()
-        gc.collect()
-        gc.disable()
-        try:
-            with torch.cuda.graph(graph, pool=self.pool):
-                bucket.logits = engine.model.forward(ids, ctx, views, wanted)
-        finally:
-            if collecting:
-                gc.enable()
+        with capture_quietly(graph, self.pool):
+            bucket.logits = engine.model.forward(ids, ctx, views, wanted)
         bucket.kernels = ops.launch_count() - before
         if self.pool is None:
             self.pool = graph.pool()

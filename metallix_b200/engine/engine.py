@@ -31,6 +31,7 @@ from .model import DecoderModel
 _DTYPES = {"bfloat16": torch.bfloat16, "bf16": torch.bfloat16, "float32": torch.float32,
            "fp32": torch.float32, torch.bfloat16: torch.bfloat16, torch.float32: torch.float32}
 ATTENTION_TILE = 16  # query tokens per tile of the general kernel (csrc/kernels/attention_tile.cu)
+STEP_GRAPHS = 8       # how many shapes of general steps keep a captured graph
 WIDE_TILE = 128      # and of the tensor-core prompt kernels (csrc/kernels/attention_prefill*.cu)
 
 
@@ -87,6 +88,9 @@ class Engine:
         self.manager = self.cache.manager
         from .decode_graph import DecodeGraphs
         self.graphs = DecodeGraphs(self) if cuda_graphs and DecodeGraphs.usable(self.model) else None
+        # Graphs of general steps by shape (see _run), under the same condition.
+        self._step_graphs: Optional[Dict] = {} if self.graphs is not None else None
+        self._shapes_seen: Dict = {}
         self._ids: Dict[Hashable, int] = {}   # request name -> manager id
         self._next_id = 1 << 40               # above any id a scheduler hands out
         self.steps = 0
@@ -302,6 +306,14 @@ class Engine:
             raise StepError(f"out of cache pages: the step does not fit (free pages per group: {free})")
 
     def _run(self, entries: List[StepEntry]) -> Optional[torch.Tensor]:
+        """A general step: any mix of portions of prompts and decoded tokens.
+
+        The step's integers (token ids, positions, tiles, block tables, slots)
+        go to the device as one packed buffer. A step whose *shape* (the token
+        counts of its entries, how many logits are wanted) has been seen before
+        replays a CUDA graph captured for that shape, with its integers copied
+        into the graph's buffer: a prompt cut into equal portions, or the same
+        batch again, then costs one launch instead of some two hundred."""
         manager, cache = self.manager, self.cache
         page_tokens = cache.page_tokens
         counts = [len(e.tokens) for e in entries]
@@ -350,6 +362,12 @@ class Engine:
             tile_request.append(row)
             tile_start.append(begin)
             tile_length.append(count)
+        # A step that may be replayed as a graph has block tables of the full
+        # width, so that its buffer has one layout whatever the contexts are.
+        shape_key = (tuple(counts), len(wanted))
+        graphed = self._step_graphs is not None and (
+            shape_key in self._step_graphs or self._shapes_seen.get(shape_key, 0) >= 1)
+        full_width = -(-self.max_context // page_tokens)
         # One packed int32 buffer, one copy to the device.
         pieces = [token_ids, positions, token_request, request_slots,
                   np.asarray(tile_request, dtype=np.int32), np.asarray(tile_start, dtype=np.int32),
@@ -361,7 +379,7 @@ class Engine:
         shapes = [None] * len(pieces)
         for group in cache.groups:
             tables = group_tables[group.index]
-            width = max(len(t) for t in tables)
+            width = full_width if graphed else max(len(t) for t in tables)
             table = np.full((rows, width), -1, dtype=np.int32)
             slots = np.empty(total, dtype=np.int32)
             for row, pages in enumerate(tables):
@@ -378,28 +396,66 @@ class Engine:
         for piece, size in zip(pieces, sizes):
             packed_np[cursor:cursor + size] = piece
             cursor += size
-        on_device = packed.to(self.device, non_blocking=True)
-        views, cursor = [], 0
-        for size, shape in zip(sizes, shapes):
-            view = on_device[cursor:cursor + size]
-            views.append(view.view(shape) if shape is not None else view)
-            cursor += size
-        (d_ids, d_positions, d_token_request, d_request_slots, d_tile_request, d_tile_start,
-         d_tile_length, d_wanted, d_decode_token, d_decode_request, d_wide_request, d_wide_start,
-         d_wide_length) = views[:13]
-        tables = {g.index: views[13 + 2 * g.index] for g in cache.groups}
-        slots = {g.index: views[14 + 2 * g.index] for g in cache.groups}
-
-        ctx = StepContext(
-            device=self.device, dtype=self.dtype, num_tokens=total, num_requests=rows,
-            positions=d_positions, token_request=d_token_request, request_slots=d_request_slots,
-            request_offsets=[int(v) for v in offsets], request_positions=starts,
-            tile_request=d_tile_request, tile_start=d_tile_start, tile_length=d_tile_length,
-            multi_tiles=multi_tiles, decode_token=d_decode_token if decode_token else None,
-            decode_request=d_decode_request if decode_token else None, longest_context=longest,
-            wide_tile_request=d_wide_request, wide_tile_start=d_wide_start,
-            wide_tile_length=d_wide_length)
         self._keep = packed  # the pinned buffer must outlive the asynchronous copy
-        return self.model.forward(
-            d_ids, ctx, lambda entry, write: cache.view(entry, write, tables, slots),
-            d_wanted if wanted else None)
+
+        def forward(on_device: torch.Tensor, longest_context: int) -> Optional[torch.Tensor]:
+            views, cursor = [], 0
+            for size, shape in zip(sizes, shapes):
+                view = on_device[cursor:cursor + size]
+                views.append(view.view(shape) if shape is not None else view)
+                cursor += size
+            (d_ids, d_positions, d_token_request, d_request_slots, d_tile_request, d_tile_start,
+             d_tile_length, d_wanted, d_decode_token, d_decode_request, d_wide_request, d_wide_start,
+             d_wide_length) = views[:13]
+            tables = {g.index: views[13 + 2 * g.index] for g in cache.groups}
+            slots = {g.index: views[14 + 2 * g.index] for g in cache.groups}
+            ctx = StepContext(
+                device=self.device, dtype=self.dtype, num_tokens=total, num_requests=rows,
+                positions=d_positions, token_request=d_token_request, request_slots=d_request_slots,
+                request_offsets=[int(v) for v in offsets], request_positions=starts,
+                tile_request=d_tile_request, tile_start=d_tile_start, tile_length=d_tile_length,
+                multi_tiles=multi_tiles, decode_token=d_decode_token if decode_token else None,
+                decode_request=d_decode_request if decode_token else None, longest_context=longest_context,
+                wide_tile_request=d_wide_request, wide_tile_start=d_wide_start,
+                wide_tile_length=d_wide_length)
+            return self.model.forward(
+                d_ids, ctx, lambda entry, write: cache.view(entry, write, tables, slots),
+                d_wanted if wanted else None)
+
+        if not graphed:
+            if self._step_graphs is not None:
+                self._shapes_seen[shape_key] = self._shapes_seen.get(shape_key, 0) + 1
+                if len(self._shapes_seen) > 4096:
+                    self._shapes_seen.clear()
+            return forward(packed.to(self.device, non_blocking=True), longest)
+        return self._replay_step(shape_key, packed, forward)
+
+    def _replay_step(self, shape_key, packed: torch.Tensor, forward) -> Optional[torch.Tensor]:
+        """Replays (after capturing it, the first time) the graph of a general
+        step of this shape with the integers in ``packed``."""
+        from .decode_graph import capture_quietly
+        held = self._step_graphs.get(shape_key)
+        if held is None:
+            static = packed.to(self.device)
+            stream = torch.cuda.Stream(device=self.device)
+            stream.wait_stream(torch.cuda.current_stream(self.device))
+            with torch.cuda.stream(stream):
+                forward(static, self.max_context)   # libraries and lazily loaded kernels settle before the capture
+            torch.cuda.current_stream(self.device).wait_stream(stream)
+            torch.cuda.synchronize(self.device)
+            graph = torch.cuda.CUDAGraph()
+            before = ops.launch_count()
+            pool = self.graphs.pool if self.graphs is not None else None
+            with capture_quietly(graph, pool):
+                logits = forward(static, self.max_context)
+            if self.graphs is not None and self.graphs.pool is None:
+                self.graphs.pool = graph.pool()
+            held = {"graph": graph, "static": static, "logits": logits, "kernels": ops.launch_count() - before}
+            if len(self._step_graphs) >= STEP_GRAPHS:
+                self._step_graphs.pop(next(iter(self._step_graphs)))   # the oldest shape makes room
+            self._step_graphs[shape_key] = held
+        held["static"].copy_(packed, non_blocking=True)
+        held["graph"].replay()
+        ops.count_launches(held["kernels"])
+        return held["logits"]
+

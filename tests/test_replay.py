@@ -113,6 +113,44 @@ def test_long_decoding(model_folders, name, dtype):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["C", "D"])
+def test_equal_portions_replay_a_graph(model_folders, name, dtype):
+    """A step whose shape has been seen before replays a captured graph with
+    the new integers: a prompt in equal portions (each further along, with a
+    longer block table), then two requests side by side in portions of two
+    sizes, match the plain implementation and what an engine without graphs
+    gives."""
+    from metallix_b200.engine import StepEntry
+    folder, config, tensors, page = model_folders[name]
+    ids = [random_ids(90 + i, 480, config["vocab_size"]) for i in range(2)]
+    reference = [plain.forward_logits(config, tensors, row) for row in ids]
+    limit, cut_limit = bounds(dtype)
+    outputs = {}
+    for graphs in (True, False):
+        engine = make_engine(model_folders, name, dtype, cuda_graphs=graphs)
+        seen = []
+        for first in range(0, 240, 48):          # five steps of one shape
+            logits = engine.step([StepEntry("a", ids[0][first:first + 48], [0, 47])])
+            seen.append(logits.cpu().double().numpy())
+            assert np.abs(seen[-1] - reference[0][[first, first + 47]]).max() < limit, (graphs, first)
+        engine.release("a")
+        for first in range(0, 480, 80):          # six steps of another: two requests, 50 and 30 tokens
+            a, b = first * 5 // 8, first * 3 // 8
+            logits = engine.step([StepEntry("a", ids[0][a:a + 50], [49]), StepEntry("b", ids[1][b:b + 30], [0, 29])])
+            seen.append(logits.cpu().double().numpy())
+            want = np.stack([reference[0][a + 49], reference[1][b], reference[1][b + 29]])
+            assert np.abs(seen[-1] - want).max() < limit, (graphs, first)
+        engine.check()
+        if graphs:
+            assert set(engine._step_graphs) == {((48,), 2), ((50, 30), 3)}
+        outputs[graphs] = seen
+        engine.release_all()
+        engine.manager.check_invariants()
+    drift = max(float(np.abs(x - y).max()) for x, y in zip(outputs[True], outputs[False]))
+    assert drift < cut_limit
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_the_first_tokens_of_a_sequence(model_folders, dtype):
     """Position 0 alone, then 1, then 2: no earlier key, a single-token prompt."""
     from metallix_b200.engine import StepEntry
