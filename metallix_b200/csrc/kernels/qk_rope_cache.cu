@@ -95,13 +95,14 @@ __global__ void qk_norm_rope_cache_kernel(
 // V values of type T moved as one access of V * sizeof(T) bytes.
 template <typename T, int V> struct alignas(sizeof(T) * V) Pack { T v[V]; };
 
-// The same work with one warp per (token, head) and no shared memory, for
-// head sizes 64, 128 and 256 with the rotation over the whole head: with
-// V = head_dim / 64, lane l holds elements V l .. V l + V - 1 of the lower
-// half and the same of the upper half, so the rotation partner of element i
-// (i +- head_dim / 2) sits in the same lane and every access is one of
-// V * sizeof(T) bytes, a warp covering whole contiguous lines.
-template <typename T, int PER_LANE>
+// The same work without shared memory, for head sizes 64, 128 and 256 with
+// the rotation over the whole head. Every access is 16 bytes: a lane holds V
+// = 16 / sizeof(T) consecutive values of the lower half of a head and the
+// same of the upper half, so the rotation partner of element i (i +- head_dim
+// / 2) sits in the same lane; head_dim / (2 V) lanes make up a head, a warp
+// takes 32 / that many heads at once, and the sum of squares runs over a
+// head's lanes only.
+template <typename T, int HD>
 __global__ void __launch_bounds__(256)
 qk_norm_rope_cache_warp_kernel(
     const T* __restrict__ q_in, const T* __restrict__ k_in, const T* __restrict__ v_in,
@@ -110,16 +111,23 @@ qk_norm_rope_cache_warp_kernel(
     const float* __restrict__ q_weight, const float* __restrict__ k_weight,
     const float* __restrict__ cos_table, const float* __restrict__ sin_table, int table_positions,
     int tokens, int heads, int kv_heads, int page_tokens, int num_pages, float eps, int* status) {
-  constexpr int HD = PER_LANE * 32;
+  constexpr int V = 16 / static_cast<int>(sizeof(T));
   constexpr int HALF = HD / 2;
+  constexpr int LANES = HALF / V;          // lanes of a head
+  constexpr int HEADS = 32 / LANES;        // heads of a warp
+  static_assert(LANES >= 1 && LANES <= 32 && (LANES & (LANES - 1)) == 0, "a head's lanes must divide a warp");
+  using Values = Pack<T, V>;
+  using Floats = Pack<float, 4>;
   chain_release();
   // Up to chain_wait(): only the step's integers, the norm weights and the
   // cos/sin tables, none of which a kernel of this step writes.
-  const int lane = threadIdx.x & 31;
+  const int lane = threadIdx.x & 31, sub = lane % LANES;
   const int per_token = heads + 2 * kv_heads;
-  const long long item = static_cast<long long>(blockIdx.x) * 8 + (threadIdx.x >> 5);
-  if (item >= static_cast<long long>(tokens) * per_token) return;
-  const int t = static_cast<int>(item / per_token), h = static_cast<int>(item % per_token);
+  const long long total = static_cast<long long>(tokens) * per_token;
+  const long long item = (static_cast<long long>(blockIdx.x) * 8 + (threadIdx.x >> 5)) * HEADS + lane / LANES;
+  // Lanes without work stay to the end: the sums below shuffle within a head's lanes.
+  bool active = item < total;
+  const int t = active ? static_cast<int>(item / per_token) : 0, h = active ? static_cast<int>(item % per_token) : 0;
   const bool is_q = h < heads;
   const bool is_k = !is_q && h < heads + kv_heads;
   const int kv = is_q ? 0 : (is_k ? h - heads : h - heads - kv_heads);
@@ -128,63 +136,73 @@ qk_norm_rope_cache_warp_kernel(
                       : v_in + t * v_stride + static_cast<long long>(kv) * HD;
   T* dst = nullptr;
   if (is_q) {
-    if (q_out == nullptr) return;
-    dst = q_out + (static_cast<size_t>(t) * heads + h) * HD;
-  } else {
-    if (slots == nullptr || cache == nullptr) return;
+    if (q_out == nullptr) active = false;
+    else dst = q_out + (static_cast<size_t>(t) * heads + h) * HD;
+  } else if (slots == nullptr || cache == nullptr) {
+    active = false;
+  } else if (active) {
     const int slot = slots[t];
-    if (slot < 0) return;
     const int page = slot / page_tokens, row = slot - page * page_tokens;
-    if (page >= num_pages) {
-      if (lane == 0) atomicOr(status, kStatusBadSlot);
-      return;
+    if (slot < 0) {
+      active = false;
+    } else if (page >= num_pages) {
+      if (sub == 0) atomicOr(status, kStatusBadSlot);
+      active = false;
+    } else {
+      dst = cache + (((static_cast<size_t>(page) * 2 + (is_k ? 0 : 1)) * kv_heads + kv) * page_tokens + row) * HD;
     }
-    dst = cache + (((static_cast<size_t>(page) * 2 + (is_k ? 0 : 1)) * kv_heads + kv) * page_tokens + row) * HD;
   }
-  constexpr int V = PER_LANE / 2;
-  using Values = Pack<T, V>;
-  using Floats = Pack<float, V>;
-  const Values* src_lo = reinterpret_cast<const Values*>(src) + lane;
-  const Values* src_hi = reinterpret_cast<const Values*>(src + HALF) + lane;
-  Values* dst_lo = reinterpret_cast<Values*>(dst) + lane;
-  Values* dst_hi = reinterpret_cast<Values*>(dst + HALF) + lane;
-  if (!is_q && !is_k) {
-    chain_wait();
-    const Values lo = *behind_wait(src_lo), hi = *behind_wait(src_hi);  // written by the kernel ahead of this one
-    *dst_lo = lo;
-    *dst_hi = hi;
-    return;
-  }
+  const bool plain_copy = !is_q && !is_k;   // values: no norm, no rotation
   const float* weight = is_q ? q_weight : k_weight;
-  float gain[PER_LANE], c[V], sn[V];
+  float gain[2 * V], c[V], sn[V];
 #pragma unroll
-  for (int j = 0; j < PER_LANE; ++j) gain[j] = 1.0f;
-  if (weight != nullptr) {
-    const Floats lo = reinterpret_cast<const Floats*>(weight)[lane];
-    const Floats hi = reinterpret_cast<const Floats*>(weight + HALF)[lane];
+  for (int j = 0; j < 2 * V; ++j) gain[j] = 1.0f;
 #pragma unroll
-    for (int j = 0; j < V; ++j) {
-      gain[j] = lo.v[j];
-      gain[V + j] = hi.v[j];
+  for (int j = 0; j < V; ++j) { c[j] = 1.0f; sn[j] = 0.0f; }
+  if (active && !plain_copy && weight != nullptr) {
+#pragma unroll
+    for (int q4 = 0; q4 < V / 4; ++q4) {
+      const Floats lo = reinterpret_cast<const Floats*>(weight + V * sub)[q4];
+      const Floats hi = reinterpret_cast<const Floats*>(weight + HALF + V * sub)[q4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        gain[q4 * 4 + j] = lo.v[j];
+        gain[V + q4 * 4 + j] = hi.v[j];
+      }
     }
   }
-  if (cos_table != nullptr) {
+  if (active && !plain_copy && cos_table != nullptr) {
     int pos = positions[t];
     if (pos < 0 || pos >= table_positions) {
-      if (lane == 0) atomicOr(status, kStatusBadSlot);
+      if (sub == 0) atomicOr(status, kStatusBadSlot);
       pos = 0;
     }
-    const Floats cs = reinterpret_cast<const Floats*>(cos_table + static_cast<size_t>(pos) * HALF)[lane];
-    const Floats ss = reinterpret_cast<const Floats*>(sin_table + static_cast<size_t>(pos) * HALF)[lane];
 #pragma unroll
-    for (int j = 0; j < V; ++j) {
-      c[j] = cs.v[j];
-      sn[j] = ss.v[j];
+    for (int q4 = 0; q4 < V / 4; ++q4) {
+      const Floats cs = reinterpret_cast<const Floats*>(cos_table + static_cast<size_t>(pos) * HALF + V * sub)[q4];
+      const Floats ss = reinterpret_cast<const Floats*>(sin_table + static_cast<size_t>(pos) * HALF + V * sub)[q4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        c[q4 * 4 + j] = cs.v[j];
+        sn[q4 * 4 + j] = ss.v[j];
+      }
     }
   }
   chain_wait();
-  const Values in_lo = *behind_wait(src_lo), in_hi = *behind_wait(src_hi);  // written by the kernel ahead
-  float x[PER_LANE];
+  src = behind_wait(src);  // written by the kernel ahead of this one
+  Values in_lo = {}, in_hi = {};
+  if (active) {
+    in_lo = reinterpret_cast<const Values*>(src)[sub];
+    in_hi = reinterpret_cast<const Values*>(src + HALF)[sub];
+  }
+  if (plain_copy) {   // the same for every lane of a head; other heads of the warp go on below
+    if (active) {
+      reinterpret_cast<Values*>(dst)[sub] = in_lo;
+      reinterpret_cast<Values*>(dst + HALF)[sub] = in_hi;
+    }
+    active = false;
+  }
+  float x[2 * V];
   float sum = 0.0f;
 #pragma unroll
   for (int j = 0; j < V; ++j) {
@@ -192,30 +210,32 @@ qk_norm_rope_cache_warp_kernel(
     x[V + j] = to_float(in_hi.v[j]);
   }
 #pragma unroll
-  for (int j = 0; j < PER_LANE; ++j) sum += x[j] * x[j];
+  for (int j = 0; j < 2 * V; ++j) sum += x[j] * x[j];
+#pragma unroll
+  for (int offset = LANES / 2; offset > 0; offset >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, offset);
   if (weight != nullptr) {
-    sum = warp_sum(sum);
     const float scale = rsqrtf(sum / static_cast<float>(HD) + eps);
 #pragma unroll
-    for (int j = 0; j < PER_LANE; ++j) x[j] = x[j] * scale * gain[j];
+    for (int j = 0; j < 2 * V; ++j) x[j] = x[j] * scale * gain[j];
   }
   if (cos_table != nullptr) {
 #pragma unroll
     for (int j = 0; j < V; ++j) {
-      // element V lane + j (below HALF) and its partner HALF further, x[V + j]
+      // element V sub + j (below HALF) and its partner HALF further, x[V + j]
       const float lo = x[j], hi = x[V + j];
       x[j] = lo * c[j] - hi * sn[j];
       x[V + j] = hi * c[j] + lo * sn[j];
     }
   }
+  if (!active) return;
   Values out_lo, out_hi;
 #pragma unroll
   for (int j = 0; j < V; ++j) {
     out_lo.v[j] = from_float<T>(x[j]);
     out_hi.v[j] = from_float<T>(x[V + j]);
   }
-  *dst_lo = out_lo;
-  *dst_hi = out_hi;
+  reinterpret_cast<Values*>(dst)[sub] = out_lo;
+  reinterpret_cast<Values*>(dst + HALF)[sub] = out_hi;
 }
 
 }  // namespace mxb
@@ -230,33 +250,28 @@ MXB_API int mxb_qk_norm_rope_cache(
     int page_tokens, int num_pages, float eps, int dtype, int* status, cudaStream_t stream) {
   if (tokens <= 0) return 0;
   if (rotary_dim < 0 || rotary_dim > head_dim || (rotary_dim & 1)) return static_cast<int>(cudaErrorInvalidValue);
-  // The warp kernel moves head_dim / 64 values per access: rows and bases must be aligned to that.
-  const int per_access = head_dim >= 64 ? head_dim / 64 : 1;
-  const size_t access = static_cast<size_t>(per_access) * (dtype == kF32 ? 4 : 2);
+  // The warp kernel moves 16 bytes per access: rows and bases must be aligned to that.
+  const int element = dtype == kF32 ? 4 : 2;
   auto aligned = [&](const void* p, long long stride) {
-    return p == nullptr || (reinterpret_cast<uintptr_t>(p) % access == 0 && (stride * (dtype == kF32 ? 4 : 2)) % access == 0);
-  };
-  auto float_aligned = [&](const float* p) {  // tables are read head_dim / 64 floats at a time
-    return p == nullptr || reinterpret_cast<uintptr_t>(p) % (static_cast<size_t>(per_access) * 4) == 0;
+    return p == nullptr || (reinterpret_cast<uintptr_t>(p) % 16 == 0 && (stride * element) % 16 == 0);
   };
   const bool vector_ok = aligned(q_in, q_stride) && aligned(k_in, k_stride) && aligned(v_in, v_stride) &&
-                         aligned(q_out, 0) && aligned(cache, 0) && float_aligned(q_weight) &&
-                         float_aligned(k_weight) && float_aligned(cos_table) && float_aligned(sin_table);
+                         aligned(q_out, 0) && aligned(cache, 0) && aligned(q_weight, 0) && aligned(k_weight, 0) &&
+                         aligned(cos_table, 0) && aligned(sin_table, 0);
   if ((head_dim == 64 || head_dim == 128 || head_dim == 256) && (cos_table == nullptr || rotary_dim == head_dim) &&
-      vector_ok) {
+      vector_ok && (dtype == kF32 || dtype == kBF16)) {
     const long long items = static_cast<long long>(tokens) * (heads + 2 * kv_heads);
-    const unsigned blocks = static_cast<unsigned>((items + 7) / 8);
+    const int heads_per_warp = 32 / (head_dim / 2 / (16 / element));
+    const unsigned blocks = static_cast<unsigned>((items + 8 * heads_per_warp - 1) / (8 * heads_per_warp));
     cudaError_t launch_status = cudaSuccess;
-#define WARP_LAUNCH(T, PL) launch_status = launch_chained(qk_norm_rope_cache_warp_kernel<T, PL>, dim3(blocks), dim3(256), 0, stream, \
+#define WARP_LAUNCH(T, HD) launch_status = launch_chained(qk_norm_rope_cache_warp_kernel<T, HD>, dim3(blocks), dim3(256), 0, stream, \
         static_cast<const T*>(q_in), static_cast<const T*>(k_in), static_cast<const T*>(v_in), q_stride, k_stride, \
         v_stride, static_cast<T*>(q_out), static_cast<T*>(cache), slots, positions, q_weight, k_weight, cos_table, \
         sin_table, table_positions, tokens, heads, kv_heads, page_tokens, num_pages, eps, status)
     if (dtype == kF32) {
-      if (head_dim == 64) WARP_LAUNCH(float, 2); else if (head_dim == 128) WARP_LAUNCH(float, 4); else WARP_LAUNCH(float, 8);
-    } else if (dtype == kBF16) {
-      if (head_dim == 64) WARP_LAUNCH(__nv_bfloat16, 2); else if (head_dim == 128) WARP_LAUNCH(__nv_bfloat16, 4); else WARP_LAUNCH(__nv_bfloat16, 8);
+      if (head_dim == 64) WARP_LAUNCH(float, 64); else if (head_dim == 128) WARP_LAUNCH(float, 128); else WARP_LAUNCH(float, 256);
     } else {
-      return static_cast<int>(cudaErrorInvalidValue);
+      if (head_dim == 64) WARP_LAUNCH(__nv_bfloat16, 64); else if (head_dim == 128) WARP_LAUNCH(__nv_bfloat16, 128); else WARP_LAUNCH(__nv_bfloat16, 256);
     }
 #undef WARP_LAUNCH
     return static_cast<int>(launch_status);
