@@ -32,6 +32,7 @@ _DTYPES = {"bfloat16": torch.bfloat16, "bf16": torch.bfloat16, "float32": torch.
            "fp32": torch.float32, torch.bfloat16: torch.bfloat16, torch.float32: torch.float32}
 ATTENTION_TILE = 16  # query tokens per tile of the general kernel (csrc/kernels/attention_tile.cu)
 STEP_GRAPHS = 8       # how many shapes of general steps keep a captured graph
+STEP_GRAPH_TOKENS = 8192   # ... of steps up to this many tokens (a graph keeps its activations)
 WIDE_TILE = 128      # and of the tensor-core prompt kernels (csrc/kernels/attention_prefill*.cu)
 
 
@@ -365,7 +366,7 @@ class Engine:
         # A step that may be replayed as a graph has block tables of the full
         # width, so that its buffer has one layout whatever the contexts are.
         shape_key = (tuple(counts), len(wanted))
-        graphed = self._step_graphs is not None and (
+        graphed = self._step_graphs is not None and total <= STEP_GRAPH_TOKENS and (
             shape_key in self._step_graphs or self._shapes_seen.get(shape_key, 0) >= 1)
         full_width = -(-self.max_context // page_tokens)
         # One packed int32 buffer, one copy to the device.
