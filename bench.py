@@ -71,7 +71,7 @@ class ClockSampler:
         try:
             self.process = subprocess.Popen(
                 ["nvidia-smi", "-i", "0", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits",
-                 "-lms", "100"], stdout=self.file, stderr=subprocess.DEVNULL)
+                 "-lms", "25"], stdout=self.file, stderr=subprocess.DEVNULL)
         except OSError:
             self.process = None
         return self
