@@ -1,6 +1,7 @@
 """Each part alone against the plain implementation, the layer order as data,
-and a toy mixer with state of its own that is defined here, registered, built
-and stepped without any change to the framework's files."""
+and toy parts that are defined here, registered, built and stepped without
+any change to the framework's files: a mixer with state of its own, a
+feed-forward with routing, a position encoding of another convention."""
 import dataclasses
 
 import numpy as np
@@ -260,3 +261,148 @@ def test_a_toy_mixer_with_state_of_its_own(model_folders):
         engine.check()
     finally:
         unregister_part("mixer", "running_mean")
+
+
+# ------------------------------------- a routed feed-forward, another position encoding
+class Top1Experts:
+    """Every token goes through the one expert its router logit is largest for
+    (the first of equal ones): out = gelu(x W_in[e]^T) W_out[e]^T. Router
+    logits in float32. Dense torch operations only (every expert runs on every
+    token and a one-hot mask picks), so the part can sit inside a captured
+    graph; it stands for a feed-forward somebody else wrote."""
+
+    def __init__(self, spec, weights, runtime):
+        take = lambda name: weights.take(spec[name]).to(runtime.device, torch.float32)
+        self.router, self.w_in, self.w_out = take("router"), take("w_in"), take("w_out")
+        self.dtype = runtime.dtype
+
+    def forward(self, x, ctx):
+        x32 = x.float()
+        chosen = torch.argmax(x32 @ self.router.t(), dim=-1)                    # [tokens]
+        mask = torch.nn.functional.one_hot(chosen, self.router.shape[0]).float()  # [tokens, experts]
+        hidden = torch.nn.functional.gelu(torch.einsum("th,eih->tei", x32, self.w_in))
+        out = torch.einsum("tei,ehi->teh", hidden, self.w_out)
+        return (out * mask[:, :, None]).sum(dim=1).to(self.dtype)
+
+
+class PairwiseRotary:
+    """Rotates the pairs (2i, 2i + 1) of every head by position * theta^(-2i/d):
+    the interleaved convention, unlike the engine's own rotate-half part. It
+    offers no tables for the fused kernel, so the attention mixer calls
+    ``apply``; torch operations only."""
+
+    def __init__(self, spec, weights, runtime):
+        self.head_dim = spec["head_dim"]
+        index = torch.arange(self.head_dim // 2, device=runtime.device, dtype=torch.float64)
+        self.frequency = float(spec["theta"]) ** (-2.0 * index / self.head_dim)   # made once: nothing is built while a graph is captured
+
+    def apply(self, q, k, positions):
+        def rotate(x):
+            tokens = x.shape[0]
+            heads = x.shape[1] // self.head_dim
+            pairs = x.float().view(tokens, heads, self.head_dim // 2, 2)
+            angle = positions.double()[:, None] * self.frequency[None, :]
+            cos, sin = torch.cos(angle).float()[:, None, :], torch.sin(angle).float()[:, None, :]
+            even, odd = pairs[..., 0], pairs[..., 1]
+            out = torch.stack([even * cos - odd * sin, odd * cos + even * sin], dim=-1)
+            return out.view(tokens, heads, self.head_dim).to(x.dtype)
+        return rotate(q), rotate(k)
+
+
+def plain_with_toy_parts(config, tensors, ids, toy):
+    """The plain model with layer 0's feed-forward replaced by the top-1
+    experts and layer 2's rotation by the pairwise one."""
+    w = {k: v.astype(np.float64) for k, v in tensors.items()}
+    x = plain.embed(w["model.embed_tokens.weight"], ids)
+    eps = plain.f32(config["rms_norm_eps"])
+    positions = np.arange(len(ids))
+    heads, kv_heads, hd = config["num_attention_heads"], config["num_key_value_heads"], config["head_dim"]
+
+    def pairwise(v):
+        index = np.arange(hd // 2, dtype=np.float64)
+        angle = positions[:, None] * toy["theta"] ** (-2.0 * index / hd)[None, :]
+        cos, sin = np.cos(angle)[:, None, :], np.sin(angle)[:, None, :]
+        out = np.empty_like(v)
+        out[..., 0::2] = v[..., 0::2] * cos - v[..., 1::2] * sin
+        out[..., 1::2] = v[..., 1::2] * cos + v[..., 0::2] * sin
+        return out
+
+    for layer in range(config["num_hidden_layers"]):
+        base = f"model.layers.{layer}"
+        attention_in = plain.rms_norm(x, w[f"{base}.input_layernorm.weight"], eps)
+        if layer == 2:
+            tokens = len(ids)
+            q = (attention_in @ w[f"{base}.self_attn.q_proj.weight"].T).reshape(tokens, heads, hd)
+            k = (attention_in @ w[f"{base}.self_attn.k_proj.weight"].T).reshape(tokens, kv_heads, hd)
+            v = (attention_in @ w[f"{base}.self_attn.v_proj.weight"].T).reshape(tokens, kv_heads, hd)
+            q = pairwise(plain.rms_norm(q, w[f"{base}.self_attn.q_norm.weight"], eps))
+            k = pairwise(plain.rms_norm(k, w[f"{base}.self_attn.k_norm.weight"], eps))
+            mixed = plain.causal_gqa_attention(q, k, v, hd ** -0.5).reshape(tokens, heads * hd)
+            residual = x + mixed @ w[f"{base}.self_attn.o_proj.weight"].T
+        else:
+            residual = x + plain.attention_block(attention_in, positions, w, f"{base}.self_attn", config)
+        mlp_in = plain.rms_norm(residual, w[f"{base}.post_attention_layernorm.weight"], eps)
+        if layer == 0:
+            chosen = np.argmax((mlp_in @ toy["router"].T).astype(np.float32), axis=-1)
+            out = np.zeros_like(mlp_in)
+            for t, e in enumerate(chosen):
+                h = mlp_in[t] @ toy["w_in"][e].T
+                h = 0.5 * h * (1.0 + np.vectorize(__import__("math").erf)(h / np.sqrt(2.0)))
+                out[t] = h @ toy["w_out"][e].T
+            x = residual + out
+        else:
+            x = residual + plain.swiglu(mlp_in, w[f"{base}.mlp.gate_proj.weight"], w[f"{base}.mlp.up_proj.weight"],
+                                        w[f"{base}.mlp.down_proj.weight"])
+    normed = plain.rms_norm(x, w["model.norm.weight"], eps)
+    return normed @ w["lm_head.weight"].T
+
+
+def test_a_routed_feed_forward_and_another_position_encoding(model_folders):
+    """Parts defined here: a feed-forward with routing in layer 0 (the other
+    layers keep SwiGLU) and a position encoding of another convention in layer
+    2's attention (which then runs its norm, rotation and cache write as
+    separate calls). Registered, built and stepped, whole, in portions and
+    token by token through the captured decode graph, without a change to the
+    framework's files."""
+    from metallix_b200.config import PartSpec, Qwen3Config
+    from metallix_b200.engine import Engine, StepEntry
+    from metallix_b200.parts import register_part, unregister_part
+    from metallix_b200.weights import load_tensors
+    folder, config, tensors, page = model_folders["B"]
+    typed = Qwen3Config.from_dict(config)
+    register_part("feed_forward", "top1_experts", Top1Experts)
+    register_part("position", "pairwise_rotary", PairwiseRotary)
+    try:
+        rng = np.random.default_rng(12)
+        toy = {"router": rng.normal(size=(4, 96)), "w_in": rng.normal(size=(4, 40, 96)) * 0.1,
+               "w_out": rng.normal(size=(4, 96, 40)) * 0.1, "theta": 500.0}
+        base = typed.to_model_spec()
+        layers = list(base.layers)
+        layers[0] = dataclasses.replace(layers[0], feed_forward=PartSpec("top1_experts", {
+            "router": "toy.router", "w_in": "toy.w_in", "w_out": "toy.w_out"}))
+        mixer = dict(layers[2].mixer.params)
+        mixer["position"] = PartSpec("pairwise_rotary", {"head_dim": config["head_dim"], "theta": toy["theta"]})
+        layers[2] = dataclasses.replace(layers[2], mixer=PartSpec("gqa_attention", mixer))
+        spec = dataclasses.replace(base, layers=tuple(layers))
+        loaded = load_tensors(folder, typed, device="cuda:0")
+        for name in ("router", "w_in", "w_out"):
+            loaded[f"toy.{name}"] = torch.tensor(toy[name], dtype=torch.float32, device="cuda:0")
+        ids = random_ids(5, 70, config["vocab_size"])
+        reference = plain_with_toy_parts(config, tensors, ids, toy)
+        engine = Engine(typed, loaded, dtype="float32", page_tokens=page, num_pages=32, spec=spec)
+        assert not engine.model.blocks[2].mixer.fused and engine.model.blocks[1].mixer.fused
+        whole = engine.step([StepEntry("w", ids, list(range(70)))]).cpu().double().numpy()
+        # a token whose two best router logits nearly tie may take the other expert: none does here
+        assert np.abs(whole - reference).max() < 5e-5
+        engine.release("w")
+        seen = [engine.step([StepEntry("p", ids[:23], [22])]), engine.step([StepEntry("p", ids[23:50], [0, 26])])]
+        got = np.concatenate([s.cpu().double().numpy() for s in seen])
+        assert np.abs(got - reference[[22, 23, 49]]).max() < 5e-5
+        assert engine.graphs is not None
+        for position in range(50, 70):      # token by token: the captured graph holds the toy parts too
+            logits = engine.step([StepEntry("p", [ids[position]], [0])]).cpu().double().numpy()
+            assert np.abs(logits[0] - reference[position]).max() < 5e-5, position
+        engine.check()
+    finally:
+        unregister_part("feed_forward", "top1_experts")
+        unregister_part("position", "pairwise_rotary")
