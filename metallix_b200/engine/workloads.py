@@ -108,7 +108,7 @@ def main(argv=None) -> int:
     config = Qwen3Config.from_dict(dict(QWEN3_0_6B, num_hidden_layers=args.layers))
     pages = args.batch * (-(-(args.prompt_len + 64) // 16)) + 64
     engine = Engine.from_random(config, 0, dtype="bfloat16", page_tokens=16, num_pages=pages,
-                                max_requests=args.batch + 2, max_context=4096,
+                                max_requests=args.batch + 2, max_context=max(4096, args.prompt_len + 256),
                                 cuda_graphs=args.graphs or args.timeline)   # the timeline is of the step as it serves
     rng = np.random.default_rng(0)
     if args.mode == "prefill":
