@@ -4,11 +4,11 @@
 //
 // One block takes up to 128 consecutive query tokens of one request and one
 // query head and walks the request's keys in tiles of 128 absolute positions.
-//   warp 0      fetches: the query tile once, then for every key tile the
-//               pages the block table names, K and V, as TMA boxes of one page
-//               x 64 values with the 128-byte swizzle (so a tile of K is a
-//               K-major operand and a tile of V an MN-major one, as they lie
-//               in the cache);
+//   warp 0, 18  fetch: warp 0 the query tile once and the keys, warp 18 the
+//               values, for every key tile the pages the block table names as
+//               TMA boxes of one page x 64 values with the 128-byte swizzle
+//               (so a tile of K is a K-major operand and a tile of V an
+//               MN-major one, as they lie in the cache);
 //   warp 1      owns tensor memory and issues the MMAs: S = Q K^T into one of
 //               two score buffers, and O_tile = P V into one of two output
 //               buffers, with P read from tensor memory where the softmax
@@ -41,7 +41,8 @@ constexpr int kFaRows = 128;     // query rows of a block
 constexpr int kFaKeys = 128;     // keys of a tile
 constexpr int kFaParts = 4;      // threads per query row
 constexpr int kFaSoftmaxThreads = kFaParts * kFaRows;
-constexpr int kFaThreads = 64 + kFaSoftmaxThreads;
+constexpr int kFaThreads = 64 + kFaSoftmaxThreads + 32;   // fetch (keys), MMA, softmax, fetch (values)
+constexpr int kFaValueWarp = kFaThreads / 32 - 1;
 constexpr int kFaTmemColumns = 512;
 constexpr int kFaHalfBytes = 128 * kTmaColumns * 2;  // a [128 x 64] bfloat16 operand block: 16 KiB
 
@@ -103,8 +104,7 @@ flash_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __
   uint64_t* s_full = v_empty + MAX_STAGES;
   uint64_t* p_full = s_full + 2;
   uint64_t* o_full = p_full + 2;
-  uint64_t* o_empty = o_full + 2;
-  uint64_t* row_ready = o_empty + 2;  // [4]: the softmax warps of a lane group meet here
+  uint64_t* row_ready = o_full + 2;  // [4]: the softmax warps of a lane group meet here
   uint32_t& tmem_base_slot = *reinterpret_cast<uint32_t*>(row_ready + 4);
   volatile int& failed = *reinterpret_cast<volatile int*>(&tmem_base_slot + 1);
   // [tile parity][part][row]: the threads of a row exchange maxima (and, at the end, sums)
@@ -133,7 +133,6 @@ flash_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __
       barrier_init(&s_full[b], 1);
       barrier_init(&p_full[b], kFaSoftmaxThreads);   // every softmax thread arrives
       barrier_init(&o_full[b], 1);
-      barrier_init(&o_empty[b], kFaSoftmaxThreads);
     }
     for (int g = 0; g < 4; ++g) barrier_init(&row_ready[g], kFaParts * 32);
     barrier_init_fence();
@@ -149,65 +148,77 @@ flash_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __
   tc_fence_after_sync();
   const uint32_t tmem_base = tmem_base_slot;
 
-  if (warp == 0) {
-    // ---- fetch: Q once, then K and V of every key tile, page by page
+  if (warp == 0 || warp == kFaValueWarp) {
+    // ---- fetch: warp 0 the query tile and the keys, the last warp the values
+    // of every key tile, page by page. A warp's 32 TMA requests of one tile go
+    // out one after the other (some 37 cycles each: with keys and values on
+    // one warp the fetch paced the whole block), so keys and values have a
+    // warp each; the page of the next tile is looked up a tile ahead.
+    const bool values = warp == kFaValueWarp;
+    const int stages = values ? VS : KS;
+    uint64_t* full = values ? v_full : k_full;
+    uint64_t* empty = values ? v_empty : k_empty;
+    unsigned char* tiles = values ? v_tiles : k_tiles;
     const int* table = block_tables + static_cast<size_t>(tile_request[tile]) * max_pages;
-    if (lane == 0) {
+    if (!values && lane == 0) {
       barrier_arrive_expect(q_full, Config::kTileBytes);
       for (int half = 0; half < HALVES; ++half)
         tma_load_2d(q_tile + half * kFaHalfBytes, &map_q, head * HD + half * kTmaColumns, t0, q_full);
     }
     const int pages_per_tile = kFaKeys / page_tokens;
     const int copies = pages_per_tile * HALVES;  // every page, every 64-value half
+    const int slot = lane / HALVES, half = lane % HALVES;  // copies <= 32: one per lane
+    const uint32_t offset = half * kFaHalfBytes + slot * page_tokens * (kTmaColumns * 2);
+    // Pages no row of the tile can see are not looked up: page 0 stands in
+    // (its values are finite and every such key is masked).
+    auto page_of = [&](int i) {
+      const int page_key = (tile_begin + i) * kFaKeys + slot * page_tokens;
+      if (i < key_tiles && lane < copies && page_key <= last_pos && page_key + page_tokens > first_key &&
+          page_key / page_tokens < max_pages)
+        return table[page_key / page_tokens];
+      return 0;
+    };
+    int page = page_of(0);
     for (int i = 0; i < key_tiles && !failed; ++i) {
-      const int k_stage = i % KS, v_stage = i % VS;
-      const int key0 = (tile_begin + i) * kFaKeys;
-      // Pages no row of the tile can see are not looked up: page 0 stands in
-      // (its values are finite and every such key is masked).
-      int page = 0;
-      const int slot = lane / HALVES, half = lane % HALVES;  // copies <= 32: one per lane
-      const int page_key = key0 + slot * page_tokens;
-      if (lane < copies && page_key <= last_pos && page_key + page_tokens > first_key &&
-          page_key / page_tokens < max_pages) {
-        page = table[page_key / page_tokens];
-        if (page < 0 || page >= num_pages) {
-          atomicOr(status, kStatusBadPage);
-          page = 0;
-        }
+      const int stage = i % stages;
+      const int upcoming = page_of(i + 1);   // in flight while this tile's requests go out
+      if (page < 0 || page >= num_pages) {
+        atomicOr(status, kStatusBadPage);
+        page = 0;
       }
-      const uint32_t offset = half * kFaHalfBytes + slot * page_tokens * (kTmaColumns * 2);
       // K as soon as the scores that read this stage last are done, V when the P V product is.
-      if (!barrier_wait(&k_empty[k_stage], ((i / KS) & 1) ^ 1, status)) { failed = 1; break; }
-      if (lane == 0) barrier_arrive_expect(&k_full[k_stage], Config::kTileBytes);
+      if (!barrier_wait(&empty[stage], ((i / stages) & 1) ^ 1, status)) { failed = 1; break; }
+      if (lane == 0) barrier_arrive_expect(&full[stage], Config::kTileBytes);
       __syncwarp();
       if (lane < copies)
-        tma_load_2d(k_tiles + k_stage * Config::kTileBytes + offset, &map_cache, half * kTmaColumns,
-                    ((page * 2) * kv_heads + kv) * page_tokens, &k_full[k_stage]);
-      if (!barrier_wait(&v_empty[v_stage], ((i / VS) & 1) ^ 1, status)) { failed = 1; break; }
-      if (lane == 0) barrier_arrive_expect(&v_full[v_stage], Config::kTileBytes);
-      __syncwarp();
-      if (lane < copies)
-        tma_load_2d(v_tiles + v_stage * Config::kTileBytes + offset, &map_cache, half * kTmaColumns,
-                    ((page * 2 + 1) * kv_heads + kv) * page_tokens, &v_full[v_stage]);
+        tma_load_2d(tiles + stage * Config::kTileBytes + offset, &map_cache, half * kTmaColumns,
+                    ((page * 2 + (values ? 1 : 0)) * kv_heads + kv) * page_tokens, &full[stage]);
+      page = upcoming;
     }
   } else if (warp == 1) {
     // ---- one thread issues every MMA
     if (lane == 0) {
       constexpr uint32_t idesc_s = tc_instruction_descriptor(kFaRows, kFaKeys);
       constexpr uint32_t idesc_o = tc_instruction_descriptor_b_mn(kFaRows, HD);
-      const uint32_t q_address = shared_address(q_tile);
+      // This one thread is the block's pacemaker: what it does per key tile
+      // (three waits, sixteen MMAs, four commits) is kept short. The
+      // descriptors of the operands are made once; a stage or a step along k
+      // only adds to their address field (16-byte units, no carry: shared
+      // memory ends below 256 KiB).
+      const uint64_t q_desc = tc_smem_descriptor(shared_address(q_tile));
+      const uint64_t k_desc = tc_smem_descriptor(shared_address(k_tiles));
+      const uint64_t v_desc = tc_smem_descriptor_mn(shared_address(v_tiles), kFaHalfBytes);
       bool ok = barrier_wait(q_full, 0, status);
       auto scores = [&](int i) {  // S_i = Q K_i^T
         const int stage = i % KS;
         if (!barrier_wait(&k_full[stage], (i / KS) & 1, status)) return false;
         tc_fence_after_sync();
-        const uint32_t k_address = shared_address(k_tiles + stage * Config::kTileBytes);
+        const uint64_t k_stage = k_desc + static_cast<uint64_t>(stage) * (Config::kTileBytes >> 4);
         const uint32_t tmem_s = tmem_base + (i & 1) * Config::kScoreColumns;
 #pragma unroll
         for (int kk = 0; kk < HD / 16; ++kk) {
-          const uint32_t offset = (kk / 4) * kFaHalfBytes + (kk % 4) * 32;
-          tc_mma(tmem_s, tc_smem_descriptor(q_address + offset), tc_smem_descriptor(k_address + offset), idesc_s,
-                 kk > 0 ? 1u : 0u);
+          const uint64_t offset = ((kk / 4) * kFaHalfBytes + (kk % 4) * 32) >> 4;
+          tc_mma(tmem_s, q_desc + offset, k_stage + offset, idesc_s, kk > 0 ? 1u : 0u);
         }
         tc_commit(&k_empty[stage]);
         tc_commit(&s_full[i & 1]);
@@ -216,17 +227,18 @@ flash_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __
       auto outputs = [&](int i) {  // O_tile_i = P_i V_i
         const int stage = i % VS, buffer = i & 1;
         if (!barrier_wait(&v_full[stage], (i / VS) & 1, status)) return false;
-        if (!barrier_wait(&o_empty[buffer], ((i >> 1) & 1) ^ 1, status)) return false;
+        // The output buffer is free: every softmax thread took tile i - 2 out of
+        // it before it arrived for P of tile i - 1, let alone of tile i.
         if (!barrier_wait(&p_full[buffer], (i >> 1) & 1, status)) return false;
         tc_fence_after_sync();
-        const uint32_t v_address = shared_address(v_tiles + stage * Config::kTileBytes);
+        const uint64_t v_stage = v_desc + static_cast<uint64_t>(stage) * (Config::kTileBytes >> 4);
         const uint32_t tmem_p = tmem_base + buffer * Config::kScoreColumns;
         const uint32_t tmem_o = tmem_base + Config::kOutputBase + buffer * HD;
 #pragma unroll
         for (int kk = 0; kk < kFaKeys / 16; ++kk) {  // 16 keys per instruction: two 8-row groups of V, 8 columns of P
           // P of the keys' quarter q lies over the first half of that quarter's score columns.
-          tc_mma_ts(tmem_o, tmem_p + (kk / 2) * (kFaKeys / kFaParts) + (kk % 2) * 8,
-                    tc_smem_descriptor_mn(v_address + kk * 2048, kFaHalfBytes), idesc_o, kk > 0 ? 1u : 0u);
+          tc_mma_ts(tmem_o, tmem_p + (kk / 2) * (kFaKeys / kFaParts) + (kk % 2) * 8, v_stage + kk * (2048 >> 4),
+                    idesc_o, kk > 0 ? 1u : 0u);
         }
         tc_commit(&v_empty[stage]);
         tc_commit(&o_full[buffer]);
@@ -267,8 +279,7 @@ flash_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __
       tc_fence_after_sync();
       uint32_t o[PART_HD];
       tc_load(tmem_lane + Config::kOutputBase + buffer * HD + part * PART_HD, o);
-      tc_fence_before_sync();
-      barrier_arrive(&o_empty[buffer]);
+      tc_fence_before_sync();   // the MMA thread reuses the buffer only behind this thread's next arrival for P
 #pragma unroll
       for (int j = 0; j < PART_HD; ++j) acc[j] = fmaf(acc[j], alpha, __uint_as_float(o[j]));
       return true;

@@ -43,6 +43,7 @@ def main(argv=None) -> int:
     parser.add_argument("--swiglu", action="store_true", help="gemm: the fused SwiGLU epilogue (n = 2 * inter)")
     parser.add_argument("--context", type=int, default=0, help="attention: keys already in the cache")
     parser.add_argument("--kernel", default="both", choices=("both", "tcgen05", "mma"))
+    parser.add_argument("--page-tokens", type=int, default=16, help="attention: tokens per cache page")
     args = parser.parse_args(argv)
 
     import numpy as np
@@ -74,7 +75,7 @@ def main(argv=None) -> int:
     if args.mode == "attention":
         ops.require_cuda()
         heads, kv_heads, head_dim, page_tokens = (QWEN3_0_6B["num_attention_heads"], QWEN3_0_6B["num_key_value_heads"],
-                                                  QWEN3_0_6B["head_dim"], 16)
+                                                  QWEN3_0_6B["head_dim"], args.page_tokens)
         tokens, total = args.prompt_len, args.context + args.prompt_len
         pages = -(-total // page_tokens)
         generator = torch.Generator(device="cuda").manual_seed(0)
