@@ -13,8 +13,7 @@
 // Replaces the reference's per-step gather of every row's whole context into
 // [rows, kv_heads, longest, head_dim] plus a masked SDPA call
 // (crates/models/qwen/src/forward/paged.rs:189-219, :1067-1076, :1216-1232).
-#include "async_copy.cuh"
-#include "common.cuh"
+#include "tcgen05.cuh"   // TMA tile loads and tensor maps (async_copy.cuh, common.cuh come with it)
 
 namespace mxb {
 
@@ -447,6 +446,220 @@ paged_attention_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, const __n
   }
 }
 
+// The same split with the keys and values fetched a page at a time: one TMA
+// box of one page x 64 values (128-byte swizzle) instead of one bulk copy per
+// 256-byte row. The copy engine takes a request every few tens of cycles
+// whatever its size, and 256 requests a block made it, not memory, set the
+// pace (clock stamps in the blocks: 4,200 of a block's 9,300 cycles went into
+// handing the requests over). A split is always its whole 128 absolute
+// positions (a page that holds none of the token's keys is a box beyond the
+// cache's last row: zeros); rows read by ldmatrix undo the swizzle.
+//   byte offset of 16-byte chunk c of row r:  half c / 8, then r * 128 + ((c % 8) ^ (r % 8)) * 16
+template <int HD> __device__ __forceinline__ uint32_t decode_swizzled_offset(int row, int chunk) {
+  return static_cast<uint32_t>((chunk >> 3) * (kSplitKeys * 128) + row * 128 + (((chunk & 7) ^ (row & 7)) << 4));
+}
+
+template <int HD>
+__global__ void __launch_bounds__(kDecodeThreads)
+paged_attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_cache, const __nv_bfloat16* __restrict__ q,
+                                  float* __restrict__ partial, const int* __restrict__ block_tables,
+                                  int max_pages, const int* __restrict__ row_token,
+                                  const int* __restrict__ row_request, const int* __restrict__ positions,
+                                  int heads, int kv_heads, int page_tokens, int num_pages, int max_splits,
+                                  int window, float scale, int* status) {
+  constexpr int HALVES = HD / kTmaColumns;                 // 64-value halves of a row
+  constexpr int TILE_BYTES = kSplitKeys * HD * 2;
+  extern __shared__ unsigned char tma_decode_raw[];
+  __shared__ __align__(8) uint64_t barriers[2];   // keys, values
+  unsigned char* sK = tma_decode_raw + ((1024 - (shared_address(tma_decode_raw) & 1023)) & 1023);
+  unsigned char* sV = sK + TILE_BYTES;
+  float* s_merge = reinterpret_cast<float*>(sK);  // [4 warps][8 heads][HD + 2], over K once the scores exist
+  static_assert(4 * 8 * (HD + 2) * sizeof(float) <= TILE_BYTES, "the merge area must fit over the keys");
+
+  chain_release();
+  // What follows up to chain_wait() reads nothing a kernel of this step writes
+  // (the step's integers and the pages of earlier positions), so it runs,
+  // copies included, while the kernels before this one are still at work.
+  const int split = blockIdx.x, kv = blockIdx.y, row = blockIdx.z;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int g = lane >> 2, t = lane & 3;
+  const int key0 = split * kSplitKeys;
+  // One thread per box: keys or values, page of the split, 64-value half.
+  const int pages = kSplitKeys / page_tokens;   // <= 16
+  const int boxes = 2 * pages * HALVES;         // <= 64
+  const bool fetcher = tid < boxes;
+  const int which = tid / (pages * HALVES), slot = (tid / HALVES) % pages, half = tid % HALVES;
+  const int page_key = key0 + slot * page_tokens;
+  // Two trips to memory before the copies can start, not three: the token and
+  // its request's row of the block table first, then the position and,
+  // without waiting to learn whether the page holds any of the token's keys,
+  // the page.
+  const int token = row_token[row];
+  const int table_row = row_request[row];
+  int page = 0;
+  if (fetcher && page_key / page_tokens < max_pages)
+    page = block_tables[static_cast<size_t>(table_row) * max_pages + page_key / page_tokens];
+  if (token < 0) return;
+  const int pos = positions[token];
+  const int group = heads / kv_heads;  // <= 8
+  const int first_key = window > 0 ? max(0, pos - window + 1) : 0;
+  if (key0 > pos || key0 + kSplitKeys <= first_key) return;   // the merge skips splits outside [first_key, pos]
+  const int lo = max(first_key - key0, 0), hi = min(pos - key0, kSplitKeys - 1);   // the split's rows that count
+
+  if (tid == 0) {
+    barrier_init(&barriers[0], 1);
+    barrier_init(&barriers[1], 1);
+    barrier_init_fence();
+    barrier_arrive_expect(&barriers[0], TILE_BYTES);   // every box is fetched, whatever it holds
+    barrier_arrive_expect(&barriers[1], TILE_BYTES);
+  }
+  __syncthreads();
+  // The page that holds the token's own position is written by the kernel
+  // ahead of this one: it waits; every other page is fetched right away. A
+  // page that holds none of the token's keys is not wanted: its box starts
+  // beyond the cache's last row, where the copy engine writes zeros.
+  const bool fresh = fetcher && pos >= page_key && pos < page_key + page_tokens;
+  bool wanted = fetcher && page_key <= pos && page_key + page_tokens > first_key;
+  if (wanted && (page < 0 || page >= num_pages)) {
+    atomicOr(status, kStatusBadPage);
+    wanted = false;
+  }
+  unsigned char* dst = (which ? sV : sK) + half * (kSplitKeys * 128) + slot * page_tokens * 128;
+  const int box_row = wanted ? ((page * 2 + which) * kv_heads + kv) * page_tokens
+                             : num_pages * 2 * kv_heads * page_tokens;
+  if (fetcher && !fresh) tma_load_2d(dst, &map_cache, half * kTmaColumns, box_row, &barriers[which]);
+  chain_wait();
+  if (fresh) tma_load_2d(dst, &map_cache, half * kTmaColumns, box_row, &barriers[which]);
+
+  // ---- the query heads of this key/value head as rows 0..group-1 of the 16-row operand
+  uint32_t qa0[HD / 16], qa2[HD / 16];
+  {
+    // q is written by the kernel ahead of this one
+    const __nv_bfloat16* qrow = behind_wait(q) + (static_cast<size_t>(token) * heads + kv * group + (g < group ? g : 0)) * HD;
+#pragma unroll
+    for (int ks = 0; ks < HD / 16; ++ks) {
+      qa0[ks] = g < group ? *reinterpret_cast<const uint32_t*>(qrow + ks * 16 + 2 * t) : 0u;
+      qa2[ks] = g < group ? *reinterpret_cast<const uint32_t*>(qrow + ks * 16 + 8 + 2 * t) : 0u;
+    }
+  }
+  const bool keys_landed = barrier_wait(&barriers[0], 0, status);
+
+  // ---- scores of this warp's 32 keys
+  const int key_base = warp * 32;
+  const bool has_keys = key_base <= hi && key_base + 31 >= lo;
+  float sc[4][4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) sc[i][0] = sc[i][1] = sc[i][2] = sc[i][3] = 0.0f;
+  if (has_keys) {
+#pragma unroll
+    for (int ks = 0; ks < HD / 16; ++ks) {
+#pragma unroll
+      for (int nb = 0; nb < 2; ++nb) {
+        uint32_t kf[4];
+        const int krow = key_base + nb * 16 + (lane & 7) + (lane >> 4) * 8;
+        decode_ldmatrix_x4(kf, decode_smem_address(sK + decode_swizzled_offset<HD>(krow, ks * 2 + ((lane >> 3) & 1))));
+        decode_mma(sc[2 * nb], qa0[ks], qa2[ks], kf[0], kf[1]);
+        decode_mma(sc[2 * nb + 1], qa0[ks], qa2[ks], kf[2], kf[3]);
+      }
+    }
+  }
+  // Row g of the tile is query head g; this thread holds keys nb * 8 + 2t, 2t + 1.
+  const float scale_log2 = scale * 1.4426950408889634f;
+  float m_w = -INFINITY;
+#pragma unroll
+  for (int nb = 0; nb < 4; ++nb) {
+#pragma unroll
+    for (int j = 0; j < 2; ++j) {
+      const int kk = key_base + nb * 8 + 2 * t + j;
+      sc[nb][j] = kk >= lo && kk <= hi ? sc[nb][j] * scale_log2 : -INFINITY;
+      m_w = fmaxf(m_w, sc[nb][j]);
+    }
+  }
+  m_w = fmaxf(m_w, __shfl_xor_sync(0xffffffffu, m_w, 1));
+  m_w = fmaxf(m_w, __shfl_xor_sync(0xffffffffu, m_w, 2));
+  const float ref = m_w == -INFINITY ? 0.0f : m_w;
+  float l_w = 0.0f;
+  uint32_t pa0[2], pa2[2];
+#pragma unroll
+  for (int nb = 0; nb < 4; ++nb) {
+    const float p0 = decode_exp2(sc[nb][0] - ref), p1 = decode_exp2(sc[nb][1] - ref);
+    l_w += p0 + p1;
+    __nv_bfloat162 packed = __floats2bfloat162_rn(p0, p1);
+    const uint32_t word = *reinterpret_cast<uint32_t*>(&packed);
+    if (nb & 1) pa2[nb >> 1] = word; else pa0[nb >> 1] = word;
+  }
+  l_w += __shfl_xor_sync(0xffffffffu, l_w, 1);
+  l_w += __shfl_xor_sync(0xffffffffu, l_w, 2);
+
+  const bool values_landed = barrier_wait(&barriers[1], 0, status);
+  // One decision for the whole block; the status word says why, and both
+  // barriers were given their time, so no copy is left in flight.
+  if (__syncthreads_or(!keys_landed || !values_landed)) return;
+
+  // A masked key has weight 0, but 0 x NaN is NaN: value rows outside the
+  // token's keys (the rest of the last page, whatever an earlier owner of the
+  // page left there) are zeroed, so that nothing is asked
+  // of what the cache holds beyond a request's own positions. A warp reads
+  // only its own 32 rows, and only a split's first and last warps have any.
+  if (has_keys && (key_base < lo || key_base + 31 > hi)) {
+    for (int i = lane; i < 32 * (HD / 8); i += 32) {
+      const int vrow = key_base + i / (HD / 8);
+      if (vrow < lo || vrow > hi)
+        *reinterpret_cast<uint4*>(sV + decode_swizzled_offset<HD>(vrow, i % (HD / 8))) = make_uint4(0u, 0u, 0u, 0u);
+    }
+    __syncwarp();
+  }
+
+  // ---- o = p v over this warp's 32 keys
+  float o[HD / 8][4];
+#pragma unroll
+  for (int i = 0; i < HD / 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.0f;
+  if (has_keys) {
+#pragma unroll
+    for (int ks = 0; ks < 2; ++ks) {
+#pragma unroll
+      for (int nb = 0; nb < HD / 16; ++nb) {
+        uint32_t vf[4];
+        const int vrow = key_base + ks * 16 + (lane & 7) + ((lane >> 3) & 1) * 8;
+        decode_ldmatrix_x4_trans(vf, decode_smem_address(sV + decode_swizzled_offset<HD>(vrow, nb * 2 + (lane >> 4))));
+        decode_mma(o[2 * nb], pa0[ks], pa2[ks], vf[0], vf[1]);
+        decode_mma(o[2 * nb + 1], pa0[ks], pa2[ks], vf[2], vf[3]);
+      }
+    }
+  }
+  __syncthreads();  // every warp is done with K and V: the merge area lies over K
+
+  // ---- merge the four warps in warp order
+  if (g < group) {
+    float* mine = s_merge + (warp * 8 + g) * (HD + 2);
+#pragma unroll
+    for (int i = 0; i < HD / 8; ++i) {
+      mine[i * 8 + 2 * t] = o[i][0];
+      mine[i * 8 + 2 * t + 1] = o[i][1];
+    }
+    if (t == 0) { mine[HD] = m_w; mine[HD + 1] = l_w; }
+  }
+  __syncthreads();
+  for (int i = tid; i < group * HD; i += kDecodeThreads) {
+    const int h = i / HD, d = i - h * HD;
+    float m_all = -INFINITY;
+#pragma unroll
+    for (int wp = 0; wp < 4; ++wp) m_all = fmaxf(m_all, s_merge[(wp * 8 + h) * (HD + 2) + HD]);
+    float sum = 0.0f, l_all = 0.0f;
+#pragma unroll
+    for (int wp = 0; wp < 4; ++wp) {
+      const float* theirs = s_merge + (wp * 8 + h) * (HD + 2);
+      const float weight = decode_exp2(theirs[HD] - m_all);  // a warp without keys has m = -inf: weight 0
+      sum += weight * theirs[d];
+      l_all += weight * theirs[HD + 1];
+    }
+    const int head = kv * group + h;
+    float* dst_partial = partial + ((static_cast<size_t>(row) * heads + head) * max_splits + split) * (HD + 2);
+    dst_partial[d] = sum;
+    if (d == 0) { dst_partial[HD] = m_all * 0.6931471805599453f; dst_partial[HD + 1] = l_all; }  // the merge kernel works in natural units
+  }
+}
+
 // out[token, head, :] = sum_s exp(m_s - M) acc_s / sum_s exp(m_s - M) l_s over
 // the splits that hold keys of this token, in ascending order. One block per
 // (token, head), one thread per value of the head. A thread fetches the
@@ -539,14 +752,32 @@ static int launch_decode_mma(const void* q, const void* cache, void* out, float*
   static_assert(kSplitKeys == kDecodeThreads, "one thread per key row of a split");
   static_assert(4 * 8 * (HD + 2) * sizeof(float) <= kSplitKeys * HD * 2, "the merge area must fit over the keys");
   dim3 grid(max_splits, kv_heads, rows);
-  const int shared = 2 * kSplitKeys * (HD * 2 + 16);
-  auto kernel = paged_attention_decode_mma_kernel<HD>;
-  cudaError_t attribute = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, shared);
-  if (attribute != cudaSuccess) return static_cast<int>(attribute);
-  cudaError_t e = launch_chained(kernel, grid, dim3(kDecodeThreads), shared, stream,
-                                 static_cast<const __nv_bfloat16*>(q), static_cast<const __nv_bfloat16*>(cache),
-                                 partial, block_tables, max_pages, row_token, row_request, positions, heads,
-                                 kv_heads, page_tokens, num_pages, max_splits, window, scale, status);
+  cudaError_t e;
+  const long long cache_rows = static_cast<long long>(num_pages) * 2 * kv_heads * page_tokens;
+  CUtensorMap map_cache;
+  // Pages of 8, 16, ... 128 tokens fill whole 8-row groups of the swizzled
+  // tile and divide a split: one TMA box per page and 64-value half. Other
+  // page sizes keep the kernel with one bulk copy per row.
+  if (page_tokens >= 8 && page_tokens <= kSplitKeys && kSplitKeys % page_tokens == 0 && cache_rows <= 0x7fffffffLL &&
+      (reinterpret_cast<uintptr_t>(cache) & 15) == 0 &&
+      make_map(&map_cache, cache, static_cast<int>(cache_rows), HD, HD, page_tokens)) {
+    const int shared = 2 * kSplitKeys * HD * 2 + 1024;   // keys and values, and room to align them to 1024 bytes
+    auto kernel = paged_attention_decode_tma_kernel<HD>;
+    cudaError_t attribute = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, shared);
+    if (attribute != cudaSuccess) return static_cast<int>(attribute);
+    e = launch_chained(kernel, grid, dim3(kDecodeThreads), shared, stream, map_cache,
+                       static_cast<const __nv_bfloat16*>(q), partial, block_tables, max_pages, row_token, row_request,
+                       positions, heads, kv_heads, page_tokens, num_pages, max_splits, window, scale, status);
+  } else {
+    const int shared = 2 * kSplitKeys * (HD * 2 + 16);
+    auto kernel = paged_attention_decode_mma_kernel<HD>;
+    cudaError_t attribute = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, shared);
+    if (attribute != cudaSuccess) return static_cast<int>(attribute);
+    e = launch_chained(kernel, grid, dim3(kDecodeThreads), shared, stream,
+                       static_cast<const __nv_bfloat16*>(q), static_cast<const __nv_bfloat16*>(cache),
+                       partial, block_tables, max_pages, row_token, row_request, positions, heads,
+                       kv_heads, page_tokens, num_pages, max_splits, window, scale, status);
+  }
   if (e != cudaSuccess) return static_cast<int>(e);
   return static_cast<int>(launch_chained(paged_attention_merge_kernel<__nv_bfloat16>, dim3(rows, heads),
                                          dim3(HD <= 64 ? 64 : (HD <= 128 ? 128 : 256)), 0, stream, static_cast<const float*>(partial),

@@ -105,11 +105,12 @@ flash_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __
   uint64_t* p_full = s_full + 2;
   uint64_t* o_full = p_full + 2;
   uint64_t* row_ready = o_full + 2;  // [4]: the softmax warps of a lane group meet here
-  uint32_t& tmem_base_slot = *reinterpret_cast<uint32_t*>(row_ready + 4);
+  uint64_t* v_tail = row_ready + 4;   // the values of a request's last page land here first
+  uint32_t& tmem_base_slot = *reinterpret_cast<uint32_t*>(v_tail + 1);
   volatile int& failed = *reinterpret_cast<volatile int*>(&tmem_base_slot + 1);
   // [tile parity][part][row]: the threads of a row exchange maxima (and, at the end, sums)
   float (*row_max)[kFaParts][kFaRows] = reinterpret_cast<float (*)[kFaParts][kFaRows]>(small + 512);
-  static_assert((1 + 4 * MAX_STAGES + 8 + 4) * 8 + 8 <= 512, "the barriers do not fit their area");
+  static_assert((1 + 4 * MAX_STAGES + 8 + 4 + 1) * 8 + 8 <= 512, "the barriers do not fit their area");
 
   const int head = blockIdx.x, tile = blockIdx.y;  // heads of one tile run side by side and share its keys in L2
   const int kv = head / (heads / kv_heads);
@@ -135,6 +136,7 @@ flash_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __
       barrier_init(&o_full[b], 1);
     }
     for (int g = 0; g < 4; ++g) barrier_init(&row_ready[g], kFaParts * 32);
+    barrier_init(v_tail, 1);
     barrier_init_fence();
     failed = 0;
   }
@@ -169,30 +171,54 @@ flash_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __
     const int copies = pages_per_tile * HALVES;  // every page, every 64-value half
     const int slot = lane / HALVES, half = lane % HALVES;  // copies <= 32: one per lane
     const uint32_t offset = half * kFaHalfBytes + slot * page_tokens * (kTmaColumns * 2);
-    // Pages no row of the tile can see are not looked up: page 0 stands in
-    // (its values are finite and every such key is masked).
+    // Pages no row of the tile can see are not looked up: their box starts
+    // beyond the cache's last row, where the copy engine writes zeros. A
+    // masked key has weight 0, but 0 x NaN is NaN, so nothing is asked of what
+    // the cache holds beyond the request's own positions: the rows of its last
+    // page behind the tile's last position are zeroed here before the MMA
+    // warp may read the values (the keys' scores are replaced, not weighted).
+    constexpr int kNoPage = -0x40000000;
+    const int beyond_cache = num_pages * 2 * kv_heads * page_tokens;
     auto page_of = [&](int i) {
       const int page_key = (tile_begin + i) * kFaKeys + slot * page_tokens;
       if (i < key_tiles && lane < copies && page_key <= last_pos && page_key + page_tokens > first_key &&
           page_key / page_tokens < max_pages)
         return table[page_key / page_tokens];
-      return 0;
+      return kNoPage;
     };
     int page = page_of(0);
     for (int i = 0; i < key_tiles && !failed; ++i) {
       const int stage = i % stages;
       const int upcoming = page_of(i + 1);   // in flight while this tile's requests go out
-      if (page < 0 || page >= num_pages) {
+      if (page != kNoPage && (page < 0 || page >= num_pages)) {
         atomicOr(status, kStatusBadPage);
-        page = 0;
+        page = kNoPage;
       }
+      const int box_row = page == kNoPage ? beyond_cache
+                                          : ((page * 2 + (values ? 1 : 0)) * kv_heads + kv) * page_tokens;
+      // rows [zero_from, zero_to) of the tile: the last page's rows behind the last position
+      const int zero_from = last_pos + 1 - (tile_begin + i) * kFaKeys;
+      const int zero_to = (last_pos / page_tokens + 1) * page_tokens - (tile_begin + i) * kFaKeys;
+      const bool tail = values && i == key_tiles - 1 && zero_from < zero_to;
+      uint64_t* landing = tail ? v_tail : &full[stage];
       // K as soon as the scores that read this stage last are done, V when the P V product is.
       if (!barrier_wait(&empty[stage], ((i / stages) & 1) ^ 1, status)) { failed = 1; break; }
-      if (lane == 0) barrier_arrive_expect(&full[stage], Config::kTileBytes);
+      if (lane == 0) barrier_arrive_expect(landing, Config::kTileBytes);
       __syncwarp();
+      unsigned char* stage_tile = tiles + stage * Config::kTileBytes;
       if (lane < copies)
-        tma_load_2d(tiles + stage * Config::kTileBytes + offset, &map_cache, half * kTmaColumns,
-                    ((page * 2 + (values ? 1 : 0)) * kv_heads + kv) * page_tokens, &full[stage]);
+        tma_load_2d(stage_tile + offset, &map_cache, half * kTmaColumns, box_row, landing);
+      if (tail) {
+        if (!barrier_wait(v_tail, 0, status)) { failed = 1; break; }
+        // a key's 64 values of one half are 128 bytes, swizzled among themselves
+        for (int c = lane; c < (zero_to - zero_from) * HALVES * 8; c += 32)
+          *reinterpret_cast<uint4*>(stage_tile + ((c >> 3) % HALVES) * kFaHalfBytes +
+                                    (zero_from + c / (HALVES * 8)) * (kTmaColumns * 2) + (c & 7) * 16) =
+              make_uint4(0u, 0u, 0u, 0u);
+        asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");   // before the tensor core reads them
+        __syncwarp();
+        if (lane == 0) barrier_arrive(&full[stage]);
+      }
       page = upcoming;
     }
   } else if (warp == 1) {

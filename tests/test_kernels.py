@@ -156,7 +156,7 @@ def run_attention(ops, dtype, q, k, v, lengths, page_tokens, scale, window=0, sh
     rng = np.random.default_rng(shuffle_seed)
     pages_needed = [-(-total // page_tokens) for total, _ in lengths]
     order = rng.permutation(sum(pages_needed) + 3)
-    cache = torch.zeros(len(order), 2, kv_heads, page_tokens, head_dim, dtype=dtype, device="cuda")
+    cache = torch.full((len(order), 2, kv_heads, page_tokens, head_dim), float("nan"), dtype=dtype, device="cuda")
     host_cache = np.zeros(cache.shape)
     width = max(pages_needed)
     tables = np.full((len(lengths), width), -1, dtype=np.int32)
@@ -287,7 +287,8 @@ def run_flash(ops, q, k, v, lengths, page_tokens, scale, window=0, seed=0, kerne
     rng = np.random.default_rng(seed)
     pages_needed = [-(-total // page_tokens) for total, _ in lengths]
     order = rng.permutation(sum(pages_needed) + 3)
-    host_cache = np.zeros((len(order), 2, kv_heads, page_tokens, head_dim))
+    # what no request wrote (free pages, the rest of a last page) is NaN: nothing may be asked of it
+    host_cache = np.full((len(order), 2, kv_heads, page_tokens, head_dim), np.nan)
     tables = np.full((len(lengths), max(pages_needed)), -1, dtype=np.int32)
     cursor = 0
     q_rows, positions, tiles = [], [], []
@@ -374,7 +375,8 @@ def run_decode_attention(ops, dtype, q, k, v, totals, page_tokens, scale, window
     rng = np.random.default_rng(seed)
     pages_needed = [-(-total // page_tokens) for total in totals]
     order = rng.permutation(sum(pages_needed) + 2)
-    host_cache = np.zeros((len(order), 2, kv_heads, page_tokens, head_dim))
+    # what no request wrote (free pages, the rest of a last page) is NaN: nothing may be asked of it
+    host_cache = np.full((len(order), 2, kv_heads, page_tokens, head_dim), np.nan)
     tables = np.full((len(totals), max(pages_needed)), -1, dtype=np.int32)
     cursor = 0
     for r, total in enumerate(totals):
