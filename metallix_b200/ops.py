@@ -53,7 +53,8 @@ _SIGNATURES = {
     "mxb_gemm_tcgen05": [_P, _P, _P, _I, _I, _I, _L, _L, _L, _I, _P, _P],
     "mxb_gemm_tcgen05_supported": [_I, _I, _I, _L, _L],
     "mxb_silu_mul": [_P, _P, _I, _L, _I, _P],
-    "mxb_argmax": [_P, _L, _I, _I, _P, _P, _P],
+    "mxb_argmax": [_P, _L, _I, _I, _P, _P, _P, _P],
+    "mxb_argmax_pieces": [_I, _I],
     "mxb_sample_icdf": [_P, _L, _I, _I, _P, _P, _P, _P, _P, _P, _P, _P],
     "mxb_sample_race": [_P, _L, _I, _I, _P, _P, _P, _P, _P, _P, _P],
     "mxb_set_chained_launches": [_I],
@@ -661,8 +662,12 @@ def argmax(logits: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Te
     if out is None:
         out = torch.empty(rows, dtype=torch.int32, device=logits.device)
     _check(out, "out", (torch.int32,), 1)
-    _call("mxb_argmax", logits.data_ptr(), stride, rows, vocab, out.data_ptr(),
+    # the first pass leaves one (value, index) pair per piece of a row here
+    scratch = torch.empty(rows * _fn("mxb_argmax_pieces")(rows, vocab), dtype=torch.int64, device=logits.device)
+    _call("mxb_argmax", logits.data_ptr(), stride, rows, vocab, out.data_ptr(), scratch.data_ptr(),
           status_word(logits.device).data_ptr(), _stream())
+    global _launches
+    _launches += 1   # two kernels
     return out
 
 

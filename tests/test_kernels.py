@@ -636,6 +636,23 @@ def test_argmax_first_maximum_and_finite_flag(ops):
         ops.check_status("cuda")
 
 
+@pytest.mark.parametrize("rows, vocab", [(1, 7), (3, 5000), (64, 4096), (300, 2051), (2, 70_001)])
+def test_argmax_in_pieces(ops, rows, vocab):
+    """A row is cut into pieces; ties within a piece, across pieces and at a
+    piece's edge go to the lower id, and rows of any length and alignment work."""
+    rng = np.random.default_rng(rows + vocab)
+    logits = rng.normal(size=(rows, vocab)).astype(np.float32)
+    for r in range(rows):
+        where = rng.integers(0, vocab, size=3)
+        logits[r, where] = 7.0 + r % 2
+    logits[0, [0, vocab - 1]] = 20.0
+    ids = ops.argmax(dev(logits)).tolist()
+    ops.check_status("cuda")
+    assert ids == [plain.greedy_pick(row) for row in logits] and ids[0] == 0
+    strided = dev(np.concatenate([logits, logits], axis=1))[:, 1:vocab + 1]   # rows that start off a 16-byte boundary
+    assert ops.argmax(strided).tolist() == [plain.greedy_pick(row) for row in strided.cpu().numpy()]
+
+
 @pytest.mark.parametrize("vocab", [8, 331, 5000])
 def test_sample_icdf_matches_the_host_definition(ops, vocab):
     rng = np.random.default_rng(vocab)
