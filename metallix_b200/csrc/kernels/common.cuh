@@ -137,6 +137,29 @@ inline cudaError_t launch_chained(void (*kernel)(KernelArgs...), dim3 grid, dim3
   return cudaLaunchKernelEx(&config, kernel, static_cast<KernelArgs>(args)...);
 }
 
+// The same for a kernel whose blocks run as clusters of `cluster_x` along x
+// (grid.x a multiple of it): the blocks of a cluster are resident together and
+// read one another's shared memory.
+template <typename... KernelArgs, typename... Args>
+inline cudaError_t launch_chained_clusters(void (*kernel)(KernelArgs...), dim3 grid, dim3 block, size_t shared,
+                                           unsigned cluster_x, cudaStream_t stream, Args... args) {
+  cudaLaunchConfig_t config = {};
+  config.gridDim = grid;
+  config.blockDim = block;
+  config.dynamicSmemBytes = shared;
+  config.stream = stream;
+  cudaLaunchAttribute attribute[2];
+  attribute[0].id = cudaLaunchAttributeClusterDimension;
+  attribute[0].val.clusterDim.x = cluster_x;
+  attribute[0].val.clusterDim.y = 1;
+  attribute[0].val.clusterDim.z = 1;
+  attribute[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attribute[1].val.programmaticStreamSerializationAllowed = 1;
+  config.attrs = attribute;
+  config.numAttrs = chained_launches() ? 2 : 1;
+  return cudaLaunchKernelEx(&config, kernel, static_cast<KernelArgs>(args)...);
+}
+
 }  // namespace mxb
 
 #define MXB_API extern "C" __attribute__((visibility("default")))

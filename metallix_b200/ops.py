@@ -55,8 +55,9 @@ _SIGNATURES = {
     "mxb_silu_mul": [_P, _P, _I, _L, _I, _P],
     "mxb_argmax": [_P, _L, _I, _I, _P, _P, _P, _P],
     "mxb_argmax_pieces": [_I, _I],
-    "mxb_sample_icdf": [_P, _L, _I, _I, _P, _P, _P, _P, _P, _P, _P, _P],
-    "mxb_sample_race": [_P, _L, _I, _I, _P, _P, _P, _P, _P, _P, _P],
+    "mxb_sample_icdf": [_P, _L, _I, _I, _P, _P, _P, _P, _P, _P, _P, _P, _P],
+    "mxb_icdf_pieces": [_I],
+    "mxb_sample_race": [_P, _L, _I, _I, _P, _P, _P, _P, _P, _P, _P, _P],
     "mxb_set_chained_launches": [_I],
     "mxb_nucleus_mask": [_P, _L, _I, _I, _P, _P, _P, _P, _P, _P],
 }
@@ -688,9 +689,13 @@ def sample_icdf(logits: torch.Tensor, temperature: torch.Tensor, seed: torch.Ten
         _need(legal.shape == (rows, vocab), "legal must be [rows, vocab]")
     if out is None:
         out = torch.empty(rows, dtype=torch.int32, device=logits.device)
+    # per piece of a row: its maximum, its weight, its last id of positive weight
+    scratch = torch.empty(3 * rows * _fn("mxb_icdf_pieces")(vocab), dtype=torch.int64, device=logits.device)
     _call("mxb_sample_icdf", logits.data_ptr(), stride, rows, vocab, temperature.data_ptr(),
           seed.data_ptr(), stream_id.data_ptr(), position.data_ptr(), _ptr(legal), out.data_ptr(),
-          status_word(logits.device).data_ptr(), _stream())
+          scratch.data_ptr(), status_word(logits.device).data_ptr(), _stream())
+    global _launches
+    _launches += 2   # three kernels
     return out
 
 
@@ -709,9 +714,12 @@ def sample_race(logits: torch.Tensor, temperature: torch.Tensor, seed: torch.Ten
         _need(legal.shape == (rows, vocab), "legal must be [rows, vocab]")
     if out is None:
         out = torch.empty(rows, dtype=torch.int32, device=logits.device)
+    scratch = torch.empty(2 * rows * _fn("mxb_argmax_pieces")(rows, vocab), dtype=torch.int64, device=logits.device)
     _call("mxb_sample_race", logits.data_ptr(), stride, rows, vocab, temperature.data_ptr(),
-          seed.data_ptr(), position.data_ptr(), _ptr(legal), out.data_ptr(),
+          seed.data_ptr(), position.data_ptr(), _ptr(legal), out.data_ptr(), scratch.data_ptr(),
           status_word(logits.device).data_ptr(), _stream())
+    global _launches
+    _launches += 1   # two kernels
     return out
 
 

@@ -718,6 +718,29 @@ def test_nucleus_mask(ops, top_p, top_k):
         assert np.array_equal(mask[r], ref), (r, mask[r].sum(), ref.sum())
 
 
+@pytest.mark.parametrize("vocab", [7, 151_936, 400_003])
+def test_nucleus_mask_of_long_and_short_rows(ops, vocab):
+    """A row lies in the shared memory of its eight blocks where it fits
+    (151,936 does, 400,003 does not); seven tokens leave some blocks empty."""
+    rng = np.random.default_rng(vocab)
+    logits = (rng.normal(size=(3, vocab)) * 2.0).astype(np.float32)
+    logits[1, vocab // 2:] = logits[1, 0]            # a plateau of equal logits that the cut may cross
+    temperature = np.array([1.0, 0.6, 1.3])
+    for top_p, top_k in ((0.9, 0), (0.5, 40), (1.0, 3), (0.97, vocab - 1)):
+        mask = ops.nucleus_mask(dev(logits), dev(temperature, torch.float64), dev(np.full(3, top_p), torch.float64),
+                                dev(np.full(3, top_k), torch.int32)).cpu().numpy().astype(bool)
+        ops.check_status("cuda")
+        for r in range(3):
+            ref = plain.nucleus_mask(logits[r], float(temperature[r]), top_p, top_k or None)
+            assert np.array_equal(mask[r], ref), (top_p, top_k, r, mask[r].sum(), ref.sum())
+    logits[2, 5] = np.nan
+    mask = ops.nucleus_mask(dev(logits), dev(temperature, torch.float64), dev(np.full(3, 0.9), torch.float64),
+                            dev(np.zeros(3), torch.int32)).cpu().numpy().astype(bool)
+    assert mask[2].all() and np.array_equal(mask[0], plain.nucleus_mask(logits[0], 1.0, 0.9, None))
+    with pytest.raises(ops.KernelError, match="non-finite"):
+        ops.check_status("cuda")
+
+
 def test_timeline_needs_a_build_of_its_own(ops):
     """The usual library records no timeline and says how to get one."""
     with pytest.raises(ops.KernelError, match="METALLIX_B200_TIMELINE"):
