@@ -92,38 +92,6 @@ __global__ void qk_norm_rope_cache_kernel(
   }
 }
 
-// Sixteen bytes of T as floats and back. bfloat16 is the upper half of a
-// float: a shift or a mask unpacks it, and one instruction rounds and packs two.
-template <typename T> struct Sixteen;
-template <> struct Sixteen<float> {
-  static constexpr int V = 4;
-  static __device__ __forceinline__ void unpack(const uint4& w, float (&x)[4]) {
-    x[0] = __uint_as_float(w.x); x[1] = __uint_as_float(w.y); x[2] = __uint_as_float(w.z); x[3] = __uint_as_float(w.w);
-  }
-  static __device__ __forceinline__ uint4 pack(const float (&x)[4]) {
-    return make_uint4(__float_as_uint(x[0]), __float_as_uint(x[1]), __float_as_uint(x[2]), __float_as_uint(x[3]));
-  }
-};
-template <> struct Sixteen<__nv_bfloat16> {
-  static constexpr int V = 8;
-  static __device__ __forceinline__ void unpack(const uint4& w, float (&x)[8]) {
-    const uint32_t words[4] = {w.x, w.y, w.z, w.w};
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      x[2 * i] = __uint_as_float(words[i] << 16);
-      x[2 * i + 1] = __uint_as_float(words[i] & 0xffff0000u);
-    }
-  }
-  static __device__ __forceinline__ uint32_t two(float lo, float hi) {
-    uint32_t d;
-    asm("cvt.rn.bf16x2.f32 %0, %1, %2;\n" : "=r"(d) : "f"(hi), "f"(lo));
-    return d;
-  }
-  static __device__ __forceinline__ uint4 pack(const float (&x)[8]) {
-    return make_uint4(two(x[0], x[1]), two(x[2], x[3]), two(x[4], x[5]), two(x[6], x[7]));
-  }
-};
-
 // V values of type T moved as one access of V * sizeof(T) bytes.
 template <typename T, int V> struct alignas(sizeof(T) * V) Pack { T v[V]; };
 
@@ -134,12 +102,6 @@ template <typename T, int V> struct alignas(sizeof(T) * V) Pack { T v[V]; };
 // / 2) sits in the same lane; head_dim / (2 V) lanes make up a head, a warp
 // takes 32 / that many heads at once, and the sum of squares runs over a
 // head's lanes only.
-//
-// The grid is (groups of heads, rows of tokens): a thread keeps its head, so
-// what does not depend on the token (which head, its norm weights) is done
-// once, and walks down the tokens blockIdx.y, blockIdx.y + gridDim.y, ... with
-// the next token's values on their way while it works on this one's. A long
-// prompt is one resident wave of blocks this way instead of two and a part.
 template <typename T, int HD>
 __global__ void __launch_bounds__(256)
 qk_norm_rope_cache_warp_kernel(
@@ -149,32 +111,55 @@ qk_norm_rope_cache_warp_kernel(
     const float* __restrict__ q_weight, const float* __restrict__ k_weight,
     const float* __restrict__ cos_table, const float* __restrict__ sin_table, int table_positions,
     int tokens, int heads, int kv_heads, int page_tokens, int num_pages, float eps, int* status) {
-  constexpr int V = Sixteen<T>::V;
+  constexpr int V = 16 / static_cast<int>(sizeof(T));
   constexpr int HALF = HD / 2;
   constexpr int LANES = HALF / V;          // lanes of a head
   constexpr int HEADS = 32 / LANES;        // heads of a warp
   static_assert(LANES >= 1 && LANES <= 32 && (LANES & (LANES - 1)) == 0, "a head's lanes must divide a warp");
+  using Values = Pack<T, V>;
   using Floats = Pack<float, 4>;
   chain_release();
   // Up to chain_wait(): only the step's integers, the norm weights and the
   // cos/sin tables, none of which a kernel of this step writes.
   const int lane = threadIdx.x & 31, sub = lane % LANES;
-  const int h = (blockIdx.x * 8 + (threadIdx.x >> 5)) * HEADS + lane / LANES;  // among a token's q, k and v heads
+  const int per_token = heads + 2 * kv_heads;
+  const long long total = static_cast<long long>(tokens) * per_token;
+  const long long item = (static_cast<long long>(blockIdx.x) * 8 + (threadIdx.x >> 5)) * HEADS + lane / LANES;
   // Lanes without work stay to the end: the sums below shuffle within a head's lanes.
-  const bool in_range = h < heads + 2 * kv_heads;
+  bool active = item < total;
+  const int t = active ? static_cast<int>(item / per_token) : 0, h = active ? static_cast<int>(item % per_token) : 0;
   const bool is_q = h < heads;
   const bool is_k = !is_q && h < heads + kv_heads;
   const int kv = is_q ? 0 : (is_k ? h - heads : h - heads - kv_heads);
+  const T* src = is_q ? q_in + t * q_stride + static_cast<long long>(h) * HD
+               : is_k ? k_in + t * k_stride + static_cast<long long>(kv) * HD
+                      : v_in + t * v_stride + static_cast<long long>(kv) * HD;
+  T* dst = nullptr;
+  if (is_q) {
+    if (q_out == nullptr) active = false;
+    else dst = q_out + (static_cast<size_t>(t) * heads + h) * HD;
+  } else if (slots == nullptr || cache == nullptr) {
+    active = false;
+  } else if (active) {
+    const int slot = slots[t];
+    const int page = slot / page_tokens, row = slot - page * page_tokens;
+    if (slot < 0) {
+      active = false;
+    } else if (page >= num_pages) {
+      if (sub == 0) atomicOr(status, kStatusBadSlot);
+      active = false;
+    } else {
+      dst = cache + (((static_cast<size_t>(page) * 2 + (is_k ? 0 : 1)) * kv_heads + kv) * page_tokens + row) * HD;
+    }
+  }
   const bool plain_copy = !is_q && !is_k;   // values: no norm, no rotation
-  const bool writes = in_range && (is_q ? q_out != nullptr : slots != nullptr && cache != nullptr);
   const float* weight = is_q ? q_weight : k_weight;
-  const T* src_head = is_q ? q_in + static_cast<long long>(h) * HD
-                    : is_k ? k_in + static_cast<long long>(kv) * HD : v_in + static_cast<long long>(kv) * HD;
-  const long long src_stride = is_q ? q_stride : (is_k ? k_stride : v_stride);
-  float gain[2 * V];
+  float gain[2 * V], c[V], sn[V];
 #pragma unroll
   for (int j = 0; j < 2 * V; ++j) gain[j] = 1.0f;
-  if (writes && !plain_copy && weight != nullptr) {
+#pragma unroll
+  for (int j = 0; j < V; ++j) { c[j] = 1.0f; sn[j] = 0.0f; }
+  if (active && !plain_copy && weight != nullptr) {
 #pragma unroll
     for (int q4 = 0; q4 < V / 4; ++q4) {
       const Floats lo = reinterpret_cast<const Floats*>(weight + V * sub)[q4];
@@ -186,105 +171,71 @@ qk_norm_rope_cache_warp_kernel(
       }
     }
   }
-  // Where token t's head goes (null: nowhere) and the row of the tables it is rotated by.
-  auto target = [&](int t, int& pos) -> T* {
-    T* dst = nullptr;
-    pos = 0;
-    if (!writes) return dst;
-    if (is_q) {
-      dst = q_out + (static_cast<size_t>(t) * heads + h) * HD;
-    } else {
-      const int slot = slots[t];
-      const int page = slot / page_tokens, row = slot - page * page_tokens;
-      if (slot < 0) return dst;   // a token that is not to be cached
-      if (page >= num_pages) {
-        if (sub == 0) atomicOr(status, kStatusBadSlot);
-        return dst;
-      }
-      dst = cache + (((static_cast<size_t>(page) * 2 + (is_k ? 0 : 1)) * kv_heads + kv) * page_tokens + row) * HD;
+  if (active && !plain_copy && cos_table != nullptr) {
+    int pos = positions[t];
+    if (pos < 0 || pos >= table_positions) {
+      if (sub == 0) atomicOr(status, kStatusBadSlot);
+      pos = 0;
     }
-    if (!plain_copy && cos_table != nullptr) {
-      pos = positions[t];
-      if (pos < 0 || pos >= table_positions) {
-        if (sub == 0) atomicOr(status, kStatusBadSlot);
-        pos = 0;
+#pragma unroll
+    for (int q4 = 0; q4 < V / 4; ++q4) {
+      const Floats cs = reinterpret_cast<const Floats*>(cos_table + static_cast<size_t>(pos) * HALF + V * sub)[q4];
+      const Floats ss = reinterpret_cast<const Floats*>(sin_table + static_cast<size_t>(pos) * HALF + V * sub)[q4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        c[q4 * 4 + j] = cs.v[j];
+        sn[q4 * 4 + j] = ss.v[j];
       }
     }
-    return dst;
-  };
-  int t = blockIdx.y, pos = 0;   // the same tokens for every thread of the block
-  T* dst = target(t, pos);
+  }
   chain_wait();
-  src_head = behind_wait(src_head);  // written by the kernel ahead of this one
-  uint4 in_lo = make_uint4(0u, 0u, 0u, 0u), in_hi = in_lo;
-  if (writes) {
-    in_lo = reinterpret_cast<const uint4*>(src_head + t * src_stride)[sub];
-    in_hi = reinterpret_cast<const uint4*>(src_head + t * src_stride + HALF)[sub];
+  src = behind_wait(src);  // written by the kernel ahead of this one
+  Values in_lo = {}, in_hi = {};
+  if (active) {
+    in_lo = reinterpret_cast<const Values*>(src)[sub];
+    in_hi = reinterpret_cast<const Values*>(src + HALF)[sub];
   }
-  for (; t < tokens; t += gridDim.y) {
-    const int t_next = t + gridDim.y;
-    int pos_next = 0;
-    T* dst_next = nullptr;
-    uint4 next_lo = make_uint4(0u, 0u, 0u, 0u), next_hi = next_lo;
-    if (t_next < tokens) {
-      if (writes) {
-        next_lo = reinterpret_cast<const uint4*>(src_head + t_next * src_stride)[sub];
-        next_hi = reinterpret_cast<const uint4*>(src_head + t_next * src_stride + HALF)[sub];
-      }
-      dst_next = target(t_next, pos_next);
+  if (plain_copy) {   // the same for every lane of a head; other heads of the warp go on below
+    if (active) {
+      reinterpret_cast<Values*>(dst)[sub] = in_lo;
+      reinterpret_cast<Values*>(dst + HALF)[sub] = in_hi;
     }
-    const bool active = dst != nullptr;
-    if (plain_copy) {   // the same for every lane of a head; other heads of the warp go on below
-      if (active) {
-        reinterpret_cast<uint4*>(dst)[sub] = in_lo;
-        reinterpret_cast<uint4*>(dst + HALF)[sub] = in_hi;
-      }
-    }
-    float lo[V], hi[V];
-    Sixteen<T>::unpack(in_lo, lo);
-    Sixteen<T>::unpack(in_hi, hi);
-    float sum = 0.0f;
-#pragma unroll
-    for (int j = 0; j < V; ++j) sum += lo[j] * lo[j];
-#pragma unroll
-    for (int j = 0; j < V; ++j) sum += hi[j] * hi[j];
-#pragma unroll
-    for (int offset = LANES / 2; offset > 0; offset >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, offset);
-    if (weight != nullptr) {
-      const float scale = rsqrtf(sum / static_cast<float>(HD) + eps);
-#pragma unroll
-      for (int j = 0; j < V; ++j) {
-        lo[j] = lo[j] * scale * gain[j];
-        hi[j] = hi[j] * scale * gain[V + j];
-      }
-    }
-    if (active && !plain_copy && cos_table != nullptr) {
-      // one row of the tables serves all heads of a token: these loads hit the first-level cache
-      const float* cos_row = cos_table + static_cast<size_t>(pos) * HALF + V * sub;
-      const float* sin_row = sin_table + static_cast<size_t>(pos) * HALF + V * sub;
-#pragma unroll
-      for (int q4 = 0; q4 < V / 4; ++q4) {
-        const float4 c = reinterpret_cast<const float4*>(cos_row)[q4];
-        const float4 sn = reinterpret_cast<const float4*>(sin_row)[q4];
-        const float cs[4] = {c.x, c.y, c.z, c.w}, ss[4] = {sn.x, sn.y, sn.z, sn.w};
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          // element V sub + 4 q4 + j (below HALF) and its partner HALF further
-          const float x = lo[q4 * 4 + j], y = hi[q4 * 4 + j];
-          lo[q4 * 4 + j] = x * cs[j] - y * ss[j];
-          hi[q4 * 4 + j] = y * cs[j] + x * ss[j];
-        }
-      }
-    }
-    if (active && !plain_copy) {
-      reinterpret_cast<uint4*>(dst)[sub] = Sixteen<T>::pack(lo);
-      reinterpret_cast<uint4*>(dst + HALF)[sub] = Sixteen<T>::pack(hi);
-    }
-    dst = dst_next;
-    pos = pos_next;
-    in_lo = next_lo;
-    in_hi = next_hi;
+    active = false;
   }
+  float x[2 * V];
+  float sum = 0.0f;
+#pragma unroll
+  for (int j = 0; j < V; ++j) {
+    x[j] = to_float(in_lo.v[j]);
+    x[V + j] = to_float(in_hi.v[j]);
+  }
+#pragma unroll
+  for (int j = 0; j < 2 * V; ++j) sum += x[j] * x[j];
+#pragma unroll
+  for (int offset = LANES / 2; offset > 0; offset >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, offset);
+  if (weight != nullptr) {
+    const float scale = rsqrtf(sum / static_cast<float>(HD) + eps);
+#pragma unroll
+    for (int j = 0; j < 2 * V; ++j) x[j] = x[j] * scale * gain[j];
+  }
+  if (cos_table != nullptr) {
+#pragma unroll
+    for (int j = 0; j < V; ++j) {
+      // element V sub + j (below HALF) and its partner HALF further, x[V + j]
+      const float lo = x[j], hi = x[V + j];
+      x[j] = lo * c[j] - hi * sn[j];
+      x[V + j] = hi * c[j] + lo * sn[j];
+    }
+  }
+  if (!active) return;
+  Values out_lo, out_hi;
+#pragma unroll
+  for (int j = 0; j < V; ++j) {
+    out_lo.v[j] = from_float<T>(x[j]);
+    out_hi.v[j] = from_float<T>(x[V + j]);
+  }
+  reinterpret_cast<Values*>(dst)[sub] = out_lo;
+  reinterpret_cast<Values*>(dst + HALF)[sub] = out_hi;
 }
 
 }  // namespace mxb
@@ -309,19 +260,11 @@ MXB_API int mxb_qk_norm_rope_cache(
                          aligned(cos_table, 0) && aligned(sin_table, 0);
   if ((head_dim == 64 || head_dim == 128 || head_dim == 256) && (cos_table == nullptr || rotary_dim == head_dim) &&
       vector_ok && (dtype == kF32 || dtype == kBF16)) {
-    const int heads_per_block = 8 * (32 / (head_dim / 2 / (16 / element)));
-    const int head_groups = (heads + 2 * kv_heads + heads_per_block - 1) / heads_per_block;
-    static int resident = 0;   // blocks of 256 threads the device holds at once, four to an SM
-    if (resident == 0) {
-      int device = 0, sms = 0;
-      cudaGetDevice(&device);
-      cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device);
-      resident = 4 * (sms > 0 ? sms : 1);
-    }
-    const int token_rows = tokens < resident / head_groups ? tokens : (resident / head_groups > 0 ? resident / head_groups : 1);
-    const dim3 grid(head_groups, token_rows);
+    const long long items = static_cast<long long>(tokens) * (heads + 2 * kv_heads);
+    const int heads_per_warp = 32 / (head_dim / 2 / (16 / element));
+    const unsigned blocks = static_cast<unsigned>((items + 8 * heads_per_warp - 1) / (8 * heads_per_warp));
     cudaError_t launch_status = cudaSuccess;
-#define WARP_LAUNCH(T, HD) launch_status = launch_chained(qk_norm_rope_cache_warp_kernel<T, HD>, grid, dim3(256), 0, stream, \
+#define WARP_LAUNCH(T, HD) launch_status = launch_chained(qk_norm_rope_cache_warp_kernel<T, HD>, dim3(blocks), dim3(256), 0, stream, \
         static_cast<const T*>(q_in), static_cast<const T*>(k_in), static_cast<const T*>(v_in), q_stride, k_stride, \
         v_stride, static_cast<T*>(q_out), static_cast<T*>(cache), slots, positions, q_weight, k_weight, cos_table, \
         sin_table, table_positions, tokens, heads, kv_heads, page_tokens, num_pages, eps, status)
