@@ -43,7 +43,7 @@ def main(argv=None) -> int:
     parser.add_argument("--swiglu", action="store_true", help="gemm: the fused SwiGLU epilogue (n = 2 * inter)")
     parser.add_argument("--context", type=int, default=0, help="attention: keys already in the cache")
     parser.add_argument("--kernel", default="both", choices=("both", "tcgen05", "mma"))
-    parser.add_argument("--page-tokens", type=int, default=16, help="attention: tokens per cache page")
+    parser.add_argument("--page-tokens", type=int, default=16, help="tokens per cache page")
     args = parser.parse_args(argv)
 
     import numpy as np
@@ -107,8 +107,8 @@ def main(argv=None) -> int:
         return 0
 
     config = Qwen3Config.from_dict(dict(QWEN3_0_6B, num_hidden_layers=args.layers))
-    pages = args.batch * (-(-(args.prompt_len + 64) // 16)) + 64
-    engine = Engine.from_random(config, 0, dtype="bfloat16", page_tokens=16, num_pages=pages,
+    pages = args.batch * (-(-(args.prompt_len + 64) // args.page_tokens) + 1) + 64 * 16 // args.page_tokens
+    engine = Engine.from_random(config, 0, dtype="bfloat16", page_tokens=args.page_tokens, num_pages=pages,
                                 max_requests=args.batch + 2, max_context=max(4096, args.prompt_len + 256),
                                 cuda_graphs=args.graphs or args.timeline)   # the timeline is of the step as it serves
     rng = np.random.default_rng(0)
