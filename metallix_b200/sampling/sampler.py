@@ -59,6 +59,55 @@ def _u64(values: Sequence[int], device) -> torch.Tensor:
     return torch.tensor(signed, dtype=torch.int64, device=device)
 
 
+class _RowTensors:
+    """What the kernels want to know about the rows of a batch, on the device.
+    Everything but the generated positions is a function of the rows'
+    SamplingParams, which stay the same from step to step while the same
+    requests decode: it is built once per batch composition. The positions go
+    through pinned memory, without a stop of the host."""
+
+    def __init__(self, params: Sequence[SamplingParams], device):
+        self.methods = [GREEDY if p.greedy else SAMPLERS[p.sampler] for p in params]
+        self.codes = sorted(set(self.methods))
+        self.temperature = torch.tensor([p.temperature if not p.greedy else 1.0 for p in params],
+                                        dtype=torch.float64, device=device)
+        self.seed = _u64([p.seed for p in params], device)
+        self.stream = _u64([p.stream for p in params], device)
+        self.truncates = any(p.truncates and not p.greedy for p in params)
+        if self.truncates:
+            self.top_p = torch.tensor([p.top_p if not p.greedy else 1.0 for p in params],
+                                      dtype=torch.float64, device=device)
+            self.top_k = torch.tensor([p.top_k if not p.greedy else 0 for p in params],
+                                      dtype=torch.int32, device=device)
+        self.method = torch.tensor(self.methods, dtype=torch.int32, device=device)
+        self.is_code = {code: self.method == code for code in self.codes} if len(self.codes) > 1 else {}
+        self.position = torch.zeros(len(params), dtype=torch.int32, device=device)
+        # two staging buffers: the copy out of one may still be queued while the next step fills the other
+        self.staging = [torch.zeros(len(params), dtype=torch.int32, pin_memory=True) for _ in range(2)]
+        self.turn = 0
+
+    def positions(self, generated_positions: Sequence[int]) -> torch.Tensor:
+        staging = self.staging[self.turn]
+        self.turn ^= 1
+        staging.numpy()[:] = generated_positions
+        self.position.copy_(staging, non_blocking=True)
+        return self.position
+
+
+_ROWS: "dict[tuple, _RowTensors]" = {}
+_ROWS_KEPT = 64
+
+
+def _row_tensors(params: Sequence[SamplingParams], device) -> _RowTensors:
+    key = (str(device), tuple(params))
+    found = _ROWS.get(key)
+    if found is None:
+        if len(_ROWS) >= _ROWS_KEPT:
+            _ROWS.pop(next(iter(_ROWS)))   # the oldest composition
+        found = _ROWS[key] = _RowTensors(params, device)
+    return found
+
+
 def pick(logits: torch.Tensor, params: Sequence[SamplingParams],
          generated_positions: Sequence[int]) -> torch.Tensor:
     """Token ids (int32, on the device) for logits ``[rows, vocab]``; row r is
@@ -66,30 +115,18 @@ def pick(logits: torch.Tensor, params: Sequence[SamplingParams],
     rows = logits.shape[0]
     if len(params) != rows or len(generated_positions) != rows:
         raise ValueError("one SamplingParams and one position per row")
-    methods = [GREEDY if p.greedy else SAMPLERS[p.sampler] for p in params]
-    if all(m == GREEDY for m in methods):
+    if all(p.greedy for p in params):
         return ops.argmax(logits)
-    device = logits.device
-    temperature = torch.tensor([p.temperature if not p.greedy else 1.0 for p in params],
-                               dtype=torch.float64, device=device)
-    seed = _u64([p.seed for p in params], device)
-    stream = _u64([p.stream for p in params], device)
-    position = torch.tensor(list(generated_positions), dtype=torch.int32, device=device)
-    legal = None
-    if any(p.truncates and not p.greedy for p in params):
-        top_p = torch.tensor([p.top_p if not p.greedy else 1.0 for p in params],
-                             dtype=torch.float64, device=device)
-        top_k = torch.tensor([p.top_k if not p.greedy else 0 for p in params],
-                             dtype=torch.int32, device=device)
-        legal = ops.nucleus_mask(logits, temperature, top_p, top_k)
+    row = _row_tensors(params, logits.device)
+    position = row.positions(generated_positions)
+    legal = ops.nucleus_mask(logits, row.temperature, row.top_p, row.top_k) if row.truncates else None
     result = None
-    method = torch.tensor(methods, dtype=torch.int32, device=device)
-    for code in sorted(set(methods)):
+    for code in row.codes:
         if code == GREEDY:
             ids = ops.argmax(logits)
         elif code == ICDF:
-            ids = ops.sample_icdf(logits, temperature, seed, stream, position, legal)
+            ids = ops.sample_icdf(logits, row.temperature, row.seed, row.stream, position, legal)
         else:
-            ids = ops.sample_race(logits, temperature, seed, position, legal)
-        result = ids if result is None else torch.where(method == code, ids, result)
+            ids = ops.sample_race(logits, row.temperature, row.seed, position, legal)
+        result = ids if result is None else torch.where(row.is_code[code], ids, result)
     return result
