@@ -733,6 +733,8 @@ def nucleus_mask(logits: torch.Tensor, temperature: torch.Tensor, top_p: torch.T
     _check(top_k, "top_k", (torch.int32,), 1)
     _need(temperature.numel() == rows and top_p.numel() == rows and top_k.numel() == rows,
           "one temperature, top_p and top_k per row")
+    _need(vocab <= 1 << 22, f"the top-k/top-p kernel takes vocabularies up to {1 << 22} ids, not {vocab}")
+    _need(rows <= 65535, f"the top-k/top-p kernel takes up to 65535 rows at a time, not {rows}")
     if out is None:
         out = torch.empty((rows, vocab), dtype=torch.uint8, device=logits.device)
     _check(out, "out", (torch.uint8,), 2)
