@@ -653,6 +653,7 @@ def silu_mul(gate_up: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch
 def _logit_rows(logits: torch.Tensor):
     _need(logits.is_cuda and logits.dtype == torch.float32 and logits.dim() == 2 and logits.stride(1) == 1,
           "logits must be CUDA float32 [rows, vocab] with contiguous rows")
+    _need(logits.shape[0] <= 65535, f"the pick kernels take up to 65535 rows at a time, not {logits.shape[0]}")
     return logits.shape[0], logits.shape[1], logits.stride(0)
 
 
@@ -734,7 +735,6 @@ def nucleus_mask(logits: torch.Tensor, temperature: torch.Tensor, top_p: torch.T
     _need(temperature.numel() == rows and top_p.numel() == rows and top_k.numel() == rows,
           "one temperature, top_p and top_k per row")
     _need(vocab <= 1 << 22, f"the top-k/top-p kernel takes vocabularies up to {1 << 22} ids, not {vocab}")
-    _need(rows <= 65535, f"the top-k/top-p kernel takes up to 65535 rows at a time, not {rows}")
     if out is None:
         out = torch.empty((rows, vocab), dtype=torch.uint8, device=logits.device)
     _check(out, "out", (torch.uint8,), 2)
