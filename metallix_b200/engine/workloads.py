@@ -118,6 +118,16 @@ def main(argv=None) -> int:
             engine.step([StepEntry("p", ids, [args.prompt_len - 1])])
             engine.release("p")
         torch.cuda.synchronize()
+        if args.graphs:   # the step is replayed as a graph from its second occurrence on
+            start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            start.record()
+            for _ in range(5):
+                engine.step([StepEntry("p", ids, [args.prompt_len - 1])])
+                engine.release("p")
+            end.record()
+            torch.cuda.synchronize()
+            milliseconds = start.elapsed_time(end) / 5
+            print(f"{milliseconds:.4f} ms per prompt step, {args.prompt_len / milliseconds * 1e3:.0f} tokens/s")
     else:
         names = [f"r{i}" for i in range(args.batch)]
         for first in range(0, args.batch, 4):
