@@ -11,6 +11,8 @@ from ..config.spec import PartSpec
 from .linear import Linear
 from .registry import Runtime, StepContext, WeightStore, register_part
 
+FUSED_ACTIVATION_ROWS = 1536   # from here on "auto" takes the tcgen05 product with the SwiGLU epilogue
+
 
 class SwiGLU:
     kind = "swiglu"
@@ -32,7 +34,14 @@ class SwiGLU:
                 and ops.gemm_skinny_takes(x, self.gate_up.weight, swiglu=True)):
             # A decode step: gate, up and the activation in one pass over the weights.
             return self.down.forward(ops.gemm_skinny(x, self.gate_up.weight, swiglu=True))
-        if self.gate_up.dtype == torch.bfloat16 and self.gate_up.backend in ("auto", "tcgen05"):
+        # From about 1,500 rows on the tcgen05 product with the activation in its
+        # epilogue beats the library's product followed by an activation pass
+        # (28 against 31 us at 2,048 rows of this model; 21 against 19 at 1,024,
+        # 10 against 8 at 128): below that the library keeps the product, as in
+        # the reference, unless the part is told to use the tcgen05 kernel.
+        fused = self.gate_up.backend == "tcgen05" or (self.gate_up.backend == "auto"
+                                                      and x.shape[0] >= FUSED_ACTIVATION_ROWS)
+        if self.gate_up.dtype == torch.bfloat16 and fused:
             from .. import tensor_core
             if tensor_core.supports(x, self.gate_up.weight, torch.bfloat16):
                 # gate, up and the activation in the product's epilogue
