@@ -76,7 +76,7 @@ flash_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __
                              const int* __restrict__ tile_request, const int* __restrict__ tile_start,
                              const int* __restrict__ tile_length, const int* __restrict__ positions, int heads,
                              int kv_heads, int page_tokens, int num_pages, int window, float scale,
-                             int shared_bytes, int* status) {
+                             int shared_bytes, float* __restrict__ partial, int* status) {
   using Config = FaConfig<HD>;
   constexpr int MAX_STAGES = Config::kKeyStages;
   constexpr int HALVES = Config::kHalves;
@@ -119,8 +119,16 @@ flash_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __
   const int pos0 = positions[t0];
   const int last_pos = pos0 + n - 1;
   const int first_key = window > 0 ? max(0, pos0 - window + 1) : 0;
-  const int tile_begin = first_key / kFaKeys, tile_end = last_pos / kFaKeys;
-  const int key_tiles = tile_end - tile_begin + 1;
+  // The key tiles of this query tile. With gridDim.z > 1 they are shared out
+  // among that many blocks (a portion of a prompt behind a long context is few
+  // query tiles with many key tiles each: this way it still fills the GPU);
+  // each block then leaves its unnormalised output, maximum and sum in
+  // `partial` and a second kernel puts them together. A block's share may be empty.
+  const int all_begin = first_key / kFaKeys, all_end = last_pos / kFaKeys;   // all_end holds the tile's last position
+  const int all_tiles = all_end - all_begin + 1;
+  const int shares = gridDim.z, share = blockIdx.z;
+  const int tile_begin = all_begin + static_cast<int>(static_cast<long long>(share) * all_tiles / shares);
+  const int key_tiles = all_begin + static_cast<int>(static_cast<long long>(share + 1) * all_tiles / shares) - tile_begin;
 
   if (threadIdx.x == 0) {
     barrier_init(q_full, 1);
@@ -199,7 +207,7 @@ flash_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __
       // rows [zero_from, zero_to) of the tile: the last page's rows behind the last position
       const int zero_from = last_pos + 1 - (tile_begin + i) * kFaKeys;
       const int zero_to = (last_pos / page_tokens + 1) * page_tokens - (tile_begin + i) * kFaKeys;
-      const bool tail = values && i == key_tiles - 1 && zero_from < zero_to;
+      const bool tail = values && tile_begin + i == all_end && zero_from < zero_to;
       uint64_t* landing = tail ? v_tail : &full[stage];
       // K as soon as the scores that read this stage last are done, V when the P V product is.
       if (!barrier_wait(&empty[stage], ((i / stages) & 1) ^ 1, status)) { failed = 1; break; }
@@ -270,7 +278,7 @@ flash_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __
         tc_commit(&o_full[buffer]);
         return true;
       };
-      ok = ok && scores(0);
+      ok = ok && (key_tiles == 0 || scores(0));
       for (int i = 0; i < key_tiles && ok && !failed; ++i) {
         if (i + 1 < key_tiles) ok = scores(i + 1);
         ok = ok && outputs(i);
@@ -362,7 +370,7 @@ flash_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __
       if (i > 0 && !accumulate(i - 1, alpha_pending)) { ok = false; break; }
       alpha_pending = alpha;
     }
-    if (ok && !failed) ok = accumulate(key_tiles - 1, alpha_pending);
+    if (ok && !failed && key_tiles > 0) ok = accumulate(key_tiles - 1, alpha_pending);
     if (!ok) failed = 1;
     // The row's sum: this thread's keys plus its partners' (all scaled to the
     // same final maximum). The buffer of this parity was last read two
@@ -373,7 +381,15 @@ flash_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __
     l = (row_max[key_tiles & 1][0][row] + row_max[key_tiles & 1][1][row]) +
         (row_max[key_tiles & 1][2][row] + row_max[key_tiles & 1][3][row]);
     if (!ok) failed = 1;
-    if (ok && valid) {
+    if (ok && valid && partial != nullptr) {
+      // [token][head][share][HD values, maximum (in units of log 2), sum]
+      float* dst = partial + ((static_cast<size_t>(t0 + row) * heads + head) * shares + share) * (HD + 2);
+#pragma unroll
+      for (int c = 0; c < PART_HD; c += 4)
+        *reinterpret_cast<float2*>(dst + part * PART_HD + c) = make_float2(acc[c], acc[c + 1]),
+        *reinterpret_cast<float2*>(dst + part * PART_HD + c + 2) = make_float2(acc[c + 2], acc[c + 3]);
+      if (part == 0) { dst[HD] = m; dst[HD + 1] = l; }
+    } else if (ok && valid) {
       const float inv = 1.0f / l;
       __nv_bfloat16* dst = out + (static_cast<size_t>(t0 + row) * heads + head) * HD + part * PART_HD;
 #pragma unroll
@@ -398,11 +414,50 @@ flash_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __
   }
 }
 
+// out[token, head, :] from the shares' unnormalised outputs, maxima and sums:
+// a block per (head, query tile, group of rows), one thread per value of the
+// head; a block takes every kMergeGroups-th row of the tile, so that the
+// trips to memory of many rows are under way at once.
+constexpr int kMergeGroups = 32;
+constexpr int kMergeShares = 8;   // at most
+
+template <int HD>
+__global__ void __launch_bounds__(HD)
+flash_prefill_merge_kernel(const float* __restrict__ partial, __nv_bfloat16* __restrict__ out,
+                           const int* __restrict__ tile_start, const int* __restrict__ tile_length, int heads,
+                           int shares) {
+  const int head = blockIdx.x, tile = blockIdx.y, d = threadIdx.x;
+  const int t0 = tile_start[tile], n = tile_length[tile];
+  for (int row = blockIdx.z; row < n; row += kMergeGroups) {
+    const float* base = partial + (static_cast<size_t>(t0 + row) * heads + head) * shares * (HD + 2);
+    float maxima[kMergeShares], sums[kMergeShares], values[kMergeShares];
+#pragma unroll
+    for (int s = 0; s < kMergeShares; ++s) {   // every load first, then the arithmetic
+      const bool live = s < shares;
+      maxima[s] = live ? base[s * (HD + 2) + HD] : -INFINITY;
+      sums[s] = live ? base[s * (HD + 2) + HD + 1] : 0.0f;
+      values[s] = live ? base[s * (HD + 2) + d] : 0.0f;
+    }
+    float highest = -INFINITY;
+#pragma unroll
+    for (int s = 0; s < kMergeShares; ++s) highest = fmaxf(highest, maxima[s]);
+    float value = 0.0f, sum = 0.0f;
+#pragma unroll
+    for (int s = 0; s < kMergeShares; ++s) {   // a share without keys of this row has maximum -inf and weight 0
+      const float weight = fa_exp2(maxima[s] - highest);
+      value = fmaf(weight, values[s], value);
+      sum = fmaf(weight, sums[s], sum);
+    }
+    out[(static_cast<size_t>(t0 + row) * heads + head) * HD + d] = __float2bfloat16_rn(value / sum);
+  }
+}
+
 template <int HD>
 static int launch_flash_tc(const void* q, const void* cache, void* out, const int* block_tables, int max_pages,
                            const int* tile_request, const int* tile_start, const int* tile_length,
                            const int* positions, int tokens, int tiles, int heads, int kv_heads, int page_tokens,
-                           int num_pages, int window, float scale, int* status, cudaStream_t stream) {
+                           int num_pages, int window, float scale, int key_shares, float* partial, int* status,
+                           cudaStream_t stream) {
   using Config = FaConfig<HD>;
   CUtensorMap map_q, map_cache;
   // q as [tokens, heads * HD]; the cache as [pages * 2 * kv_heads * page_tokens, HD].
@@ -421,10 +476,16 @@ static int launch_flash_tc(const void* q, const void* cache, void* out, const in
   const int shared_bytes = Config::kSharedBytes < shared_limit ? Config::kSharedBytes : shared_limit;
   cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, shared_bytes);
   if (e != cudaSuccess) return static_cast<int>(e);
-  dim3 grid(heads, tiles);
+  const bool shared_out = key_shares > 1;
+  dim3 grid(heads, tiles, shared_out ? key_shares : 1);
   kernel<<<grid, kFaThreads, shared_bytes, stream>>>(
       map_q, map_cache, static_cast<__nv_bfloat16*>(out), block_tables, max_pages, tile_request, tile_start,
-      tile_length, positions, heads, kv_heads, page_tokens, num_pages, window, scale, shared_bytes, status);
+      tile_length, positions, heads, kv_heads, page_tokens, num_pages, window, scale, shared_bytes,
+      shared_out ? partial : nullptr, status);
+  e = cudaGetLastError();
+  if (e != cudaSuccess || !shared_out) return static_cast<int>(e);
+  flash_prefill_merge_kernel<HD><<<dim3(heads, tiles, kMergeGroups), HD, 0, stream>>>(
+      partial, static_cast<__nv_bfloat16*>(out), tile_start, tile_length, heads, key_shares);
   return static_cast<int>(cudaGetLastError());
 }
 
@@ -444,12 +505,17 @@ MXB_API int mxb_flash_prefill_tcgen05_supported(int head_dim, int heads, int kv_
 MXB_API int mxb_flash_prefill_tcgen05_tile() { return kFaRows; }
 
 // Query tiles of up to 128 tokens each; q and out are [tokens, heads, head_dim].
+// key_shares > 1: that many blocks share a query tile's keys; partial is
+// float32 scratch of tokens * heads * key_shares * (head_dim + 2) values.
 MXB_API int mxb_flash_prefill_tcgen05(const void* q, const void* cache, void* out, const int* block_tables,
                                       int max_pages, const int* tile_request, const int* tile_start,
                                       const int* tile_length, const int* positions, int tokens, int tiles,
                                       int heads, int kv_heads, int head_dim, int page_tokens, int num_pages,
-                                      int window, float scale, int dtype, int* status, cudaStream_t stream) {
+                                      int window, float scale, int dtype, int key_shares, float* partial,
+                                      int* status, cudaStream_t stream) {
   if (tiles <= 0) return 0;
+  if (key_shares < 1 || key_shares > kMergeShares || (key_shares > 1 && partial == nullptr))
+    return static_cast<int>(cudaErrorInvalidValue);
   if (!mxb_flash_prefill_tcgen05_supported(head_dim, heads, kv_heads, page_tokens, dtype))
     return static_cast<int>(cudaErrorInvalidValue);
   if ((reinterpret_cast<uintptr_t>(q) & 15) || (reinterpret_cast<uintptr_t>(cache) & 15) ||
@@ -458,8 +524,8 @@ MXB_API int mxb_flash_prefill_tcgen05(const void* q, const void* cache, void* ou
   if (head_dim == 64)
     return launch_flash_tc<64>(q, cache, out, block_tables, max_pages, tile_request, tile_start, tile_length,
                                positions, tokens, tiles, heads, kv_heads, page_tokens, num_pages, window, scale,
-                               status, stream);
+                               key_shares, partial, status, stream);
   return launch_flash_tc<128>(q, cache, out, block_tables, max_pages, tile_request, tile_start, tile_length,
                               positions, tokens, tiles, heads, kv_heads, page_tokens, num_pages, window, scale,
-                              status, stream);
+                              key_shares, partial, status, stream);
 }

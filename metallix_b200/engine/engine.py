@@ -33,6 +33,7 @@ _DTYPES = {"bfloat16": torch.bfloat16, "bf16": torch.bfloat16, "float32": torch.
 ATTENTION_TILE = 16  # query tokens per tile of the general kernel (csrc/kernels/attention_tile.cu)
 STEP_GRAPHS = 8       # how many shapes of general steps keep a captured graph
 STEP_GRAPH_TOKENS = 8192   # ... of steps up to this many tokens (a graph keeps its activations)
+LONG_CONTEXT = 2048   # a portion of a prompt that sees this many keys or more counts as behind a long context
 WIDE_TILE = 128      # and of the tensor-core prompt kernels (csrc/kernels/attention_prefill*.cu)
 
 
@@ -329,6 +330,7 @@ class Engine:
         starts, wanted = [], []
         tile_request, tile_start, tile_length = [], [], []
         single_tiles, decode_token, decode_request, longest = [], [], [], 0
+        longest_keys = 0   # the most keys a portion of a prompt sees
         wide = []   # (keys to walk, row, first token, count) of wide tiles
         group_tables = [[] for _ in cache.groups]
         for row, entry in enumerate(entries):
@@ -351,6 +353,7 @@ class Engine:
                     tile_request.append(row)
                     tile_start.append(begin + first)
                     tile_length.append(min(ATTENTION_TILE, count - first))
+                longest_keys = max(longest_keys, start + count)
                 for first in range(0, count, WIDE_TILE):
                     size = min(WIDE_TILE, count - first)
                     wide.append((start + first + size, row, begin + first, size))
@@ -365,7 +368,10 @@ class Engine:
             tile_length.append(count)
         # A step that may be replayed as a graph has block tables of the full
         # width, so that its buffer has one layout whatever the contexts are.
-        shape_key = (tuple(counts), len(wanted))
+        # Portions behind a long context run other attention launches (a tile's
+        # keys shared out among blocks) than the same portions at a prompt's start.
+        many_keys = longest_keys >= LONG_CONTEXT
+        shape_key = (tuple(counts), len(wanted), many_keys)
         graphed = self._step_graphs is not None and total <= STEP_GRAPH_TOKENS and (
             shape_key in self._step_graphs or self._shapes_seen.get(shape_key, 0) >= 1)
         full_width = -(-self.max_context // page_tokens)
@@ -399,7 +405,7 @@ class Engine:
             cursor += size
         self._keep = packed  # the pinned buffer must outlive the asynchronous copy
 
-        def forward(on_device: torch.Tensor, longest_context: int) -> Optional[torch.Tensor]:
+        def forward(on_device: torch.Tensor, longest_context: int, keys: int) -> Optional[torch.Tensor]:
             views, cursor = [], 0
             for size, shape in zip(sizes, shapes):
                 view = on_device[cursor:cursor + size]
@@ -417,7 +423,7 @@ class Engine:
                 tile_request=d_tile_request, tile_start=d_tile_start, tile_length=d_tile_length,
                 multi_tiles=multi_tiles, decode_token=d_decode_token if decode_token else None,
                 decode_request=d_decode_request if decode_token else None, longest_context=longest_context,
-                wide_tile_request=d_wide_request, wide_tile_start=d_wide_start,
+                longest_keys=keys, wide_tile_request=d_wide_request, wide_tile_start=d_wide_start,
                 wide_tile_length=d_wide_length)
             return self.model.forward(
                 d_ids, ctx, lambda entry, write: cache.view(entry, write, tables, slots),
@@ -428,8 +434,10 @@ class Engine:
                 self._shapes_seen[shape_key] = self._shapes_seen.get(shape_key, 0) + 1
                 if len(self._shapes_seen) > 4096:
                     self._shapes_seen.clear()
-            return forward(packed.to(self.device, non_blocking=True), longest)
-        return self._replay_step(shape_key, packed, forward)
+            return forward(packed.to(self.device, non_blocking=True), longest, longest_keys)
+        # a graph serves every context of its kind: the bound is the engine's
+        bound = self.max_context if many_keys else LONG_CONTEXT - 1
+        return self._replay_step(shape_key, packed, lambda on_device, longest_context: forward(on_device, longest_context, bound))
 
     def _replay_step(self, shape_key, packed: torch.Tensor, forward) -> Optional[torch.Tensor]:
         """Replays (after capturing it, the first time) the graph of a general

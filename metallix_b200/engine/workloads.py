@@ -92,7 +92,7 @@ def main(argv=None) -> int:
         flops = 4.0 * head_dim * heads * sum(args.context + t + 1 for t in range(tokens))
         for kernel in (("tcgen05", "mma") if args.kernel == "both" else (args.kernel,)):
             run = lambda: ops.flash_prefill(q, cache, out, table, tile_request, tile_start, tile_length, positions,
-                                            head_dim ** -0.5, kernel=kernel)
+                                            head_dim ** -0.5, kernel=kernel, longest_context=total)
             for _ in range(3):
                 run()
             start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)

@@ -42,7 +42,8 @@ _SIGNATURES = {
     "mxb_flash_prefill": [_P, _P, _P, _P, _I, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _F, _I, _P, _P],
     "mxb_flash_prefill_supported": [_I, _I, _I, _I],
     "mxb_flash_prefill_tile": [],
-    "mxb_flash_prefill_tcgen05": [_P, _P, _P, _P, _I, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _F, _I, _P, _P],
+    "mxb_flash_prefill_tcgen05": [_P, _P, _P, _P, _I, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _F, _I, _I, _P,
+                                  _P, _P],
     "mxb_flash_prefill_tcgen05_supported": [_I, _I, _I, _I, _I],
     "mxb_flash_prefill_tcgen05_tile": [],
     "mxb_gemm_simple": [_P, _I, _P, _P, _I, _I, _I, _I, _L, _L, _L, _P],
@@ -409,13 +410,33 @@ def flash_prefill_tcgen05_supported(head_dim: int, heads: int, kv_heads: int, pa
     return bool(_fn("mxb_flash_prefill_tcgen05_supported")(head_dim, heads, kv_heads, page_tokens, _CODES[dtype]))
 
 
+KEY_SHARES = None   # an int forces the number of blocks that share a query tile's keys (tests, comparisons)
+
+
+def flash_key_shares(blocks: int, longest_context: int, window: int = 0) -> int:
+    """How many blocks share the keys of a query tile of the tcgen05 prompt
+    kernel: one, unless the step has so few (tile, head) blocks and so many
+    keys that most SMs would stand idle (a portion of a prompt behind a long
+    context). Each share keeps at least 1,024 keys."""
+    if KEY_SHARES is not None:
+        return max(1, int(KEY_SHARES))
+    keys = min(longest_context, window) if window else longest_context
+    if blocks >= 100 or keys < 2048:
+        return 1
+    return max(1, min(8, 148 // blocks, keys // 1024))
+
+
 def flash_prefill(q: torch.Tensor, cache: torch.Tensor, out: torch.Tensor, block_tables: torch.Tensor,
                   tile_request: torch.Tensor, tile_start: torch.Tensor, tile_length: torch.Tensor,
-                  positions: torch.Tensor, scale: float, window: int = 0, kernel: str = "auto") -> torch.Tensor:
+                  positions: torch.Tensor, scale: float, window: int = 0, kernel: str = "auto",
+                  longest_context: int = 0) -> torch.Tensor:
     """Causal attention of prompt portions on the tensor cores (bfloat16,
     float32 softmax and accumulation); tiles hold up to 128 consecutive tokens
     of one request. ``kernel``: "tcgen05" (TMA, tensor memory), "mma" (the
-    warp-level kernel) or "auto" (tcgen05 where it takes the page size)."""
+    warp-level kernel) or "auto" (tcgen05 where it takes the page size).
+    ``longest_context`` (the most keys any of the tiles sees, 0: unknown)
+    lets the tcgen05 kernel share a tile's keys out among several blocks when
+    the tiles alone would leave most of the GPU idle."""
     _check(q, "q", (torch.bfloat16,), 3)
     _check(out, "out", (torch.bfloat16,), 3)
     _check(cache, "cache", (torch.bfloat16,), 5)
@@ -440,11 +461,18 @@ def flash_prefill(q: torch.Tensor, cache: torch.Tensor, out: torch.Tensor, block
           f"the tcgen05 prompt kernel does not take head_dim {head_dim} with pages of {page_tokens} tokens")
     if tcgen05 and kernel != "mma":
         _need(q.is_contiguous() and cache.is_contiguous(), "q and cache must be contiguous")
+        shares = flash_key_shares(tiles * heads, int(longest_context), int(window or 0))
+        partial = None
+        if shares > 1:
+            partial = torch.empty(tokens * heads * shares * (head_dim + 2), dtype=torch.float32, device=q.device)
         _call("mxb_flash_prefill_tcgen05", q.data_ptr(), cache.data_ptr(), out.data_ptr(),
               block_tables.data_ptr(), block_tables.shape[1], tile_request.data_ptr(), tile_start.data_ptr(),
               tile_length.data_ptr(), positions.data_ptr(), tokens, tiles, heads, kv_heads, head_dim,
-              page_tokens, num_pages, int(window or 0), float(scale), _CODES[q.dtype],
+              page_tokens, num_pages, int(window or 0), float(scale), _CODES[q.dtype], shares, _ptr(partial),
               status_word(q.device).data_ptr(), _stream())
+        if shares > 1:
+            global _launches
+            _launches += 1   # the kernel that puts the shares together
         return out
     _call("mxb_flash_prefill", q.data_ptr(), cache.data_ptr(), out.data_ptr(), block_tables.data_ptr(),
           block_tables.shape[1], tile_request.data_ptr(), tile_start.data_ptr(), tile_length.data_ptr(),

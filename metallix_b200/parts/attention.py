@@ -112,7 +112,7 @@ class GQAttention:
             if ctx.wide_tile_request.numel():
                 ops.flash_prefill(q_heads, cache.pool, out, cache.block_tables, ctx.wide_tile_request,
                                   ctx.wide_tile_start, ctx.wide_tile_length, ctx.positions, self.scale,
-                                  self.window)
+                                  self.window, longest_context=ctx.longest_keys)
             rest = None if split else slice(ctx.multi_tiles, None)   # single tokens not yet served
         else:
             rest = slice(0, ctx.multi_tiles) if split else slice(0, None)

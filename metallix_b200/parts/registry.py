@@ -119,6 +119,7 @@ class StepContext:
     decode_token: Optional[torch.Tensor] = None    # int32 [decode rows]
     decode_request: Optional[torch.Tensor] = None  # int32 [decode rows]
     longest_context: int = 0           # upper bound of position + 1 over the decode rows
+    longest_keys: int = 0              # upper bound of the keys a wide tile sees (0: no bound known, taken as few)
     # Tiles of up to 64 tokens over the multi-token requests, for the
     # tensor-core prompt kernel; longest keys first.
     wide_tile_request: Optional[torch.Tensor] = None

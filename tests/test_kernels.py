@@ -369,6 +369,38 @@ def test_flash_prefill_one_far_key_and_cuts(ops, kernel):
     assert np.array_equal(part[77:], whole[245:250])
 
 
+@pytest.mark.parametrize("shares", [2, 3, 5])
+def test_flash_prefill_with_a_tile_s_keys_shared_out(ops, shares):
+    """Several blocks take a query tile's key tiles between them and a second
+    kernel puts their results together; a tile with fewer key tiles than
+    blocks leaves some of them empty-handed."""
+    heads, kv_heads, head_dim, page_tokens = 4, 2, 128, 16
+    dtype = torch.bfloat16
+    rng = np.random.default_rng(shares)
+    lengths = [(1500, 200), (130, 130), (700, 3), (40, 40), (1000, 260)]
+    q = [rounded(rng.normal(size=(n, heads, head_dim)), dtype) for n, _ in lengths]
+    k = [rounded(rng.normal(size=(n, kv_heads, head_dim)), dtype) for n, _ in lengths]
+    v = [rounded(rng.normal(size=(n, kv_heads, head_dim)), dtype) for n, _ in lengths]
+    scale = head_dim ** -0.5
+    assert ops.flash_key_shares(64, 4096) == 2 and ops.flash_key_shares(64, 1000) == 1
+    assert ops.flash_key_shares(16, 8192) == 8 and ops.flash_key_shares(256, 8192) == 1
+    assert ops.flash_key_shares(16, 8192, window=1024) == 1
+    try:
+        for window in (0, 300):
+            ops.KEY_SHARES = None
+            alone = run_flash(ops, q, k, v, lengths, page_tokens, scale, window=window, kernel="tcgen05")
+            ops.KEY_SHARES = shares
+            shared = run_flash(ops, q, k, v, lengths, page_tokens, scale, window=window, kernel="tcgen05")
+            cursor = 0
+            for r, (total, queries) in enumerate(lengths):
+                ref = plain.causal_gqa_attention(q[r], k[r], v[r], scale, window=window or None)[total - queries:]
+                assert np.abs(shared[cursor:cursor + queries] - ref).max() < 2e-2, (window, r)
+                cursor += queries
+            assert np.abs(shared - alone).max() < 1e-2
+    finally:
+        ops.KEY_SHARES = None
+
+
 def run_decode_attention(ops, dtype, q, k, v, totals, page_tokens, scale, window=0, pad_rows=0, seed=0):
     """One query (the last position) per request through the split-key kernel."""
     heads, head_dim, kv_heads = q[0].shape[1], q[0].shape[2], k[0].shape[1]

@@ -142,7 +142,7 @@ def test_equal_portions_replay_a_graph(model_folders, name, dtype):
             assert np.abs(seen[-1] - want).max() < limit, (graphs, first)
         engine.check()
         if graphs:
-            assert set(engine._step_graphs) == {((48,), 2), ((50, 30), 3)}
+            assert set(engine._step_graphs) == {((48,), 2, False), ((50, 30), 3, False)}   # (tokens per request, wanted, behind a long context)
         outputs[graphs] = seen
         engine.release_all()
         engine.manager.check_invariants()
@@ -218,3 +218,34 @@ def test_trace_run_program(model_folders, references, tmp_path, dtype):
             assert np.abs(got - want).max() < limit, step["step"]
         for e in step["entries"]:
             offsets[e["id"]] += len(e["tokens"])
+
+
+def test_portions_behind_a_long_context_share_their_keys(tmp_path):
+    """A portion of a prompt with 2,048 or more keys in front of it is few
+    query tiles with many key tiles each: the prompt kernel then shares a
+    tile's keys out among blocks, eagerly and in a captured graph."""
+    from metallix_b200 import Qwen3Config, ops, write_model_folder
+    from metallix_b200.engine import Engine, StepEntry
+    raw = dict(architectures=["Qwen3ForCausalLM"], model_type="qwen3", hidden_act="silu",
+               num_hidden_layers=2, hidden_size=128, num_attention_heads=6, num_key_value_heads=2,
+               head_dim=64, intermediate_size=192, vocab_size=500, rope_theta=100000.0,
+               rms_norm_eps=1e-6, tie_word_embeddings=True, max_position_embeddings=2560)
+    folder = str(tmp_path / "long")
+    write_model_folder(folder, Qwen3Config.from_dict(raw), 5, dtype="bfloat16", norm_dtype="float32")
+    config, tensors = plain.read_model(folder)
+    ids = random_ids(12, 2300, config["vocab_size"])
+    wanted = [2099, 2163, 2227, 2299]
+    reference = plain.forward_logits(config, tensors, ids)[wanted]
+    assert ops.flash_key_shares(6, 2164) == 2
+    for graphs in (False, True):
+        engine = Engine.from_folder(folder, dtype="bfloat16", page_tokens=16, num_pages=160, max_requests=2,
+                                    cuda_graphs=graphs)
+        seen = [engine.step([StepEntry("r", ids[:2100], [2099])])]
+        for start in (2100, 2164):               # the same shape twice: the second one replays a graph
+            seen.append(engine.step([StepEntry("r", ids[start:start + 64], [63])]))
+        seen.append(engine.step([StepEntry("r", ids[2228:2300], [71])]))
+        engine.check()
+        logits = np.concatenate([x.cpu().double().numpy() for x in seen])
+        assert np.abs(logits - reference).max() < TOL_BF16_VS_EXACT, graphs
+        if graphs:
+            assert ((64,), 1, True) in engine._step_graphs
