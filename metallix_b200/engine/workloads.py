@@ -4,6 +4,7 @@
     python -m metallix_b200.engine.workloads prefill --layers 4
     python -m metallix_b200.engine.workloads gemm --m 2048 --n 4096 --k 1024
     python -m metallix_b200.engine.workloads attention --prompt-len 2048
+    python -m metallix_b200.engine.workloads pick --batch 8
 
 ``decode``: ``--batch`` requests with ``--prompt-len`` tokens each, then a few
 decode steps (eagerly, so that a profiler sees every kernel; ``--graphs``
@@ -13,7 +14,8 @@ of a layer holds the chain of one replayed step). ``prefill``:
 one prompt of ``--prompt-len`` tokens, three times. ``gemm``: the tcgen05
 product against the library's on one shape. ``attention``: the two prompt
 attention kernels alone on one prompt of ``--prompt-len`` tokens over
-``--context`` cached ones. Random weights, random token ids;
+``--context`` cached ones. ``pick``: the samplers alone on ``--batch`` rows of
+logits over the model's vocabulary. Random weights, random token ids;
 ``--layers`` keeps captures small (a profiler replays every kernel many times).
 """
 from __future__ import annotations
@@ -30,7 +32,7 @@ QWEN3_0_6B = dict(architectures=["Qwen3ForCausalLM"], model_type="qwen3", hidden
 
 def main(argv=None) -> int:
     parser = argparse.ArgumentParser(description=__doc__.split("\n\n")[0])
-    parser.add_argument("mode", choices=("decode", "prefill", "gemm", "attention"))
+    parser.add_argument("mode", choices=("decode", "prefill", "gemm", "attention", "pick"))
     parser.add_argument("--batch", type=int, default=8)
     parser.add_argument("--layers", type=int, default=4)
     parser.add_argument("--prompt-len", type=int, default=2048)
@@ -69,6 +71,40 @@ def main(argv=None) -> int:
             microseconds = start.elapsed_time(end) * 100
             print(f"{name}: {microseconds:.1f} us, {2 * args.m * args.n * args.k / microseconds / 1e6:.0f} TFLOP/s"
                   " (launch overhead included)")
+        ops.check_status("cuda")
+        return 0
+
+    if args.mode == "pick":
+        ops.require_cuda()
+        rows, vocab = args.batch, QWEN3_0_6B["vocab_size"]
+        generator = torch.Generator(device="cuda").manual_seed(0)
+        logits = torch.randn((rows, vocab), device="cuda", generator=generator) * 3.0
+        temperature = torch.full((rows,), 0.8, dtype=torch.float64, device="cuda")
+        seed = torch.arange(rows, dtype=torch.int64, device="cuda")
+        position = torch.arange(rows, dtype=torch.int32, device="cuda")
+        top_p = torch.full((rows,), 0.9, dtype=torch.float64, device="cuda")
+        top_k = torch.full((rows,), 50, dtype=torch.int32, device="cuda")
+        no_k = torch.zeros(rows, dtype=torch.int32, device="cuda")
+        picks = (("greedy", lambda: ops.argmax(logits)),
+                 ("inverse CDF", lambda: ops.sample_icdf(logits, temperature, seed, seed, position)),
+                 ("race", lambda: ops.sample_race(logits, temperature, seed, position)),
+                 ("top-k 50 and top-p 0.9 mask", lambda: ops.nucleus_mask(logits, temperature, top_p, top_k)),
+                 ("top-p 0.9 mask", lambda: ops.nucleus_mask(logits, temperature, top_p, no_k)))
+        for name, function in picks:
+            for _ in range(3):
+                function()
+            torch.cuda.synchronize()
+            graph = torch.cuda.CUDAGraph()   # replayed, so that the launches from Python do not count
+            with torch.cuda.graph(graph):
+                for _ in range(10):
+                    function()
+            graph.replay()
+            start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            start.record()
+            graph.replay()
+            end.record()
+            torch.cuda.synchronize()
+            print(f"{name}: {start.elapsed_time(end) * 100:.1f} us for {rows} rows of {vocab} logits")
         ops.check_status("cuda")
         return 0
 
