@@ -283,25 +283,32 @@ icdf_pick_kernel(const float* __restrict__ logits, long long row_stride, int voc
   }
   const double* row_sums = behind_wait(sums) + r * pieces;
   const int* row_lasts = behind_wait(lasts) + r * pieces;
+  // The pieces' sums into shared memory, all threads at once: the one thread
+  // that walks them would otherwise wait for memory at every step it takes.
+  extern __shared__ double s_piece_sums[];   // [pieces]
+  int last_here = -1;
+  for (int p = tid; p < pieces; p += kIcdfThreads) {
+    s_piece_sums[p] = row_sums[p];
+    last_here = max(last_here, row_lasts[p]);
+  }
+  if (tid == 0) s_last = -1;
+  __syncthreads();
+  if (last_here >= 0) atomicMax(&s_last, last_here);
+  __syncthreads();
   if (tid == 0) {
     double total = 0.0;
-    int last = -1;
-    for (int p = 0; p < pieces; ++p) {
-      total += row_sums[p];
-      last = max(last, row_lasts[p]);
-    }
+    for (int p = 0; p < pieces; ++p) total += s_piece_sums[p];   // piece order: one order of additions
     const double target = request_uniform(seed[r], stream[r], static_cast<uint32_t>(position[r])) * total;
     double before = 0.0;
     int piece = -1;
     for (int p = 0; p < pieces; ++p) {
-      const double sum = row_sums[p];
+      const double sum = s_piece_sums[p];
       if (sum > 0.0 && target < before + sum) { piece = p; break; }
       before += sum;
     }
     s_target = target;
     s_before = before;
     s_piece = piece;
-    s_last = last;
     s_owner = 0x7fffffff;
   }
   __syncthreads();
@@ -498,7 +505,12 @@ MXB_API int mxb_sample_icdf(const float* logits, long long row_stride, int rows,
   e = launch_chained(icdf_sum_kernel, dim3(pieces, rows), dim3(kIcdfThreads), 0, stream, logits, row_stride, vocab,
                      temperature, legal, static_cast<const Best*>(maxima), sums, lasts);
   if (e != cudaSuccess) return static_cast<int>(e);
-  return static_cast<int>(launch_chained(icdf_pick_kernel, dim3(rows), dim3(kIcdfThreads), 0, stream, logits,
+  const size_t pick_shared = static_cast<size_t>(pieces) * sizeof(double);
+  if (pick_shared > 48 * 1024) {
+    e = cudaFuncSetAttribute(icdf_pick_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(pick_shared));
+    if (e != cudaSuccess) return static_cast<int>(e);
+  }
+  return static_cast<int>(launch_chained(icdf_pick_kernel, dim3(rows), dim3(kIcdfThreads), pick_shared, stream, logits,
                                          row_stride, vocab, pieces, temperature, seed, stream_id, position, legal,
                                          static_cast<const Best*>(maxima), static_cast<const double*>(sums),
                                          static_cast<const int*>(lasts), ids, status));
