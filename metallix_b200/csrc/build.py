@@ -139,7 +139,7 @@ def _build_kernels(out_dir: str) -> str:
         if os.path.exists(library) and os.path.exists(stamp) and open(stamp).read() == tag:
             return library
         nvcc = _nvcc()
-        object_dir = os.path.join(out_dir, "obj")
+        object_dir = os.path.join(out_dir, "obj_timeline" if timeline else "obj")
         os.makedirs(object_dir, exist_ok=True)
         with _Heartbeat(f"{len(sources)} CUDA kernel files"):
             def compile_one(source: str) -> str:
@@ -162,6 +162,14 @@ def _build_kernels(out_dir: str) -> str:
             os.replace(partial, library)
             with open(stamp, "w") as handle:
                 handle.write(tag)
+            # Objects of earlier versions of the sources are of no use any more.
+            kept = {os.path.basename(path) for path in objects}
+            for name in os.listdir(object_dir):
+                if name.endswith(".o") and name not in kept:
+                    try:
+                        os.remove(os.path.join(object_dir, name))
+                    except OSError:
+                        pass
         return library
     finally:
         lock.close()
