@@ -193,7 +193,7 @@ def decoder_layer(x, positions, w, layer, config, rounding=None, shared_kv=None,
 
 
 def forward_logits(config, tensors, ids, dtype=np.float64, bf16_activations=False,
-                   order=None, reads=None):
+                   order=None, reads=None, rows=None):
     """Logits [T, V] at every position of one whole sequence (forward.rs:741-773,
     :995-1020): embedding, the layers in order, final norm, output head through
     the embedding when tied, else lm_head (forward.rs:574-580; an absent
@@ -201,8 +201,10 @@ def forward_logits(config, tensors, ids, dtype=np.float64, bf16_activations=Fals
     activations to bfloat16 where a bfloat16 engine stores them, keeping the
     residual sum unrounded. ``order`` runs the layers in another order;
     ``reads[i] = j`` lets the i-th run use the keys and values the j-th run
-    produced."""
-    w = {name: value.astype(dtype) for name, value in tensors.items()}
+    produced. ``rows``: only these positions go through the final norm and the
+    head (forward.rs:1585-1597 norms the requested rows only); the result is
+    then [len(rows), V]."""
+    w = {name: value.astype(dtype, copy=False) for name, value in tensors.items()}
     rounding = bf16_round if bf16_activations else None
     r = rounding or (lambda a: a)
     positions = np.arange(len(ids))
@@ -215,6 +217,8 @@ def forward_logits(config, tensors, ids, dtype=np.float64, bf16_activations=Fals
         x = decoder_layer(x, positions, w, layer, config, rounding, shared_kv=shared, keep=keep)
         produced.append(keep[0])
     eps = f32(config.get("rms_norm_eps", 1e-6))
+    if rows is not None:
+        x = x[np.asarray(rows, dtype=np.int64)]
     normed = r(rms_norm(x, w["model.norm.weight"], eps))
     head = (w["model.embed_tokens.weight"] if config.get("tie_word_embeddings", False)
             else w["lm_head.weight"])

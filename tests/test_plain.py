@@ -124,3 +124,28 @@ def test_bf16_rounding():
     rounded = plain.bf16_round(values)
     assert rounded[0] == 1.0 and rounded[1] == 1.0 and rounded[4] == -2.5   # 1 + 2^-8 ties to even
     assert rounded[2] == 1.0 and rounded[3] == 1.0078125 and rounded[5] == 3.140625
+
+
+def test_two_plain_implementations_agree(model_folders):
+    """The numpy implementation (whole sequences under a mask) and the torch
+    one (one position at a time over growing keys and values, the rotation as
+    a complex product, repeated key/value heads, its own file reader) were
+    written apart from the same lines of the reference; they must give the
+    same logits, also when layers run in another order or share a cache."""
+    import plain_qwen3_torch as second
+    worst = 0.0
+    for name in ("A", "B", "C", "D"):
+        folder, config, tensors, _ = model_folders[name]
+        other_config, other_tensors = second.load_folder(folder)
+        assert other_config == config and set(other_tensors) == set(tensors)
+        ids = random_ids(len(name) + 40, 37, config["vocab_size"])
+        layers = config["num_hidden_layers"]
+        variants = [dict(), dict(order=list(range(layers)) + [0]),             # a layer run twice
+                    dict(order=list(range(layers)) + [0], reads={layers: 0})]  # ... reading the first run's cache
+        for variant in variants:
+            first = plain.forward_logits(config, tensors, ids, **variant)
+            again = second.all_logits(other_config, other_tensors, ids, **variant).numpy()
+            scale = np.abs(first).max()
+            worst = max(worst, float(np.abs(first - again).max() / scale))
+            assert np.abs(first - again).max() <= 1e-9 * scale, (name, variant)
+    print(f"largest relative difference between the two plain implementations: {worst:.2e}")

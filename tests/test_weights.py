@@ -97,6 +97,47 @@ def test_random_folder_loads_by_name(tmp_path):
         assert not torch.equal(other["model.embed_tokens.weight"], tensors["model.embed_tokens.weight"])
 
 
+def test_random_values_come_from_a_counter():
+    """Element i of a tensor depends on (seed, name, i) alone: a tensor made
+    alone, as part of a larger one, or in another order has the same values,
+    and the Philox words are those of the plain implementation."""
+    import plain_qwen3 as plain
+    from metallix_b200.weights import random_init
+    key = random_init._tensor_key(4, "model.norm.weight")
+    words = random_init.philox_words(key, (1 << 32) - 2, 4, "cpu")   # across the low word's carry
+    for column in range(4):
+        block = (1 << 32) - 2 + column
+        want = plain.philox4x32_10((block & 0xFFFFFFFF, block >> 32, 0, random_init._DOMAIN), key)
+        assert tuple(int(words[row, column]) for row in range(4)) == want
+    small = random_init.random_tensor(9, "w", (7,), False)
+    large = random_init.random_tensor(9, "w", (5, 1000), False)
+    assert torch.equal(small, large.reshape(-1)[:7])
+    assert not torch.equal(small, random_init.random_tensor(9, "v", (7,), False))
+    # N(0, 0.02): moments of a million values, and tails beyond four sigma exist
+    values = random_init.random_tensor(1, "moments", (1000, 1000), False).double() / 0.02
+    assert abs(float(values.mean())) < 5e-3 and abs(float(values.std()) - 1.0) < 5e-3
+    assert abs(float((values ** 4).mean()) - 3.0) < 0.05 and float(values.abs().max()) > 4.0
+    # the series behind the transform against the library functions
+    u = torch.rand(10000, dtype=torch.float64).clamp_min(2.0 ** -33)
+    assert float((random_init._log_unit(u) - torch.log(u)).abs().max()) < 1e-14
+    word = torch.randint(0, 1 << 32, (10000,), dtype=torch.int64)
+    cos, sin = random_init._unit_circle(word)
+    angle = word.double() * (2.0 * torch.pi / (1 << 32))
+    assert float((cos - torch.cos(angle)).abs().max()) < 1e-14 and float((sin - torch.sin(angle)).abs().max()) < 1e-14
+
+
+@pytest.mark.gpu
+def test_random_values_are_the_same_on_cpu_and_gpu():
+    from metallix_b200.weights import random_init
+    for norm in (False, True):
+        host = random_init.random_tensor(11, "model.layers.0.mlp.up_proj.weight", (257, 1031), norm, "cpu")
+        device = random_init.random_tensor(11, "model.layers.0.mlp.up_proj.weight", (257, 1031), norm, "cuda")
+        assert torch.equal(host, device.cpu())
+    config = Qwen3Config.from_dict(TINY_B)
+    host, device = random_tensors(config, 2), random_tensors(config, 2, device="cuda")
+    assert all(torch.equal(host[name], device[name].cpu()) for name in host)
+
+
 def test_stored_dtype_is_kept(tmp_path):
     config = Qwen3Config.from_dict(TINY_A)
     folder = write_model_folder(str(tmp_path / "mixed"), config, 3, dtype="bfloat16", norm_dtype="float32")
