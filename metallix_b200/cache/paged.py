@@ -45,6 +45,16 @@ class Group:
 class PagedCache:
     """Pools, state slots and the manager for one model."""
 
+    @staticmethod
+    def page_bytes(needs: Sequence[Optional[CacheNeed]], page_tokens: int, dtype: torch.dtype) -> int:
+        """Bytes that one page index takes over all groups and all their
+        entries: what a pool of n pages per group costs is n times this. The
+        reference sizes its pool from a byte budget the same way
+        (crates/core/engine/src/blocks.rs:162-180)."""
+        size = torch.empty((), dtype=dtype).element_size()
+        return sum(2 * need.kv_heads * need.head_dim * page_tokens * size
+                   for need in needs if need is not None and need.kind == "kv_pages")
+
     def __init__(self, needs: Sequence[Optional[CacheNeed]], page_tokens: int, num_pages: int,
                  max_requests: int, dtype: torch.dtype, device, allocate: bool = True):
         if page_tokens <= 0 or page_tokens & (page_tokens - 1):

@@ -674,7 +674,7 @@ template <typename T>
 __global__ void __launch_bounds__(256)
 paged_attention_merge_kernel(const float* __restrict__ partial, T* __restrict__ out,
                              const int* __restrict__ row_token, const int* __restrict__ positions,
-                             int rows, int heads, int head_dim, int max_splits, int window) {
+                             int rows, int heads, int head_dim, int max_splits, int window, int* status) {
   chain_release();
   const int row = blockIdx.x, head = blockIdx.y, d = threadIdx.x;
   const int token = row_token[row];  // the step's integers are not written by any kernel of the step
@@ -682,6 +682,12 @@ paged_attention_merge_kernel(const float* __restrict__ partial, T* __restrict__ 
   const int pos = positions[token];
   const int first_key = window > 0 ? max(0, pos - window + 1) : 0;
   const int first_split = first_key / kSplitKeys, last_split = pos / kSplitKeys;
+  if (last_split >= max_splits) {
+    // The caller's bound on the contexts does not cover this row: its partial
+    // results lie outside what the scratch was sized for. The row is left as it is.
+    if (d == 0) atomicOr(status, kStatusBadSlot);
+    return;
+  }
   const int splits = last_split - first_split + 1;
   const int stride = head_dim + 2;
   const float* base = partial + ((static_cast<size_t>(row) * heads + head) * max_splits + first_split) * stride;
@@ -740,7 +746,7 @@ static int launch_decode(const void* q, const void* cache, void* out, float* par
   if (e != cudaSuccess) return static_cast<int>(e);
   return static_cast<int>(launch_chained(paged_attention_merge_kernel<T>, dim3(rows, heads), dim3(HD <= 64 ? 64 : (HD <= 128 ? 128 : 256)), 0,
                                          stream, static_cast<const float*>(partial), static_cast<T*>(out),
-                                         row_token, positions, rows, heads, HD, max_splits, window));
+                                         row_token, positions, rows, heads, HD, max_splits, window, status));
 }
 
 template <int HD>
@@ -782,7 +788,7 @@ static int launch_decode_mma(const void* q, const void* cache, void* out, float*
   return static_cast<int>(launch_chained(paged_attention_merge_kernel<__nv_bfloat16>, dim3(rows, heads),
                                          dim3(HD <= 64 ? 64 : (HD <= 128 ? 128 : 256)), 0, stream, static_cast<const float*>(partial),
                                          static_cast<__nv_bfloat16*>(out), row_token, positions, rows, heads,
-                                         HD, max_splits, window));
+                                         HD, max_splits, window, status));
 }
 
 }  // namespace mxb

@@ -73,6 +73,8 @@ def build_parser() -> argparse.ArgumentParser:
     gen.add_argument("--verify-cache", action="store_true",
                      help="recompute every generated position from the whole sequence and compare")
     gen.add_argument("--gemm", choices=("auto", "tcgen05", "cublas", "simple"), default="auto")
+    gen.add_argument("--trace-out", metavar="FILE",
+                     help="write a Chrome/Perfetto JSON timeline of the steps (host and device spans)")
     gen.add_argument("-v", "--verbose", "--debug", action="store_true", dest="verbose")
 
     rnd = commands.add_parser("random-weights", help="write a model folder with random weights")
@@ -83,19 +85,41 @@ def build_parser() -> argparse.ArgumentParser:
     return parser
 
 
-def _verify_cache(engine, result, tolerance: float) -> dict:
-    """Runs prompt + generated tokens as one whole step on a fresh request and
-    compares the picked tokens (crates/app/cli/src/qwen_forward.rs:916-939)."""
+VERIFY_BOUNDS = {"float32": (5e-4, 1e-4), "bfloat16": (0.0, 2.5e-2)}   # (absolute, relative to the row's largest |logit|)
+
+
+def _verify_cache(engine, checker, result, dtype: str) -> dict:
+    """Recomputes the logits of every generated position twice over and
+    compares them, as the reference's ``--verify-cache`` compares cached and
+    uncached logits (crates/app/cli/src/qwen_forward.rs:916-939): once with
+    the serving engine from the whole sequence in one step (cache against no
+    cache), and once with ``checker``, a second engine over the same weights
+    that runs other kernels end to end (no captured graphs, no overlapped
+    launches, matrix products on CUDA cores instead of tensor cores or the
+    library), so that an error the serving paths share does not hide."""
     import torch
     from .. import ops
     from .engine import StepEntry
     ids = list(result.input_ids) + list(result.generated_ids[:-1])
     first = len(result.input_ids) - 1
-    logits = engine.step([StepEntry("verify-cache", ids, list(range(first, len(ids))))])
-    picked = ops.argmax(logits).tolist()
+    wanted = list(range(first, len(ids)))
+    whole = engine.step([StepEntry("verify-cache", ids, wanted)]).clone()
+    picked = ops.argmax(whole).tolist()
     engine.check()
     engine.release("verify-cache")
-    return {"positions": len(picked), "greedy_tokens_match": picked == list(result.generated_ids)}
+    other = checker.step([StepEntry("verify-cache", ids, wanted)])
+    checker.check()
+    checker.release("verify-cache")
+    absolute, relative = VERIFY_BOUNDS[dtype]
+    difference = (whole.double() - other.double()).abs()
+    magnitude = other.double().abs().amax(dim=1, keepdim=True)
+    bound = absolute + relative * (other.double().abs() if dtype == "float32" else magnitude)
+    return {"positions": len(picked), "greedy_tokens_match": picked == list(result.generated_ids),
+            "max_abs_logit_difference": float(difference.max()),
+            "max_difference_of_row_magnitude": float((difference / magnitude).max()),
+            "logits_within_bound": bool((difference <= bound).all()),
+            "bound": {"absolute": absolute, "relative": relative},
+            "checked_against": "a second engine: eager launches, CUDA-core matrix products"}
 
 
 def run_gen(args) -> int:
@@ -128,8 +152,10 @@ def run_gen(args) -> int:
         options["num_pages"] = args.num_pages
     elif args.kv_pool_mib:
         # The pool by bytes, as the reference's --kv-pool-mib (cli.rs:219-284): whole pages only.
-        per_page = config.kv_bytes_per_token(2 if args.dtype == "bfloat16" else 4) * args.block_size
-        options["num_pages"] = max(args.kv_pool_mib * 2 ** 20 // per_page, 1)
+        options["pool_bytes"] = args.kv_pool_mib * 2 ** 20
+    # Rotation tables and graphs are laid out for the contexts this call can reach.
+    longest = max(len(prompt) for prompt in prompts) + args.max_tokens
+    options["max_context"] = max(-(-longest // 256) * 256, 256)
     if args.model:
         engine = Engine.from_folder(args.model, **options)
     else:
@@ -141,12 +167,22 @@ def run_gen(args) -> int:
                        seed=args.seed or 0, top_p=args.top_p, top_k=args.top_k,
                        sampler=args.sampler, eos_ids=args.eos_ids, ignore_eos=args.ignore_eos,
                        max_num_seqs=args.max_num_seqs, max_tokens_per_step=args.max_tokens_per_step,
-                       prefill_chunk=args.prefill_chunk_tokens)
+                       prefill_chunk=args.prefill_chunk_tokens, trace_out=args.trace_out)
+    from ..config.registry import resolve
+    family = resolve(config.to_dict()).model_type   # "qwen3": the reference's receipts name the family so
+    checker, verified = None, True
+    if args.verify_cache and not args.sample:
+        checker_options = dict(options, cuda_graphs=False, chained_launches=False, gemm_backend="simple")
+        longest = max(len(r.input_ids) + len(r.generated_ids) for r in results)
+        checker_options["num_pages"] = -(-longest // args.block_size) + 1
+        checker_options.pop("pool_bytes", None)
+        checker = (Engine.from_folder(args.model, **checker_options) if args.model
+                   else Engine.from_random(config, args.random_weights, **checker_options))
     for result in results:
         report = {
             "schema_version": 1,
-            "operation": "qwen3_sampled_cached_generation" if args.sample
-                         else "qwen3_greedy_cached_generation",
+            "operation": f"{family}_sampled_cached_generation" if args.sample
+                         else f"{family}_greedy_cached_generation",
             "backend": f"metallix_b200 sm_100a {args.dtype}",
             "input_ids": result.input_ids,
             "generated_ids": result.generated_ids,
@@ -163,13 +199,16 @@ def run_gen(args) -> int:
                                   "seed": args.seed, "temperature": args.temperature,
                                   "top_p": args.top_p, "top_k": args.top_k}
         if args.verify_cache and not args.sample and not result.failed:
-            report["cache_comparisons"] = _verify_cache(engine, result, 0.0)
+            report["cache_comparisons"] = _verify_cache(engine, checker, result, args.dtype)
+            verified = verified and report["cache_comparisons"]["logits_within_bound"]
         print(json.dumps(report), flush=True)
         if args.verbose:
             print(f"prefill {result.prefill_ms:.2f} ms, {len(result.decode_ms)} decode steps, "
                   f"median {sorted(result.decode_ms)[len(result.decode_ms) // 2] if result.decode_ms else 0:.3f} ms",
                   file=sys.stderr)
-    return 1 if any(r.failed for r in results) else 0
+    if any(r.failed for r in results):
+        return 1
+    return 0 if verified else 3
 
 
 def run_random_weights(args) -> int:
@@ -178,8 +217,8 @@ def run_random_weights(args) -> int:
     with open(args.config) as handle:
         config = parse_config(json.load(handle))
     write_model_folder(args.out, config, args.seed, dtype=args.dtype)
-    print(json.dumps({"model": args.out, "seed": args.seed, "dtype": args.dtype,
-                      "parameters": config.parameter_count()}))
+    parameters = sum(math.prod(shape) for shape in config.tensor_shapes().values())
+    print(json.dumps({"model": args.out, "seed": args.seed, "dtype": args.dtype, "parameters": parameters}))
     return 0
 
 

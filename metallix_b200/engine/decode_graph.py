@@ -2,29 +2,33 @@
 
 A step in which every request brings exactly one token launches the same
 kernels every time; only ids, positions, slots and block tables change. Such a
-step is captured once per batch-size bucket and replayed: one copy of the
-step's integers into the graph's static buffer, one graph launch. The
-reference hides the same launch cost by queueing step t+1 before step t is
+step is captured once per (batch-size bucket, context bucket) and replayed: one
+copy of the step's integers into the graph's static buffer, one graph launch.
+The reference hides the same launch cost by queueing step t+1 before step t is
 read (crates/models/qwen/src/forward/paged.rs:784-858); here the launches
 themselves go away.
 
 Rows beyond the live requests are padding: id 0, position 0, slot -1 (no cache
-write) and a negative decode row (no attention). Block tables are padded to
-the width of the longest context the engine allows.
+write), and whatever the parts' own integers say of a padding row (the
+attention: a tile of no tokens, a negative decode row). Block tables are as
+wide as the context bucket: the longest live context rounded up to 2,048 times
+a power of two, so that table width, split counts and scratch follow the
+contexts that are live, not the longest one the engine allows.
 """
 from __future__ import annotations
 
 import contextlib
 import gc
 import weakref
-from typing import Dict, List, Optional, Sequence
+from typing import Dict, List, Optional, Sequence, Tuple
 
 import numpy as np
 import torch
 
-from ..parts.registry import StepContext
+from ..parts.registry import StepContext, StepPlan, block_parts, graph_safe
 
 BUCKETS = (1, 2, 4, 8, 16, 24, 32, 48, 64, 96, 128, 192, 256)
+_GENERIC = ("ids", "positions", "token_request", "request_slots", "wanted")
 
 
 @contextlib.contextmanager
@@ -43,12 +47,14 @@ def capture_quietly(graph: torch.cuda.CUDAGraph, pool):
 
 
 class _Bucket:
-    def __init__(self, size: int):
-        self.size = size
+    def __init__(self, size: int, bound: int, table_width: int):
+        self.size, self.bound, self.table_width = size, bound, table_width
         self.graph: Optional[torch.cuda.CUDAGraph] = None
         self.static: Optional[torch.Tensor] = None   # int32 metadata on the device
         self.logits: Optional[torch.Tensor] = None
         self.layout: Dict[str, slice] = {}
+        self.facts: Dict[str, dict] = {}              # per preparing part: the host values baked into the graph
+        self.prepared: Dict[int, list] = {}           # live rows -> [(layout name, array)] of the parts' integers
         self.kernels = 0                              # our kernel launches inside the graph
         self.staging: List[dict] = []                 # pinned host buffers for the step's integers
         self.turn = 0
@@ -57,10 +63,9 @@ class _Bucket:
 class DecodeGraphs:
     def __init__(self, engine):
         self._engine = weakref.ref(engine)   # the engine owns this object, not the reverse
-        self.buckets: Dict[int, _Bucket] = {}
+        self.buckets: Dict[Tuple[int, int], _Bucket] = {}
         self.pool = None
         cache = engine.cache
-        self.table_width = -(-engine.max_context // cache.page_tokens)
         self._windowed = any(g.need.window for g in cache.groups)
         self.h2d_bytes = 0
         # Mirrors of the manager's tables: manager id -> (epoch, pages, per-group rows)
@@ -72,9 +77,11 @@ class DecodeGraphs:
 
     @staticmethod
     def usable(model) -> bool:
-        """Every mixer must promise to launch the same kernels whatever the
-        step's integers are (no host reads of device values)."""
-        return all(getattr(block.mixer, "graph_safe", False) for block in model.blocks)
+        """Every part of every block must launch the same work whatever the
+        step's integers and the device's values are (no host reads): a mixer
+        has to promise it (``graph_safe = True``), any other part may deny it
+        (``graph_safe = False``)."""
+        return all(graph_safe(part) for block in model.blocks for part in block_parts(block))
 
     def bucket_for(self, rows: int) -> Optional[int]:
         for size in BUCKETS:
@@ -82,38 +89,63 @@ class DecodeGraphs:
                 return size
         return None
 
+    def sizes_captured(self) -> List[int]:
+        return sorted({size for size, _ in self.buckets})
+
     # ----------------------------------------------------------------- layout
-    def _layout(self, size: int) -> Dict[str, slice]:
-        groups = len(self.engine.cache.groups)
-        names = ["ids", "positions", "token_request", "request_slots", "tile_request", "tile_start",
-                 "tile_length", "wanted", "decode_token", "decode_request"]
-        layout, cursor = {}, 0
-        for name in names:
+    def _plan(self, bucket: _Bucket, live: int) -> StepPlan:
+        # positions are not given: what a part prepares for a replayed decode
+        # step may depend on which rows are live only
+        return StepPlan([1] * bucket.size, None, live, bucket.bound, replayable=True)
+
+    def _prepare(self, bucket: _Bucket, live: int) -> list:
+        """[(layout name, int32 array)] of the parts' own integers for a step
+        with ``live`` requests; kept per ``live``."""
+        held = bucket.prepared.get(live)
+        if held is None:
+            held = []
+            for key, part in self.engine._preparers.items():
+                result = part.prepare_step(self._plan(bucket, live))
+                for name, array in result.arrays.items():
+                    held.append((f"{key}/{name}", np.ascontiguousarray(array, dtype=np.int32).reshape(-1)))
+                bucket.facts.setdefault(key, dict(result.facts))
+            bucket.prepared[live] = held
+        return held
+
+    def _layout(self, bucket: _Bucket) -> None:
+        size, layout, cursor = bucket.size, {}, 0
+        for name in _GENERIC:
             layout[name] = slice(cursor, cursor + size)
             cursor += size
-        for g in range(groups):
+        for name, array in self._prepare(bucket, 0):
+            layout[name] = slice(cursor, cursor + array.size)
+            cursor += array.size
+        for g in range(len(self.engine.cache.groups)):
             layout[f"slots{g}"] = slice(cursor, cursor + size)
             cursor += size
-            layout[f"table{g}"] = slice(cursor, cursor + size * self.table_width)
-            cursor += size * self.table_width
+            layout[f"table{g}"] = slice(cursor, cursor + size * bucket.table_width)
+            cursor += size * bucket.table_width
         layout["end"] = slice(cursor, cursor)
-        return layout
+        bucket.layout = layout
 
     def _context(self, bucket: _Bucket) -> StepContext:
         s, size, engine = bucket.static, bucket.size, self.engine
         cut = lambda name: s[bucket.layout[name]]
+        extras = {}
+        for key in engine._preparers:
+            extras[key] = dict(bucket.facts[key])
+            for name, _ in bucket.prepared[0]:
+                if name.startswith(key + "/"):
+                    extras[key][name[len(key) + 1:]] = cut(name)
         return StepContext(
             device=engine.device, dtype=engine.dtype, num_tokens=size, num_requests=size,
             positions=cut("positions"), token_request=cut("token_request"),
-            request_slots=cut("request_slots"), request_offsets=list(range(size + 1)),
-            request_positions=[0] * size, tile_request=cut("tile_request"),
-            tile_start=cut("tile_start"), tile_length=cut("tile_length"), multi_tiles=0,
-            decode_token=cut("decode_token"), decode_request=cut("decode_request"),
-            longest_context=engine.max_context)
+            request_slots=cut("request_slots"), request_offsets=None, request_positions=None,
+            extras=extras)
 
     def _views(self, bucket: _Bucket):
         s, size, cache = bucket.static, bucket.size, self.engine.cache
-        tables = {g.index: s[bucket.layout[f"table{g.index}"]].view(size, self.table_width)
+        tables = {g.index: s[bucket.layout[f"table{g.index}"]].view(size, bucket.table_width)
                   for g in cache.groups}
         slots = {g.index: s[bucket.layout[f"slots{g.index}"]] for g in cache.groups}
         return lambda entry, write: cache.view(entry, write, tables, slots)
@@ -123,30 +155,30 @@ class DecodeGraphs:
         size, layout, cache = bucket.size, bucket.layout, self.engine.cache
         index = np.arange(size, dtype=np.int32)
         out[:] = 0
-        for name in ("token_request", "tile_request", "tile_start", "wanted", "decode_request"):
+        for name in ("token_request", "wanted"):
             out[layout[name]] = index
-        out[layout["decode_token"]] = -1
+        for name, array in self._prepare(bucket, 0):
+            out[layout[name]] = array
         for g in cache.groups:
             out[layout[f"slots{g.index}"]] = -1
             out[layout[f"table{g.index}"]] = -1
 
-    def _host_fill(self, bucket: _Bucket, rows: Sequence, out: np.ndarray, held_rows: Optional[list] = None,
-                   filled: int = 0) -> None:
+    def _host_fill(self, bucket: _Bucket, rows: Sequence, stage: dict) -> None:
         """rows: (manager id, token id, position, state slot) of the live
-        requests; fills one step's integers into ``out``, which holds the
-        constants and, in its first ``filled`` rows, an earlier step.
-        ``held_rows[row]`` remembers whose block table a row of ``out`` holds,
-        so that a table is copied again only when it has changed."""
-        size, layout, cache = bucket.size, bucket.layout, self.engine.cache
+        requests; fills one step's integers into the staging buffer, which
+        holds the constants and, in its first ``stage["filled"]`` rows, an
+        earlier step. ``stage["held"][row]`` remembers whose block table a row
+        holds, so that a table is copied again only when it has changed."""
+        out, held_rows, filled = stage["array"], stage["held"], stage["filled"]
+        layout, cache = bucket.layout, self.engine.cache
         manager, page_tokens = self.engine.manager, cache.page_tokens
-        live = len(rows)
-        ids, positions, request_slots, tile_length, decode_token = (
-            out[layout[k]] for k in ("ids", "positions", "request_slots", "tile_length", "decode_token"))
-        tile_length[:live] = 1
-        decode_token[:live] = np.arange(live, dtype=np.int32)
+        live, width = len(rows), bucket.table_width
+        ids, positions, request_slots = (out[layout[k]] for k in ("ids", "positions", "request_slots"))
+        if stage["live"] != live:    # the parts' integers change only with the number of live rows
+            for name, array in self._prepare(bucket, live):
+                out[layout[name]] = array
+            stage["live"] = live
         if filled > live:   # rows an earlier, larger step left behind become padding again
-            tile_length[live:filled] = 0
-            decode_token[live:filled] = -1
             ids[live:filled] = 0
             positions[live:filled] = 0
             request_slots[live:filled] = 0
@@ -158,32 +190,29 @@ class DecodeGraphs:
             epoch = manager.epoch(rid)
             mirror = self._host_tables.get(rid)
             if mirror is None or mirror[0] != epoch or mirror[1] < pages or self._windowed:
-                held = []
-                for g in cache.groups:
-                    padded = np.full(self.table_width, -1, dtype=np.int32)
-                    table = manager.table(rid, g.index)
-                    padded[:len(table)] = table
-                    held.append(padded)
+                held = [np.asarray(manager.table(rid, g.index), dtype=np.int32) for g in cache.groups]
                 if len(self._host_tables) > 4 * manager.max_requests():
                     self._host_tables.clear()   # requests that left long ago
                 mirror = self._host_tables[rid] = (epoch, pages, held)
             held = mirror[2]
-            copy_table = held_rows is None or held_rows[row] is not held
-            if held_rows is not None:
-                held_rows[row] = held
+            copy_table = held_rows[row] is not held
+            held_rows[row] = held
             for g in cache.groups:
+                pages_held = held[g.index]
                 if copy_table:
                     table = out[layout[f"table{g.index}"]]
-                    table[row * self.table_width:(row + 1) * self.table_width] = held[g.index]
+                    count = min(len(pages_held), width)
+                    table[row * width:row * width + count] = pages_held[:count]
+                    table[row * width + count:(row + 1) * width] = -1
                 out[layout[f"slots{g.index}"]][row] = \
-                    held[g.index][position // page_tokens] * page_tokens + position % page_tokens
+                    pages_held[position // page_tokens] * page_tokens + position % page_tokens
 
     # ---------------------------------------------------------------- capture
-    def _capture(self, size: int) -> _Bucket:
+    def _capture(self, size: int, bound: int) -> _Bucket:
         from .. import ops
         engine = self.engine
-        bucket = _Bucket(size)
-        bucket.layout = self._layout(size)
+        bucket = _Bucket(size, bound, -(-bound // engine.cache.page_tokens))
+        self._layout(bucket)
         total = bucket.layout["end"].start
         host = np.zeros(total, dtype=np.int32)
         self._host_constants(bucket, host)   # all padding: nothing is read or written
@@ -194,7 +223,7 @@ class DecodeGraphs:
             pinned = torch.empty(total, dtype=torch.int32, pin_memory=True)
             pinned.numpy()[:] = host
             bucket.staging.append({"pinned": pinned, "array": pinned.numpy(), "copied": None,
-                                   "filled": 0, "held": [None] * size})
+                                   "filled": 0, "live": 0, "held": [None] * size})
         ctx, views = self._context(bucket), self._views(bucket)
         ids, wanted = bucket.static[bucket.layout["ids"]], bucket.static[bucket.layout["wanted"]]
         stream = torch.cuda.Stream(device=engine.device)
@@ -223,15 +252,16 @@ class DecodeGraphs:
         ever seeing them: the tokens an earlier step picked."""
         from .. import ops
         size = self.bucket_for(len(rows))
-        bucket = self.buckets.get(size)
+        bound = self.engine.context_bucket(max(row[2] for row in rows) + 1)
+        bucket = self.buckets.get((size, bound))
         if bucket is None:
-            bucket = self.buckets[size] = self._capture(size)
+            bucket = self.buckets[(size, bound)] = self._capture(size, bound)
         total = bucket.layout["end"].start
         stage = bucket.staging[bucket.turn]
         bucket.turn ^= 1
         if stage["copied"] is not None:
             stage["copied"].synchronize()   # the copy of two steps ago out of this buffer (long done)
-        self._host_fill(bucket, rows, stage["array"], stage["held"], stage["filled"])
+        self._host_fill(bucket, rows, stage)
         stage["filled"] = len(rows)
         bucket.static.copy_(stage["pinned"], non_blocking=True)
         if stage["copied"] is None:

@@ -24,17 +24,15 @@ import torch
 from .. import ops
 from ..cache import PagedCache
 from ..config import read_config
-from ..parts.registry import Runtime, StepContext
+from ..parts.registry import Runtime, StepContext, StepPlan, step_preparers
 from ..weights import load_tensors, random_tensors
 from .model import DecoderModel
 
 _DTYPES = {"bfloat16": torch.bfloat16, "bf16": torch.bfloat16, "float32": torch.float32,
            "fp32": torch.float32, torch.bfloat16: torch.bfloat16, torch.float32: torch.float32}
-ATTENTION_TILE = 16  # query tokens per tile of the general kernel (csrc/kernels/attention_tile.cu)
 STEP_GRAPHS = 8       # how many shapes of general steps keep a captured graph
 STEP_GRAPH_TOKENS = 8192   # ... of steps up to this many tokens (a graph keeps its activations)
-LONG_CONTEXT = 2048   # a portion of a prompt that sees this many keys or more counts as behind a long context
-WIDE_TILE = 128      # and of the tensor-core prompt kernels (csrc/kernels/attention_prefill*.cu)
+CONTEXT_BUCKET = 2048  # a captured graph serves contexts up to a power of two times this many positions
 
 
 class StepError(ValueError):
@@ -66,9 +64,17 @@ class Engine:
                  page_tokens: int = 16, num_pages: Optional[int] = None,
                  max_tokens: Optional[int] = None, max_requests: int = 64,
                  max_context: Optional[int] = None, device="cuda:0", gemm_backend: str = "auto",
-                 spec=None, cuda_graphs: bool = True, chained_launches: bool = True):
+                 spec=None, cuda_graphs: bool = True, chained_launches: bool = True,
+                 pool_bytes: Optional[int] = None, pool_fraction: Optional[float] = None,
+                 consume_tensors: bool = False):
+        """The cache pool is sized by the first of these that is given:
+        ``num_pages``; ``max_tokens`` (positions all live requests may hold);
+        ``pool_bytes``; ``pool_fraction`` of the device memory that is free
+        once the weights are resident (what a large model on one GPU wants);
+        else four contexts of up to 4,096 positions."""
         ops.require_cuda()
-        ops.set_chained_launches(chained_launches)
+        self.chained_launches = bool(chained_launches)
+        ops.set_chained_launches(self.chained_launches)
         self.config = config
         self.device = torch.device(device)
         self.dtype = resolve_dtype(dtype)
@@ -81,7 +87,16 @@ class Engine:
             torch.backends.cudnn.allow_tf32 = False
         self.runtime = Runtime(device=self.device, dtype=self.dtype, max_positions=self.max_context,
                                gemm_backend=gemm_backend)
-        self.model = DecoderModel(self.spec, tensors, self.runtime)
+        self.model = DecoderModel(self.spec, tensors, self.runtime, consume=consume_tensors)
+        if num_pages is None and max_tokens is None and (pool_bytes is not None or pool_fraction is not None):
+            if pool_bytes is None:
+                if not 0.0 < pool_fraction <= 1.0:
+                    raise ValueError(f"pool_fraction must lie in (0, 1], got {pool_fraction}")
+                torch.cuda.empty_cache()   # what building the model freed goes back to the device first
+                free, _ = torch.cuda.mem_get_info(self.device)     # the weights are on the device by now
+                pool_bytes = int(free * pool_fraction)
+            per_page = PagedCache.page_bytes(self.model.cache_needs(), page_tokens, self.dtype)
+            num_pages = max(int(pool_bytes) // per_page, 1) if per_page else 1
         if num_pages is None:
             tokens = max_tokens if max_tokens is not None else min(self.max_context, 4096) * 4
             num_pages = -(-tokens // page_tokens)
@@ -89,9 +104,15 @@ class Engine:
                                 self.dtype, self.device)
         self.manager = self.cache.manager
         from .decode_graph import DecodeGraphs
+        self._preparers = step_preparers(self.model.blocks)   # parts with integers of their own per step
         self.graphs = DecodeGraphs(self) if cuda_graphs and DecodeGraphs.usable(self.model) else None
-        # Graphs of general steps by shape (see _run), under the same condition.
-        self._step_graphs: Optional[Dict] = {} if self.graphs is not None else None
+        # Graphs of general steps by shape (see _run). Such a graph is warmed
+        # up and captured on a live step, which therefore runs more than once:
+        # harmless where a step only writes pages (written again with the
+        # same values), not where a part keeps state that a step advances.
+        stateless = all(need is None or need.kind != "state" for need in self.cache.needs)
+        self._step_graphs: Optional[Dict] = {} if self.graphs is not None and stateless else None
+        self.replay_general_steps = True   # False: general steps are launched kernel by kernel (measurements)
         self._shapes_seen: Dict = {}
         self._ids: Dict[Hashable, int] = {}   # request name -> manager id
         self._next_id = 1 << 40               # above any id a scheduler hands out
@@ -106,7 +127,7 @@ class Engine:
         device = options.get("device", "cuda:0")
         ops.require_cuda()
         tensors = load_tensors(model_dir, config, device=device)
-        return cls(config, tensors, **options)
+        return cls(config, tensors, consume_tensors=True, **options)
 
     @classmethod
     def from_random(cls, config, seed: int, **options) -> "Engine":
@@ -115,7 +136,7 @@ class Engine:
         dtype = resolve_dtype(options.get("dtype", "bfloat16"))
         name = "bfloat16" if dtype == torch.bfloat16 else "float32"
         tensors = random_tensors(config, seed, dtype=name, device=options.get("device", "cuda:0"))
-        return cls(config, tensors, **options)
+        return cls(config, tensors, consume_tensors=True, **options)
 
     # ---------------------------------------------------------------- requests
     def live(self, request: Hashable) -> bool:
@@ -147,6 +168,7 @@ class Engine:
         the next step overwrites: read it before stepping again. Call
         ``check()`` after reading results."""
         entries = [e if isinstance(e, StepEntry) else StepEntry(**e) for e in entries]
+        ops.set_chained_launches(self.chained_launches)   # another engine may have chosen otherwise
         self._validate(entries)
         manager, fresh = self.manager, []
         try:
@@ -307,15 +329,28 @@ class Engine:
             free = [self.manager.free_pages(g) for g in range(self.manager.num_groups())]
             raise StepError(f"out of cache pages: the step does not fit (free pages per group: {free})")
 
+    def context_bucket(self, longest: int) -> int:
+        """The bound a captured graph is laid out for when its longest request
+        holds ``longest`` positions: 2,048 times a power of two, at most the
+        engine's limit. Block tables, split counts and scratch of a graph
+        follow the contexts that are live, not the longest one allowed."""
+        bound = CONTEXT_BUCKET
+        while bound < longest:
+            bound *= 2
+        return min(bound, self.max_context)
+
     def _run(self, entries: List[StepEntry]) -> Optional[torch.Tensor]:
         """A general step: any mix of portions of prompts and decoded tokens.
 
-        The step's integers (token ids, positions, tiles, block tables, slots)
-        go to the device as one packed buffer. A step whose *shape* (the token
-        counts of its entries, how many logits are wanted) has been seen before
-        replays a CUDA graph captured for that shape, with its integers copied
-        into the graph's buffer: a prompt cut into equal portions, or the same
-        batch again, then costs one launch instead of some two hundred."""
+        The step's integers (token ids, positions, block tables, slots, and
+        what the parts prepare for themselves, such as the attention's tile
+        lists) go to the device as one packed buffer. A step whose *shape*
+        (the token counts of its entries, how many logits are wanted, the
+        bucket of its longest context, and what the parts say decides their
+        launches) has been seen before replays a CUDA graph captured for that
+        shape, with its integers copied into the graph's buffer: a prompt cut
+        into equal portions, or the same batch again, then costs one launch
+        instead of some two hundred."""
         manager, cache = self.manager, self.cache
         page_tokens = cache.page_tokens
         counts = [len(e.tokens) for e in entries]
@@ -328,10 +363,6 @@ class Engine:
         token_request = np.empty(total, dtype=np.int32)
         request_slots = np.empty(rows, dtype=np.int32)
         starts, wanted = [], []
-        tile_request, tile_start, tile_length = [], [], []
-        single_tiles, decode_token, decode_request, longest = [], [], [], 0
-        longest_keys = 0   # the most keys a portion of a prompt sees
-        wide = []   # (keys to walk, row, first token, count) of wide tiles
         group_tables = [[] for _ in cache.groups]
         for row, entry in enumerate(entries):
             rid = self._rid(entry)
@@ -343,47 +374,30 @@ class Engine:
             token_request[begin:begin + count] = row
             request_slots[row] = manager.slot(rid)
             wanted.extend(begin + index for index in entry.want)
-            if count == 1:
-                single_tiles.append((row, begin, 1))
-                decode_token.append(begin)
-                decode_request.append(row)
-                longest = max(longest, start + 1)
-            else:
-                for first in range(0, count, ATTENTION_TILE):
-                    tile_request.append(row)
-                    tile_start.append(begin + first)
-                    tile_length.append(min(ATTENTION_TILE, count - first))
-                longest_keys = max(longest_keys, start + count)
-                for first in range(0, count, WIDE_TILE):
-                    size = min(WIDE_TILE, count - first)
-                    wide.append((start + first + size, row, begin + first, size))
             for group in cache.groups:
                 group_tables[group.index].append(manager.table(rid, group.index))
-
-        multi_tiles = len(tile_request)
-        wide.sort(key=lambda item: -item[0])   # the tiles with most keys start first
-        for row, begin, count in single_tiles:  # tiles of multi-token requests first
-            tile_request.append(row)
-            tile_start.append(begin)
-            tile_length.append(count)
-        # A step that may be replayed as a graph has block tables of the full
-        # width, so that its buffer has one layout whatever the contexts are.
-        # Portions behind a long context run other attention launches (a tile's
-        # keys shared out among blocks) than the same portions at a prompt's start.
-        many_keys = longest_keys >= LONG_CONTEXT
-        shape_key = (tuple(counts), len(wanted), many_keys)
-        graphed = self._step_graphs is not None and total <= STEP_GRAPH_TOKENS and (
+        longest = max(start + count for start, count in zip(starts, counts))
+        plan = StepPlan(counts, starts, rows, longest)
+        prepared = {key: part.prepare_step(plan) for key, part in self._preparers.items()}
+        # A step that may be replayed as a graph has block tables as wide as
+        # its context bucket, so that its buffer has one layout whatever the
+        # contexts inside the bucket are.
+        bound = self.context_bucket(longest)
+        shape_key = (tuple(counts), len(wanted), bound, tuple(p.graph_key for p in prepared.values()))
+        graphed = self._step_graphs is not None and self.replay_general_steps and total <= STEP_GRAPH_TOKENS and (
             shape_key in self._step_graphs or self._shapes_seen.get(shape_key, 0) >= 1)
-        full_width = -(-self.max_context // page_tokens)
+        if graphed:   # the parts' integers and bounds for every step of this shape
+            plan = StepPlan(counts, starts, rows, bound, replayable=True)
+            prepared = {key: part.prepare_step(plan) for key, part in self._preparers.items()}
         # One packed int32 buffer, one copy to the device.
-        pieces = [token_ids, positions, token_request, request_slots,
-                  np.asarray(tile_request, dtype=np.int32), np.asarray(tile_start, dtype=np.int32),
-                  np.asarray(tile_length, dtype=np.int32), np.asarray(wanted, dtype=np.int32),
-                  np.asarray(decode_token, dtype=np.int32), np.asarray(decode_request, dtype=np.int32),
-                  np.asarray([w[1] for w in wide], dtype=np.int32),
-                  np.asarray([w[2] for w in wide], dtype=np.int32),
-                  np.asarray([w[3] for w in wide], dtype=np.int32)]
+        pieces = [token_ids, positions, token_request, request_slots, np.asarray(wanted, dtype=np.int32)]
         shapes = [None] * len(pieces)
+        for key, result in prepared.items():
+            for array in result.arrays.values():
+                pieces.append(np.ascontiguousarray(array, dtype=np.int32).reshape(-1))
+                shapes.append(tuple(array.shape) if array.ndim > 1 else None)
+        first_table = len(pieces)
+        full_width = -(-bound // page_tokens)
         for group in cache.groups:
             tables = group_tables[group.index]
             width = full_width if graphed else max(len(t) for t in tables)
@@ -405,39 +419,38 @@ class Engine:
             cursor += size
         self._keep = packed  # the pinned buffer must outlive the asynchronous copy
 
-        def forward(on_device: torch.Tensor, longest_context: int, keys: int) -> Optional[torch.Tensor]:
+        def forward(on_device: torch.Tensor) -> Optional[torch.Tensor]:
             views, cursor = [], 0
             for size, shape in zip(sizes, shapes):
                 view = on_device[cursor:cursor + size]
                 views.append(view.view(shape) if shape is not None else view)
                 cursor += size
-            (d_ids, d_positions, d_token_request, d_request_slots, d_tile_request, d_tile_start,
-             d_tile_length, d_wanted, d_decode_token, d_decode_request, d_wide_request, d_wide_start,
-             d_wide_length) = views[:13]
-            tables = {g.index: views[13 + 2 * g.index] for g in cache.groups}
-            slots = {g.index: views[14 + 2 * g.index] for g in cache.groups}
+            d_ids, d_positions, d_token_request, d_request_slots, d_wanted = views[:5]
+            extras, at = {}, 5
+            for key, result in prepared.items():
+                extras[key] = dict(result.facts)
+                for name in result.arrays:
+                    extras[key][name] = views[at]
+                    at += 1
+            tables = {g.index: views[first_table + 2 * g.index] for g in cache.groups}
+            slots = {g.index: views[first_table + 1 + 2 * g.index] for g in cache.groups}
             ctx = StepContext(
                 device=self.device, dtype=self.dtype, num_tokens=total, num_requests=rows,
                 positions=d_positions, token_request=d_token_request, request_slots=d_request_slots,
-                request_offsets=[int(v) for v in offsets], request_positions=starts,
-                tile_request=d_tile_request, tile_start=d_tile_start, tile_length=d_tile_length,
-                multi_tiles=multi_tiles, decode_token=d_decode_token if decode_token else None,
-                decode_request=d_decode_request if decode_token else None, longest_context=longest_context,
-                longest_keys=keys, wide_tile_request=d_wide_request, wide_tile_start=d_wide_start,
-                wide_tile_length=d_wide_length)
+                # inside a graph the host's view of one step would be baked in for all
+                request_offsets=None if graphed else [int(v) for v in offsets],
+                request_positions=None if graphed else starts, extras=extras)
             return self.model.forward(
                 d_ids, ctx, lambda entry, write: cache.view(entry, write, tables, slots),
                 d_wanted if wanted else None)
 
         if not graphed:
-            if self._step_graphs is not None:
+            if self._step_graphs is not None and self.replay_general_steps:
                 self._shapes_seen[shape_key] = self._shapes_seen.get(shape_key, 0) + 1
                 if len(self._shapes_seen) > 4096:
                     self._shapes_seen.clear()
-            return forward(packed.to(self.device, non_blocking=True), longest, longest_keys)
-        # a graph serves every context of its kind: the bound is the engine's
-        bound = self.max_context if many_keys else LONG_CONTEXT - 1
-        return self._replay_step(shape_key, packed, lambda on_device, longest_context: forward(on_device, longest_context, bound))
+            return forward(packed.to(self.device, non_blocking=True))
+        return self._replay_step(shape_key, packed, forward)
 
     def _replay_step(self, shape_key, packed: torch.Tensor, forward) -> Optional[torch.Tensor]:
         """Replays (after capturing it, the first time) the graph of a general
@@ -449,14 +462,14 @@ class Engine:
             stream = torch.cuda.Stream(device=self.device)
             stream.wait_stream(torch.cuda.current_stream(self.device))
             with torch.cuda.stream(stream):
-                forward(static, self.max_context)   # libraries and lazily loaded kernels settle before the capture
+                forward(static)   # libraries and lazily loaded kernels settle before the capture
             torch.cuda.current_stream(self.device).wait_stream(stream)
             torch.cuda.synchronize(self.device)
             graph = torch.cuda.CUDAGraph()
             before = ops.launch_count()
             pool = self.graphs.pool if self.graphs is not None else None
             with capture_quietly(graph, pool):
-                logits = forward(static, self.max_context)
+                logits = forward(static)
             if self.graphs is not None and self.graphs.pool is None:
                 self.graphs.pool = graph.pool()
             held = {"graph": graph, "static": static, "logits": logits, "kernels": ops.launch_count() - before}

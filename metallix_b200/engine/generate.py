@@ -11,6 +11,8 @@ those of ``mx gen`` (crates/app/cli/src/qwen_forward.rs:1021-1050).
 """
 from __future__ import annotations
 
+import contextlib
+import json
 import time
 from dataclasses import dataclass, field
 from typing import Callable, Dict, List, Optional, Sequence
@@ -45,11 +47,31 @@ class GenerationStats:
     step_ms: List[float] = field(default_factory=list)
 
 
+class _DeviceSpan:
+    def __init__(self, store: dict, key: int):
+        self.store, self.key = store, key
+
+    def __enter__(self):
+        self.start = torch.cuda.Event(enable_timing=True)
+        self.start.record()
+
+    def __exit__(self, *exc):
+        if exc[0] is None:
+            end = torch.cuda.Event(enable_timing=True)
+            end.record()
+            self.store[self.key] = (self.start, end)
+
+
+_NO_SPAN = contextlib.nullcontext()
+
+
 class Generator:
     """Continuous batching over one engine."""
 
     def __init__(self, engine: Engine, max_num_seqs: int = 8, max_tokens_per_step: int = 8192,
-                 prefill_chunk: int = 0, run_ahead: bool = True):
+                 prefill_chunk: int = 0, run_ahead: bool = True, trace: bool = False):
+        """``trace``: keep one record per step (what the plan held, host time,
+        device time between CUDA events) for ``write_trace``."""
         host = build.host()
         self.engine = engine
         self.host = host
@@ -67,6 +89,9 @@ class Generator:
         self._host_tokens: Optional[torch.Tensor] = None
         self._tokens_copied: Optional[torch.cuda.Event] = None
         self._timing: Dict[int, GenerationResult] = {}
+        self._trace: Optional[List[dict]] = [] if trace else None
+        self._trace_origin = time.perf_counter()
+        self._launch_events: Dict[int, tuple] = {}   # id(plan) -> CUDA events around its launch
 
     def add(self, prompt: Sequence[int], max_new_tokens: int, params: SamplingParams = SamplingParams(),
             eos_ids: Sequence[int] = (), ignore_eos: bool = False) -> int:
@@ -112,10 +137,12 @@ class Generator:
         arrived) it is dropped and the plan runs as usual. What a request
         generates is the same either way; the device no longer waits for the
         host between two steps."""
-        if self._ahead is not None:
-            plan, logits = self._ahead      # launched during the previous call
+        ahead = self._ahead is not None
+        if ahead:
+            plan, logits, events_key = self._ahead      # launched during the previous call
             self._ahead = None
         else:
+            events_key = None
             if self._planned is not None:
                 plan, self._planned = self._planned, None
             else:
@@ -124,6 +151,7 @@ class Generator:
             if not plan.entries:
                 return []
             logits = self._launch(plan)
+            events_key = id(plan)
         started = time.perf_counter()
         rows = [self._params[e.id] for e in plan.entries if e.wants_token]
         positions = [e.generated_position for e in plan.entries if e.wants_token]
@@ -158,7 +186,7 @@ class Generator:
                     and [e.id for e in following.entries] == requests
                     and all(len(e.tokens) == 1 and e.wants_token for e in following.entries)):
                 self.engine.commit_ahead(requests)
-                self._ahead = (following, ahead_logits)
+                self._ahead = (following, ahead_logits, id(requests))
                 self.stats.ahead_kept += 1
             else:
                 self.engine.drop_ahead(requests)
@@ -169,6 +197,15 @@ class Generator:
         self.stats.decode_tokens += plan.decode_tokens
         self.stats.prefill_tokens += plan.prefill_tokens
         self.stats.step_ms.append((now - started) * 1e3)
+        if self._trace is not None:
+            self._trace.append({
+                "step": self.stats.steps - 1, "host_start": started - self._trace_origin, "host_end": now - self._trace_origin,
+                "events": self._launch_events.pop(events_key, None), "requests": len(plan.entries),
+                "decode_tokens": plan.decode_tokens, "prefill_tokens": plan.prefill_tokens,
+                "preempted": len(plan.preempted), "launched_ahead": ahead,
+                "waiting": self.scheduler.num_waiting(), "free_pages": self.engine.manager.free_pages(0)})
+            if len(self._launch_events) > 8:
+                self._launch_events.clear()   # launches of steps that were dropped
         for event in events:
             result = self._timing[event.id]
             if not result.generated_ids and not result.decode_ms and result.prefill_ms == 0.0:
@@ -185,10 +222,15 @@ class Generator:
             entries.append(StepEntry(request=entry.id, tokens=entry.tokens,
                                      want=(count - 1,) if entry.wants_token else (), managed=True))
         try:
-            return self.engine.step(entries)
+            with self._device_span(plan):
+                return self.engine.step(entries)
         except Exception as error:
             self.scheduler.fail_plan(plan, f"step failed: {error}")
             raise
+
+    def _device_span(self, key):
+        """CUDA events around a step's launches, kept under ``key`` for the trace."""
+        return _NO_SPAN if self._trace is None else _DeviceSpan(self._launch_events, id(key))
 
     def _token_buffer(self, count: int) -> torch.Tensor:
         if self._host_tokens is None or self._host_tokens.numel() < count:
@@ -211,7 +253,8 @@ class Generator:
             if entry.generated_position + 1 >= self._limits[entry.id]:
                 return None
             requests.append(entry.id)
-        logits = self.engine.launch_ahead(requests, picked)
+        with self._device_span(requests):
+            logits = self.engine.launch_ahead(requests, picked)
         return None if logits is None else (requests, logits)
 
     def result(self, rid: int) -> GenerationResult:
@@ -223,6 +266,38 @@ class Generator:
         result.preemptions = info.preemptions
         result.cached_tokens = len(info.prompt) + max(len(info.output) - 1, 0)
         return result
+
+    def write_trace(self, path: str) -> None:
+        """A Chrome / Perfetto JSON timeline: per step one span of the host
+        (track "host") and one of the device between the CUDA events around
+        its launches (track "device"), with what the plan held as arguments;
+        after the reference's ``--trace-out`` timeline of ``engine.step`` and
+        ``engine.prefill`` spans (crates/app/cli/src/cli.rs:70-74,
+        crates/app/cli/src/engine_loop.rs:619-628)."""
+        if self._trace is None:
+            raise ValueError("this generator keeps no trace: build it with trace=True")
+        torch.cuda.synchronize(self.engine.device)
+        events, origin, device_offset = [], None, 0.0
+        for record in self._trace:
+            arguments = {k: record[k] for k in ("step", "requests", "decode_tokens", "prefill_tokens", "preempted",
+                                                 "launched_ahead", "waiting", "free_pages")}
+            events.append({"name": "engine.step", "ph": "X", "pid": 1, "tid": 1, "cat": "host",
+                           "ts": record["host_start"] * 1e6,
+                           "dur": (record["host_end"] - record["host_start"]) * 1e6, "args": arguments})
+            pair = record["events"]
+            if pair is None:
+                continue
+            if origin is None:   # device times are relative to the first step's start, laid at its host time
+                origin, device_offset = pair[0], record["host_start"] * 1e6
+            arguments = dict(arguments, device_ms=pair[0].elapsed_time(pair[1]))
+            name = "engine.prefill" if record["prefill_tokens"] else "engine.decode"
+            events.append({"name": name, "ph": "X", "pid": 1, "tid": 2, "cat": "device",
+                           "ts": device_offset + origin.elapsed_time(pair[0]) * 1e3,
+                           "dur": pair[0].elapsed_time(pair[1]) * 1e3, "args": arguments})
+        meta = [{"name": "thread_name", "ph": "M", "pid": 1, "tid": 1, "args": {"name": "host"}},
+                {"name": "thread_name", "ph": "M", "pid": 1, "tid": 2, "args": {"name": "device"}}]
+        with open(path, "w", encoding="utf-8") as handle:
+            json.dump({"traceEvents": meta + events, "displayTimeUnit": "ms"}, handle)
 
     def run(self, on_token: Optional[Callable] = None) -> None:
         """Steps until nothing waits or runs."""
@@ -236,19 +311,22 @@ def generate(engine: Engine, prompts: Sequence[Sequence[int]], max_new_tokens: i
              temperature: float = 0.0, seed: int = 0, top_p: float = 1.0, top_k: int = 0,
              sampler: str = "icdf", eos_ids: Optional[Sequence[int]] = None,
              ignore_eos: bool = False, max_num_seqs: int = 8, max_tokens_per_step: int = 8192,
-             prefill_chunk: int = 0, run_ahead: bool = True) -> List[GenerationResult]:
+             prefill_chunk: int = 0, run_ahead: bool = True, trace_out: Optional[str] = None) -> List[GenerationResult]:
     """Generates for every prompt (lists of token ids) and returns the results
     in the prompts' order. ``temperature`` 0 is greedy; otherwise request i
-    draws from (seed, stream i). ``eos_ids`` defaults to the configuration's."""
+    draws from (seed, stream i). ``eos_ids`` defaults to the configuration's.
+    ``trace_out``: a file for the timeline of the steps (``Generator.write_trace``)."""
     if eos_ids is None:
         eos_ids = tuple(getattr(engine.config, "eos_token_ids", ()) or ())
     generator = Generator(engine, max_num_seqs=max_num_seqs,
                           max_tokens_per_step=max_tokens_per_step, prefill_chunk=prefill_chunk,
-                          run_ahead=run_ahead)
+                          run_ahead=run_ahead, trace=trace_out is not None)
     ids = [generator.add(prompt, max_new_tokens,
                          SamplingParams(temperature=temperature, seed=seed, stream=index,
                                         top_p=top_p, top_k=top_k, sampler=sampler),
                          eos_ids=eos_ids, ignore_eos=ignore_eos)
            for index, prompt in enumerate(prompts)]
     generator.run()
+    if trace_out is not None:
+        generator.write_trace(trace_out)
     return [generator.result(rid) for rid in ids]

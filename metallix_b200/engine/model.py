@@ -13,7 +13,11 @@ from ..parts.registry import (CacheView, Runtime, StepContext, WeightStore, _BUI
 
 
 class DecoderModel:
-    def __init__(self, spec: ModelSpec, tensors: Dict[str, torch.Tensor], runtime: Runtime):
+    def __init__(self, spec: ModelSpec, tensors: Dict[str, torch.Tensor], runtime: Runtime,
+                 consume: bool = False):
+        """``consume``: the caller gives ``tensors`` away; entries are removed
+        as the parts take them, so that a model close to the device's memory
+        never holds its weights twice."""
         spec.validate()
         self.spec, self.runtime = spec, runtime
         weights = WeightStore(tensors)
@@ -24,11 +28,15 @@ class DecoderModel:
             if builder is None:
                 raise KeyError(f"no block arrangement of kind {layer.block.kind!r}")
             self.blocks.append(builder(layer, weights, runtime))
+            if consume:
+                weights.drop_taken(keep=(spec.embedding.get("weight"), spec.head.get("weight")))
         self.final_norm = build_part("norm", spec.final_norm, weights, runtime)
         head_builder = _BUILDERS.get(("head", spec.head.kind))
         if head_builder is None:
             raise KeyError(f"no head of kind {spec.head.kind!r}")
         self.head = head_builder(spec.head, weights, runtime, self.embedding)
+        if consume:
+            weights.drop_taken()
         self.order = list(spec.order)
         self.vocab_size = spec.vocab_size
 

@@ -140,11 +140,19 @@ def require_cuda() -> None:
     build.kernels()
 
 
+_chained: Optional[bool] = None
+
+
 def set_chained_launches(enabled: bool) -> None:
     """Lets consecutive kernels of this library overlap (programmatic dependent
     launch): a kernel may start, and fetch weights, while its predecessor is
-    still running, and waits for the predecessor before it reads its output."""
-    _fn("mxb_set_chained_launches")(1 if enabled else 0)
+    still running, and waits for the predecessor before it reads its output.
+    The switch belongs to the library; an engine sets it to its own choice
+    before it launches."""
+    global _chained
+    if _chained is not enabled:
+        _fn("mxb_set_chained_launches")(1 if enabled else 0)
+        _chained = bool(enabled)
 
 
 TIMELINE_SOURCES = ("norms", "gemm_load", "gemm_stream", "qk_rope", "attention")

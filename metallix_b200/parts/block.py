@@ -28,6 +28,9 @@ class PreNormResidualBlock:
         self.feed_forward = build_part("feed_forward", layer.feed_forward, weights, runtime)
         self.dtype = runtime.dtype
 
+    def parts(self):
+        return [self.mixer_norm, self.mixer, self.feed_forward_norm, self.feed_forward]
+
     def forward(self, residual: torch.Tensor, pending: Optional[torch.Tensor], ctx: StepContext,
                 cache: CacheView) -> torch.Tensor:
         """``residual`` (float32, updated in place) plus ``pending`` is the

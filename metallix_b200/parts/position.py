@@ -24,14 +24,18 @@ class RotaryHalf:
         if rotary_dim % 2 or not 0 < rotary_dim <= head_dim:
             raise ValueError(f"rotary_dim {rotary_dim} must be even and within head_dim {head_dim}")
         self.theta, self.rotary_dim, self.head_dim = float(theta), rotary_dim, head_dim
-        half = rotary_dim // 2
-        index = torch.arange(half, dtype=torch.float64, device=runtime.device)
-        frequency = torch.pow(torch.tensor(self.theta, dtype=torch.float64, device=runtime.device),
-                              -2.0 * index / rotary_dim)
-        position = torch.arange(runtime.max_positions, dtype=torch.float64, device=runtime.device)
-        angle = position[:, None] * frequency[None, :]
-        self.cos = torch.cos(angle).to(torch.float32).contiguous()
-        self.sin = torch.sin(angle).to(torch.float32).contiguous()
+        # Layers with the same parameters share one pair of tables.
+        key = ("rope_half", self.theta, rotary_dim, runtime.max_positions, str(runtime.device))
+        if key not in runtime.shared:
+            half = rotary_dim // 2
+            index = torch.arange(half, dtype=torch.float64, device=runtime.device)
+            frequency = torch.pow(torch.tensor(self.theta, dtype=torch.float64, device=runtime.device),
+                                  -2.0 * index / rotary_dim)
+            position = torch.arange(runtime.max_positions, dtype=torch.float64, device=runtime.device)
+            angle = position[:, None] * frequency[None, :]
+            runtime.shared[key] = (torch.cos(angle).to(torch.float32).contiguous(),
+                                   torch.sin(angle).to(torch.float32).contiguous())
+        self.cos, self.sin = runtime.shared[key]
 
     def apply(self, q: torch.Tensor, k: torch.Tensor, positions: torch.Tensor):
         """Rotates q [tokens, heads * head_dim] and k [tokens, kv_heads * head_dim];

@@ -13,7 +13,7 @@ and a model spec that names ``PartSpec("my_mixer", {...})`` then builds it.
 from __future__ import annotations
 
 from dataclasses import dataclass, field
-from typing import Callable, Dict, List, Optional, Tuple
+from typing import Callable, Dict, Hashable, List, Optional, Sequence, Tuple
 
 import torch
 
@@ -53,6 +53,9 @@ class Runtime:
     dtype: torch.dtype          # compute dtype: torch.bfloat16 or torch.float32
     max_positions: int          # longest context the engine will run
     gemm_backend: str = "auto"  # how bfloat16 matrix products run: auto | tcgen05 | cublas | simple
+    # Read-only tensors that parts built from equal parameters may share
+    # (tables of a position encoding, say), by a key of those parameters.
+    shared: Dict[tuple, object] = field(default_factory=dict)
 
 
 class WeightStore:
@@ -70,6 +73,15 @@ class WeightStore:
 
     def has(self, name: str) -> bool:
         return name in self._tensors
+
+    def drop_taken(self, keep=()) -> None:
+        """Forgets the tensors that parts have taken (except ``keep``), for an
+        owner that hands its dictionary over: a part that stacked or cast a
+        weight holds a copy, and the original's memory is wanted back while a
+        large model is still being built."""
+        for name in set(self.taken):
+            if name not in keep:
+                self._tensors.pop(name, None)
 
 
 @dataclass
@@ -93,11 +105,53 @@ class CacheView:
 
 
 @dataclass
+class StepPlan:
+    """A step as the host knows it, handed to the parts that keep integers
+    of their own for it (``prepare_step``): request row r brings
+    ``counts[r]`` tokens at positions ``starts[r]`` onwards; rows from
+    ``live`` on are padding of a captured graph (they bring a token that
+    nothing may read or write). ``context_bound`` bounds position + 1 of every
+    token. ``replayable``: the integers go into a captured graph that later
+    steps of the same shape replay with other positions, so sizes of the
+    arrays may depend on ``counts`` (and on the part's ``graph_key``) only, and
+    bounds that kernels are launched with must be ``context_bound``, not
+    what this one step needs."""
+
+    counts: Sequence[int]
+    starts: Sequence[int]
+    live: int
+    context_bound: int
+    replayable: bool = False
+
+
+@dataclass
+class Prepared:
+    """What a part's ``prepare_step(plan)`` returns. ``arrays``: int32 numpy
+    arrays by name, which travel to the device with the step's other integers
+    (one copy) and come back as device tensors under the same names;
+    ``facts``: host values for the part's ``forward``; ``graph_key``: what,
+    beyond the shape of the step, decides which kernels the part launches (two
+    steps may share a captured graph only if it is equal)."""
+
+    arrays: Dict[str, "object"] = field(default_factory=dict)
+    facts: Dict[str, object] = field(default_factory=dict)
+    graph_key: Hashable = None
+
+
+@dataclass
 class StepContext:
     """One step's batch, as the parts see it. Tokens of all requests are
     packed one after another; request row r owns tokens
     ``request_offsets[r] .. request_offsets[r + 1] - 1`` at consecutive
-    positions starting at ``request_positions[r]``."""
+    positions starting at ``request_positions[r]``. The two host lists are
+    None while a graph is captured or replayed: a part that needs them on the
+    host cannot ride in a graph (it says ``graph_safe = False``).
+
+    A part that needs integers of its own for a step (tile lists of an
+    attention kernel, say) defines ``step_key`` (parts with the same key share
+    one preparation) and ``prepare_step(plan) -> Prepared``; the engine calls
+    it once per step and leaves the result, arrays on the device, in
+    ``extras[step_key]``: a dict of the arrays and the facts by name."""
 
     device: torch.device
     dtype: torch.dtype
@@ -106,23 +160,48 @@ class StepContext:
     positions: torch.Tensor            # int32 [tokens], absolute position of each token
     token_request: torch.Tensor        # int32 [tokens], request row of each token
     request_slots: torch.Tensor        # int32 [requests], state slot of each request row
-    request_offsets: List[int]         # host, [requests + 1]
-    request_positions: List[int]       # host, first position of each row's tokens
-    tile_request: torch.Tensor         # int32 [tiles], attention query tiles of every request
-    tile_start: torch.Tensor
-    tile_length: torch.Tensor
-    # The same batch split by kind of request, for mixers with a kernel of
-    # their own for single decoded tokens: tiles of the requests that bring
-    # several tokens, and (token, request row) of those that bring one.
-    # ``decode_token`` may hold negative entries (padding rows).
-    multi_tiles: int = 0               # the first ``multi_tiles`` tiles belong to multi-token requests
-    decode_token: Optional[torch.Tensor] = None    # int32 [decode rows]
-    decode_request: Optional[torch.Tensor] = None  # int32 [decode rows]
-    longest_context: int = 0           # upper bound of position + 1 over the decode rows
-    longest_keys: int = 0              # upper bound of the keys a wide tile sees (0: no bound known, taken as few)
-    # Tiles of up to 64 tokens over the multi-token requests, for the
-    # tensor-core prompt kernel; longest keys first.
-    wide_tile_request: Optional[torch.Tensor] = None
-    wide_tile_start: Optional[torch.Tensor] = None
-    wide_tile_length: Optional[torch.Tensor] = None
+    request_offsets: Optional[List[int]]    # host, [requests + 1]
+    request_positions: Optional[List[int]]  # host, first position of each row's tokens
     extras: Dict[str, object] = field(default_factory=dict)
+
+
+def step_preparers(blocks) -> Dict[str, object]:
+    """The parts of ``blocks`` that prepare integers for a step, one per
+    ``step_key``."""
+    found: Dict[str, object] = {}
+    for block in blocks:
+        for part in block_parts(block):
+            key = getattr(part, "step_key", None)
+            if key is not None and key not in found and hasattr(part, "prepare_step"):
+                found[key] = part
+    return found
+
+
+def block_parts(block) -> List[object]:
+    """Every part a block holds: what its ``parts()`` names (else its
+    ``mixer``, ``feed_forward`` and the two norms), and what those parts name
+    in turn through a ``parts()`` of their own (an attention mixer holds head
+    norms and a position encoding)."""
+    def own(holder):
+        if hasattr(holder, "parts"):
+            return [p for p in holder.parts() if p is not None]
+        return []
+    first = own(block) or [getattr(block, name) for name in
+                           ("mixer_norm", "mixer", "feed_forward_norm", "feed_forward")
+                           if getattr(block, name, None) is not None]
+    found, queue = [], list(first)
+    while queue:
+        part = queue.pop(0)
+        if any(part is other for other in found):
+            continue
+        found.append(part)
+        queue.extend(own(part))
+    return found
+
+
+def graph_safe(part) -> bool:
+    """Whether a part may ride in a captured graph: it launches the same work
+    whatever the step's integers and the device's values are (no host reads).
+    A mixer must say so (``graph_safe = True``); any other part is taken at
+    its word only when it says no (``graph_safe = False``)."""
+    return bool(getattr(part, "graph_safe", not hasattr(part, "cache_need")))

@@ -197,11 +197,45 @@ def test_command_line(model_folders, tmp_path):
     result = subprocess.run([sys.executable, os.path.join(ROOT, "bin", "mxb"), "gen", "--model", folder,
                              "--input-ids", ",".join(map(str, prompt)), "--max-tokens", "6",
                              "--dtype", "float32", "--block-size", str(page), "--num-pages", "32",
-                             "--verify-cache"], capture_output=True, text=True, timeout=600)
+                             "--verify-cache", "--trace-out", str(tmp_path / "trace.json")],
+                            capture_output=True, text=True, timeout=600)
     assert result.returncode == 0, result.stderr[-2000:]
     report = json.loads(result.stdout.strip().splitlines()[-1])
     assert report["generated_ids"] == expected and report["finish_reason"] == "length"
     assert report["input_ids"] == prompt and report["cached_tokens"] == 7 + 5
     assert report["logical_kv_bytes"] == 12 * 2 * 2 * 2 * 16 * 4   # tokens * layers * (K, V) * heads * dim * bytes
-    assert report["cache_comparisons"]["greedy_tokens_match"] is True
+    assert report["operation"] == "qwen3_greedy_cached_generation"
+    comparison = report["cache_comparisons"]
+    assert comparison["greedy_tokens_match"] is True and comparison["logits_within_bound"] is True
+    assert comparison["positions"] == 6 and comparison["max_abs_logit_difference"] < 1e-4
     assert len(report["decode_ms"]) == 5
+    # the timeline: one host span per step, device spans named by what the step did
+    trace = json.load(open(tmp_path / "trace.json"))["traceEvents"]
+    host = [e for e in trace if e.get("cat") == "host"]
+    device = [e for e in trace if e.get("cat") == "device"]
+    assert len(host) == 6 and [e["args"]["step"] for e in host] == list(range(6))
+    assert host[0]["args"]["prefill_tokens"] == 7 and host[1]["args"]["decode_tokens"] == 1
+    assert device and device[0]["name"] == "engine.prefill" and all(e["dur"] > 0 for e in device)
+    assert any(e["name"] == "engine.decode" for e in device)
+
+
+def test_random_weights_are_the_same_made_in_place_or_written_first(tmp_path):
+    """``gen --config X --random-weights S`` and ``random-weights --seed S``
+    followed by ``gen --model`` generate from the same tensors."""
+    from conftest import TINY_D
+    config_path = tmp_path / "config.json"
+    config_path.write_text(json.dumps(TINY_D))
+    mxb = [sys.executable, os.path.join(ROOT, "bin", "mxb")]
+    common = ["--input-ids", "5,9,200,31", "--max-tokens", "12", "--dtype", "bfloat16", "--ignore-eos"]
+    direct = subprocess.run(mxb + ["gen", "--config", str(config_path), "--random-weights", "3"] + common,
+                            capture_output=True, text=True, timeout=600)
+    assert direct.returncode == 0, direct.stderr[-2000:]
+    folder = tmp_path / "written"
+    made = subprocess.run(mxb + ["random-weights", "--config", str(config_path), "--seed", "3", "--out", str(folder)],
+                          capture_output=True, text=True, timeout=600)
+    assert made.returncode == 0, made.stderr[-2000:]
+    loaded = subprocess.run(mxb + ["gen", "--model", str(folder)] + common, capture_output=True, text=True, timeout=600)
+    assert loaded.returncode == 0, loaded.stderr[-2000:]
+    first = json.loads(direct.stdout.strip().splitlines()[-1])["generated_ids"]
+    second = json.loads(loaded.stdout.strip().splitlines()[-1])["generated_ids"]
+    assert len(first) == 12 and first == second

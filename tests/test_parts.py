@@ -27,23 +27,16 @@ def store(tensors):
 def context(dtype, counts, starts):
     """A StepContext for requests with ``counts`` tokens starting at ``starts``."""
     from metallix_b200.parts import StepContext
-    positions, token_request, tile_request, tile_start, tile_length, offsets = [], [], [], [], [], [0]
+    positions, token_request, offsets = [], [], [0]
     for row, (count, start) in enumerate(zip(counts, starts)):
-        begin = len(positions)
         positions += list(range(start, start + count))
         token_request += [row] * count
-        for first in range(0, count, 16):
-            tile_request.append(row)
-            tile_start.append(begin + first)
-            tile_length.append(min(16, count - first))
         offsets.append(len(positions))
     as_int = lambda v: torch.tensor(v, dtype=torch.int32, device="cuda")
     return StepContext(device=torch.device("cuda:0"), dtype=dtype, num_tokens=len(positions),
                        num_requests=len(counts), positions=as_int(positions),
                        token_request=as_int(token_request), request_slots=as_int(list(range(len(counts)))),
-                       request_offsets=offsets, request_positions=list(starts),
-                       tile_request=as_int(tile_request), tile_start=as_int(tile_start),
-                       tile_length=as_int(tile_length))
+                       request_offsets=offsets, request_positions=list(starts))
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])

@@ -74,15 +74,38 @@ def test_noalloc_entry_point_matches_the_ordinary_one_twice_in_a_row(dtype, limi
                                    case["row_request"], case["positions"], case["scale"], case["longest"],
                                    window)
         ops.check_status("cuda")
-        got = torch.full_like(case["q"], float("nan"))
-        status_word = torch.zeros(1, dtype=torch.int32, device="cuda")   # warm torch's own pools
-        del status_word
-        before = torch.cuda.memory_reserved()
-        code, status = call_noalloc(library, case, got, window)
+        # A first call looks the array's address up (and lets the driver load
+        # the kernels it needs); the calls after it must leave the device's
+        # free memory where it was. The driver's own count is read, not the
+        # tensor library's: an allocation inside the entry point would not
+        # pass through the latter.
+        first = torch.full_like(case["q"], float("nan"))
+        code, status = call_noalloc(library, case, first, window)
         assert code == 0 and status == 0
-        assert torch.cuda.memory_reserved() == before   # nothing new was taken from the device
+        assert (first.double() - expected.double()).abs().max().item() < limit
+        got = torch.full_like(case["q"], float("nan"))
+        torch.cuda.synchronize()
+        free_before, _ = torch.cuda.mem_get_info()
+        code, status = call_noalloc(library, case, got, window)
+        free_after, _ = torch.cuda.mem_get_info()
+        assert code == 0 and status == 0
+        assert free_after == free_before   # nothing was taken from the device, nothing given back
         assert not torch.isnan(got).any()
         assert (got.double() - expected.double()).abs().max().item() < limit
+
+
+def test_noalloc_entry_point_flags_a_context_beyond_its_bound():
+    """``longest_context`` sizes the scratch; a row whose position lies beyond
+    it is left untouched and reported in the status word, instead of reading
+    partial results that were never sized for it."""
+    from metallix_b200.csrc import build
+    library = build.kernels()
+    case = make_case(4, torch.bfloat16, [100, 700, 60], heads=8, kv_heads=2, head_dim=128, page_tokens=16)
+    case["longest"] = 256                       # the second request holds 700 positions
+    out = torch.full_like(case["q"], 7.0)
+    code, status = call_noalloc(library, case, out)
+    assert code == 0 and status & 2
+    assert bool((out[1] == 7.0).all()) and not bool((out[0] == 7.0).any()) and not bool((out[2] == 7.0).any())
 
 
 def test_noalloc_entry_point_refuses_what_does_not_fit():
