@@ -678,6 +678,10 @@ def main():
     parser.add_argument("--context", type=int, default=4096)
     parser.add_argument("--gemm", default="auto")
     parser.add_argument("--no-points", action="store_true", help="skip batch 1 and 64")
+    parser.add_argument("--decode-many", type=int, default=2048)
+    parser.add_argument("--decode-resident", type=int, default=None,
+                        help="blocks of the decode attention the GPU is taken to hold at once (0: one block per "
+                             "tile always); default: the library's")
     # --shape 8b / 32b
     parser.add_argument("--requests", type=int, default=64)
     parser.add_argument("--max-tokens-per-step", type=int, default=8192)
@@ -706,6 +710,9 @@ def main():
     if args.gpus != 1:
         print(f"bench.py measures one GPU: this engine runs on a single B200, --gpus {args.gpus} is outside it")
         return 2
+    if args.decode_resident is not None:
+        from metallix_b200 import ops
+        ops.set_decode_resident_blocks(args.decode_resident, max(args.decode_many, args.decode_resident))
     if args.workload:
         return workload(args)
     if args.shape == "8b":

@@ -660,6 +660,253 @@ paged_attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_cache,
   }
 }
 
+// ---------------------------------------------------------------------------
+// The same attention for steps whose (token, key/value head) pairs are few
+// enough that all their blocks can be resident at once but whose tiles are
+// too many for that: a pair gets `slots` blocks, and block s takes the 128-key
+// tiles first + s, first + s + slots, ... of the token's keys one after
+// another, with a running maximum, sum and accumulator per warp. The next
+// tile's keys are fetched while this tile's values are still being used, its
+// values while the next scores are taken, so two tiles' copies overlap in the
+// 64 KB a block holds anyway. Every block is resident from the start, so every
+// block's first tile is fetched before the wait for the kernel ahead, and no
+// block waits for a slot on an SM behind a whole round of others. A block
+// leaves one partial result (slot s of the pair); the merge kernel puts the
+// slots together in slot order. Which block takes which tile depends on the
+// token's position and on `slots` alone.
+template <int HD>
+__global__ void __launch_bounds__(kDecodeThreads)
+paged_attention_decode_resident_kernel(const __grid_constant__ CUtensorMap map_cache, const __nv_bfloat16* __restrict__ q,
+                                       float* __restrict__ partial, const int* __restrict__ block_tables,
+                                       int max_pages, const int* __restrict__ row_token,
+                                       const int* __restrict__ row_request, const int* __restrict__ positions,
+                                       int heads, int kv_heads, int page_tokens, int num_pages, int max_splits,
+                                       int window, float scale, int* status) {
+  constexpr int HALVES = HD / kTmaColumns;                 // 64-value halves of a row
+  constexpr int TILE_BYTES = kSplitKeys * HD * 2;
+  extern __shared__ unsigned char tma_decode_raw[];
+  __shared__ __align__(8) uint64_t barriers[2];   // keys, values
+  unsigned char* sK = tma_decode_raw + ((1024 - (shared_address(tma_decode_raw) & 1023)) & 1023);
+  unsigned char* sV = sK + TILE_BYTES;
+  float* s_merge = reinterpret_cast<float*>(sK);           // [4 warps][8 heads][HD + 2], over K once the scores exist
+  static_assert(4 * 8 * (HD + 2) * sizeof(float) <= TILE_BYTES, "the merge area must fit over the keys");
+
+  chain_release();
+  // What follows up to chain_wait() reads nothing a kernel of this step writes.
+  const int rank = blockIdx.x, slots = gridDim.x, kv = blockIdx.y, row = blockIdx.z;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int g = lane >> 2, t = lane & 3;
+  // One thread per box: keys or values, page of the tile, 64-value half.
+  const int pages = kSplitKeys / page_tokens;   // <= 16
+  const int boxes = 2 * pages * HALVES;         // <= 64
+  const bool fetcher = tid < boxes;
+  const int which = tid / (pages * HALVES), slot = (tid / HALVES) % pages, half = tid % HALVES;
+  const int token = row_token[row];
+  const int table_row = row_request[row];
+  const int* table = block_tables + static_cast<size_t>(table_row) * max_pages;
+  // The page of this block's first tile is asked for together with the
+  // position, on the guess that no window has moved the first tile.
+  int page = 0;
+  if (fetcher && rank * pages + slot < max_pages) page = table[rank * pages + slot];
+  if (token < 0) return;   // a padding row
+  const int pos = positions[token];
+  const int group = heads / kv_heads;  // <= 8
+  const int first_key = window > 0 ? max(0, pos - window + 1) : 0;
+  const int first_tile = first_key / kSplitKeys, last_tile = pos / kSplitKeys;
+  int tile = first_tile + rank;
+  if (first_tile > 0) {
+    page = 0;
+    if (fetcher && tile * pages + slot < max_pages) page = table[tile * pages + slot];
+  }
+
+  if (tid == 0) {
+    barrier_init(&barriers[0], 1);
+    barrier_init(&barriers[1], 1);
+    barrier_init_fence();
+    if (tile <= last_tile) {
+      barrier_arrive_expect(&barriers[0], TILE_BYTES);   // every box is fetched, whatever it holds
+      barrier_arrive_expect(&barriers[1], TILE_BYTES);
+    }
+  }
+  __syncthreads();
+  unsigned char* dst = (which ? sV : sK) + half * (kSplitKeys * 128) + slot * page_tokens * 128;
+  // The box of page `page_id` of tile `of_tile` for this thread: beyond the
+  // cache's last row (zeros) when the page holds none of the token's keys.
+  auto box_row_of = [&](int of_tile, int page_id) {
+    const int page_key = of_tile * kSplitKeys + slot * page_tokens;
+    bool wanted = page_key <= pos && page_key + page_tokens > first_key;
+    if (wanted && (page_id < 0 || page_id >= num_pages)) {
+      atomicOr(status, kStatusBadPage);
+      wanted = false;
+    }
+    return wanted ? ((page_id * 2 + which) * kv_heads + kv) * page_tokens : num_pages * 2 * kv_heads * page_tokens;
+  };
+  // The page that holds the token's own position is written by the kernel
+  // ahead of this one: it waits; every other page of the first tile is
+  // fetched right away.
+  bool fresh = false;
+  if (fetcher && tile <= last_tile) {
+    const int page_key = tile * kSplitKeys + slot * page_tokens;
+    fresh = pos >= page_key && pos < page_key + page_tokens;
+    if (!fresh) tma_load_2d(dst, &map_cache, half * kTmaColumns, box_row_of(tile, page), &barriers[which]);
+  }
+  chain_wait();
+  if (fresh) tma_load_2d(dst, &map_cache, half * kTmaColumns, box_row_of(tile, page), &barriers[which]);
+
+  // ---- the query heads of this key/value head as rows 0..group-1 of the 16-row operand
+  uint32_t qa0[HD / 16], qa2[HD / 16];
+  {
+    // q is written by the kernel ahead of this one
+    const __nv_bfloat16* qrow = behind_wait(q) + (static_cast<size_t>(token) * heads + kv * group + (g < group ? g : 0)) * HD;
+#pragma unroll
+    for (int ks = 0; ks < HD / 16; ++ks) {
+      qa0[ks] = g < group ? *reinterpret_cast<const uint32_t*>(qrow + ks * 16 + 2 * t) : 0u;
+      qa2[ks] = g < group ? *reinterpret_cast<const uint32_t*>(qrow + ks * 16 + 8 + 2 * t) : 0u;
+    }
+  }
+  const float scale_log2 = scale * 1.4426950408889634f;
+  const int key_base = warp * 32;
+  float m_run = -INFINITY, l_run = 0.0f;   // of this warp's keys of all tiles so far, row g
+  float o[HD / 8][4];
+#pragma unroll
+  for (int i = 0; i < HD / 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.0f;
+
+  if (tile > last_tile) return;   // more slots than tiles: the merge skips this one
+  for (uint32_t turn = 0; tile <= last_tile; tile += slots, ++turn) {
+    const uint32_t parity = turn & 1;
+    const int next = tile + slots;
+    int next_page = 0;   // asked for now, needed when this tile's keys are used up
+    if (fetcher && next <= last_tile && next * pages + slot < max_pages) next_page = table[next * pages + slot];
+    const int key0 = tile * kSplitKeys;
+    const int lo = max(first_key - key0, 0), hi = min(pos - key0, kSplitKeys - 1);   // the tile's rows that count
+    const bool has_keys = key_base <= hi && key_base + 31 >= lo;
+    const bool keys_landed = barrier_wait(&barriers[0], parity, status);
+
+    // ---- scores of this warp's 32 keys
+    float sc[4][4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) sc[i][0] = sc[i][1] = sc[i][2] = sc[i][3] = 0.0f;
+    if (has_keys) {
+#pragma unroll
+      for (int ks = 0; ks < HD / 16; ++ks) {
+#pragma unroll
+        for (int nb = 0; nb < 2; ++nb) {
+          uint32_t kf[4];
+          const int krow = key_base + nb * 16 + (lane & 7) + (lane >> 4) * 8;
+          decode_ldmatrix_x4(kf, decode_smem_address(sK + decode_swizzled_offset<HD>(krow, ks * 2 + ((lane >> 3) & 1))));
+          decode_mma(sc[2 * nb], qa0[ks], qa2[ks], kf[0], kf[1]);
+          decode_mma(sc[2 * nb + 1], qa0[ks], qa2[ks], kf[2], kf[3]);
+        }
+      }
+    }
+    // Row g of the tile is query head g; this thread holds keys nb * 8 + 2t, 2t + 1.
+    float m_t = -INFINITY;
+#pragma unroll
+    for (int nb = 0; nb < 4; ++nb) {
+#pragma unroll
+      for (int j = 0; j < 2; ++j) {
+        const int kk = key_base + nb * 8 + 2 * t + j;
+        sc[nb][j] = kk >= lo && kk <= hi ? sc[nb][j] * scale_log2 : -INFINITY;
+        m_t = fmaxf(m_t, sc[nb][j]);
+      }
+    }
+    m_t = fmaxf(m_t, __shfl_xor_sync(0xffffffffu, m_t, 1));
+    m_t = fmaxf(m_t, __shfl_xor_sync(0xffffffffu, m_t, 2));
+    const float m_new = fmaxf(m_run, m_t);
+    const float ref = m_new == -INFINITY ? 0.0f : m_new;
+    const float carry = decode_exp2(m_run - ref);   // what earlier tiles gathered, on the new maximum (0 if nothing yet)
+    float l_t = 0.0f;
+    uint32_t pa0[2], pa2[2];
+#pragma unroll
+    for (int nb = 0; nb < 4; ++nb) {
+      const float p0 = decode_exp2(sc[nb][0] - ref), p1 = decode_exp2(sc[nb][1] - ref);
+      l_t += p0 + p1;
+      __nv_bfloat162 packed = __floats2bfloat162_rn(p0, p1);
+      const uint32_t word = *reinterpret_cast<uint32_t*>(&packed);
+      if (nb & 1) pa2[nb >> 1] = word; else pa0[nb >> 1] = word;
+    }
+    l_t += __shfl_xor_sync(0xffffffffu, l_t, 1);
+    l_t += __shfl_xor_sync(0xffffffffu, l_t, 2);
+    l_run = l_run * carry + l_t;
+    m_run = m_new;
+
+    // Every warp is done with the keys: the next tile's may come. One
+    // decision for the whole block if a wait ran out (the status word says so).
+    if (__syncthreads_or(!keys_landed)) break;
+    if (next <= last_tile) {
+      if (tid == 0) barrier_arrive_expect(&barriers[0], TILE_BYTES);
+      if (fetcher && which == 0) tma_load_2d(dst, &map_cache, half * kTmaColumns, box_row_of(next, next_page), &barriers[0]);
+    }
+    const bool values_landed = barrier_wait(&barriers[1], parity, status);
+
+    // A masked key has weight 0, but 0 x NaN is NaN: value rows outside the
+    // token's keys (the rest of the last page, whatever an earlier owner of
+    // the page left there) are zeroed. A warp reads only its own 32 rows.
+    if (has_keys && (key_base < lo || key_base + 31 > hi)) {
+      for (int i = lane; i < 32 * (HD / 8); i += 32) {
+        const int vrow = key_base + i / (HD / 8);
+        if (vrow < lo || vrow > hi)
+          *reinterpret_cast<uint4*>(sV + decode_swizzled_offset<HD>(vrow, i % (HD / 8))) = make_uint4(0u, 0u, 0u, 0u);
+      }
+      __syncwarp();
+    }
+
+    // ---- o = o * carry + p v over this warp's 32 keys
+    if (turn > 0) {
+#pragma unroll
+      for (int i = 0; i < HD / 8; ++i) { o[i][0] *= carry; o[i][1] *= carry; }
+    }
+    if (has_keys) {
+#pragma unroll
+      for (int ks = 0; ks < 2; ++ks) {
+#pragma unroll
+        for (int nb = 0; nb < HD / 16; ++nb) {
+          uint32_t vf[4];
+          const int vrow = key_base + ks * 16 + (lane & 7) + ((lane >> 3) & 1) * 8;
+          decode_ldmatrix_x4_trans(vf, decode_smem_address(sV + decode_swizzled_offset<HD>(vrow, nb * 2 + (lane >> 4))));
+          decode_mma(o[2 * nb], pa0[ks], pa2[ks], vf[0], vf[1]);
+          decode_mma(o[2 * nb + 1], pa0[ks], pa2[ks], vf[2], vf[3]);
+        }
+      }
+    }
+    if (__syncthreads_or(!values_landed)) break;   // every warp is done with the values
+    if (next <= last_tile) {
+      if (tid == 0) barrier_arrive_expect(&barriers[1], TILE_BYTES);
+      if (fetcher && which == 1) tma_load_2d(dst, &map_cache, half * kTmaColumns, box_row_of(next, next_page), &barriers[1]);
+    }
+  }
+
+  // ---- the four warps in warp order: this block's partial result (the area lies over K, which is used up)
+  if (g < group) {
+    float* mine = s_merge + (warp * 8 + g) * (HD + 2);
+#pragma unroll
+    for (int i = 0; i < HD / 8; ++i) {
+      mine[i * 8 + 2 * t] = o[i][0];
+      mine[i * 8 + 2 * t + 1] = o[i][1];
+    }
+    if (t == 0) { mine[HD] = m_run; mine[HD + 1] = l_run; }
+  }
+  __syncthreads();
+  for (int i = tid; i < group * HD; i += kDecodeThreads) {
+    const int h = i / HD, d = i - h * HD;
+    float m_all = -INFINITY;
+#pragma unroll
+    for (int wp = 0; wp < 4; ++wp) m_all = fmaxf(m_all, s_merge[(wp * 8 + h) * (HD + 2) + HD]);
+    float sum = 0.0f, l_all = 0.0f;
+#pragma unroll
+    for (int wp = 0; wp < 4; ++wp) {
+      const float* theirs = s_merge + (wp * 8 + h) * (HD + 2);
+      const float weight = decode_exp2(theirs[HD] - m_all);  // a warp without keys has m = -inf: weight 0
+      sum += weight * theirs[d];
+      l_all += weight * theirs[HD + 1];
+    }
+    const int head = kv * group + h;
+    float* dst_partial = partial + ((static_cast<size_t>(row) * heads + head) * max_splits + rank) * (HD + 2);
+    dst_partial[d] = sum;
+    if (d == 0) { dst_partial[HD] = m_all * 0.6931471805599453f; dst_partial[HD + 1] = l_all; }  // the merge kernel works in natural units
+  }
+}
+
 // out[token, head, :] = sum_s exp(m_s - M) acc_s / sum_s exp(m_s - M) l_s over
 // the splits that hold keys of this token, in ascending order. One block per
 // (token, head), one thread per value of the head. A thread fetches the
@@ -674,7 +921,8 @@ template <typename T>
 __global__ void __launch_bounds__(256)
 paged_attention_merge_kernel(const float* __restrict__ partial, T* __restrict__ out,
                              const int* __restrict__ row_token, const int* __restrict__ positions,
-                             int rows, int heads, int head_dim, int max_splits, int window, int* status) {
+                             int rows, int heads, int head_dim, int max_splits, int window, int slots,
+                             int* status) {
   chain_release();
   const int row = blockIdx.x, head = blockIdx.y, d = threadIdx.x;
   const int token = row_token[row];  // the step's integers are not written by any kernel of the step
@@ -688,9 +936,11 @@ paged_attention_merge_kernel(const float* __restrict__ partial, T* __restrict__ 
     if (d == 0) atomicOr(status, kStatusBadSlot);
     return;
   }
-  const int splits = last_split - first_split + 1;
+  // One partial result per split of 128 keys, or (slots > 0) per block of the
+  // resident kernel: slot s gathered the tiles first + s, first + s + slots, ...
+  const int splits = slots > 0 ? min(slots, last_split - first_split + 1) : last_split - first_split + 1;
   const int stride = head_dim + 2;
-  const float* base = partial + ((static_cast<size_t>(row) * heads + head) * max_splits + first_split) * stride;
+  const float* base = partial + ((static_cast<size_t>(row) * heads + head) * max_splits + (slots > 0 ? 0 : first_split)) * stride;
   chain_wait();
   base = behind_wait(base);  // the partial results are written by the kernel ahead of this one
   float m = kDecodeMinusHuge, acc = 0.0f, l = 0.0f;
@@ -746,8 +996,11 @@ static int launch_decode(const void* q, const void* cache, void* out, float* par
   if (e != cudaSuccess) return static_cast<int>(e);
   return static_cast<int>(launch_chained(paged_attention_merge_kernel<T>, dim3(rows, heads), dim3(HD <= 64 ? 64 : (HD <= 128 ? 128 : 256)), 0,
                                          stream, static_cast<const float*>(partial), static_cast<T*>(out),
-                                         row_token, positions, rows, heads, HD, max_splits, window, status));
+                                         row_token, positions, rows, heads, HD, max_splits, window, 0, status));
 }
+
+static int decode_resident_blocks = 444;   // blocks of the decode attention that fit the GPU at once (3 an SM); 0: always one block per tile
+static int decode_many_blocks = 2048;      // blocks of a step with more (token, key/value head) pairs than that
 
 template <int HD>
 static int launch_decode_mma(const void* q, const void* cache, void* out, float* partial,
@@ -768,6 +1021,31 @@ static int launch_decode_mma(const void* q, const void* cache, void* out, float*
       (reinterpret_cast<uintptr_t>(cache) & 15) == 0 &&
       make_map(&map_cache, cache, static_cast<int>(cache_rows), HD, HD, page_tokens)) {
     const int shared = 2 * kSplitKeys * HD * 2 + 1024;   // keys and values, and room to align them to 1024 bytes
+    // A block that walks over several tiles keeps the copy engine busy
+    // without a new block's start-up per tile, so a pair of (token, key/value
+    // head) gets as few blocks as still fill the GPU: as many as keep the
+    // whole grid resident at once when the pairs are few, else a few rounds'
+    // worth. Where that would leave a block fewer than two tiles (few pairs,
+    // short contexts) one block per tile is as good and simpler.
+    const int pairs = rows * kv_heads;
+    int slots = 0;
+    if (decode_resident_blocks > 0 && pairs > 0) {
+      const int target = pairs <= decode_resident_blocks ? decode_resident_blocks : decode_many_blocks;
+      slots = target / pairs > 0 ? target / pairs : 1;
+    }
+    if (slots > 0 && 2 * slots <= max_splits) {
+      auto kernel = paged_attention_decode_resident_kernel<HD>;
+      cudaError_t attribute = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, shared);
+      if (attribute != cudaSuccess) return static_cast<int>(attribute);
+      e = launch_chained(kernel, dim3(slots, kv_heads, rows), dim3(kDecodeThreads), shared, stream, map_cache,
+                         static_cast<const __nv_bfloat16*>(q), partial, block_tables, max_pages, row_token, row_request,
+                         positions, heads, kv_heads, page_tokens, num_pages, max_splits, window, scale, status);
+      if (e != cudaSuccess) return static_cast<int>(e);
+      return static_cast<int>(launch_chained(paged_attention_merge_kernel<__nv_bfloat16>, dim3(rows, heads),
+                                             dim3(HD <= 64 ? 64 : (HD <= 128 ? 128 : 256)), 0, stream,
+                                             static_cast<const float*>(partial), static_cast<__nv_bfloat16*>(out),
+                                             row_token, positions, rows, heads, HD, max_splits, window, slots, status));
+    }
     auto kernel = paged_attention_decode_tma_kernel<HD>;
     cudaError_t attribute = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, shared);
     if (attribute != cudaSuccess) return static_cast<int>(attribute);
@@ -788,7 +1066,7 @@ static int launch_decode_mma(const void* q, const void* cache, void* out, float*
   return static_cast<int>(launch_chained(paged_attention_merge_kernel<__nv_bfloat16>, dim3(rows, heads),
                                          dim3(HD <= 64 ? 64 : (HD <= 128 ? 128 : 256)), 0, stream, static_cast<const float*>(partial),
                                          static_cast<__nv_bfloat16*>(out), row_token, positions, rows, heads,
-                                         HD, max_splits, window, status));
+                                         HD, max_splits, window, 0, status));
 }
 
 }  // namespace mxb
@@ -805,6 +1083,17 @@ MXB_API int mxb_paged_attention_decode_supported(int head_dim, int heads, int kv
 }
 
 MXB_API int mxb_paged_attention_split_keys() { return kSplitKeys; }
+
+// How many blocks of the bfloat16 decode attention the GPU holds at once (3
+// an SM with their 64 KB of keys and values), and how many blocks a step with
+// more (token, key/value head) pairs than that is cut into. 0: one block per
+// tile always.
+MXB_API int mxb_set_decode_resident_blocks(int blocks, int many) {
+  if (blocks < 0 || many < blocks) return static_cast<int>(cudaErrorInvalidValue);
+  decode_resident_blocks = blocks;
+  decode_many_blocks = many;
+  return 0;
+}
 
 // partial: float32 scratch of rows * heads * max_splits * (head_dim + 2) values.
 // rows of row_token that are negative are padding. max_splits must cover the

@@ -39,6 +39,7 @@ _SIGNATURES = {
                                    _F, _I, _P, _P],
     "mxb_paged_attention_decode_supported": [_I, _I, _I, _I],
     "mxb_paged_attention_split_keys": [],
+    "mxb_set_decode_resident_blocks": [_I, _I],
     "mxb_flash_prefill": [_P, _P, _P, _P, _I, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _F, _I, _P, _P],
     "mxb_flash_prefill_supported": [_I, _I, _I, _I],
     "mxb_flash_prefill_tile": [],
@@ -498,6 +499,17 @@ def decode_attention_supported(head_dim: int, heads: int, kv_heads: int, dtype: 
 
 def decode_split_keys() -> int:
     return _fn("mxb_paged_attention_split_keys")()
+
+
+def set_decode_resident_blocks(blocks: int, many: int = 2048) -> None:
+    """How many blocks of the bfloat16 decode attention the GPU holds at once
+    (444: three on each of 148 SMs), and into how many blocks a step with more
+    (token, key/value head) pairs than that is cut (2,048). A pair gets that
+    many blocks divided by the number of pairs, each walking over its 128-key
+    tiles; where a block would be left fewer than two tiles, and with
+    ``blocks`` 0, every tile has a block of its own. For comparisons and tests."""
+    _need(_fn("mxb_set_decode_resident_blocks")(int(blocks), int(many)) == 0,
+          "the number of resident blocks cannot be negative nor exceed that of a step with many pairs")
 
 
 def paged_attention_decode(q: torch.Tensor, cache: torch.Tensor, out: torch.Tensor,

@@ -450,6 +450,56 @@ def test_split_key_decode_attention(ops, dtype, heads, kv_heads, head_dim, page_
             assert np.abs(out[r] - ref).max() < tol(dtype, 5e-6, 2e-2), (window, r, total)
 
 
+@pytest.mark.parametrize("resident", [0, 444, 120, 12])
+@pytest.mark.parametrize("heads, kv_heads, head_dim, page_tokens", [(6, 2, 64, 8), (4, 2, 128, 16), (16, 2, 128, 128)])
+def test_decode_attention_with_blocks_that_walk_over_tiles(ops, resident, heads, kv_heads, head_dim, page_tokens):
+    """The bfloat16 kernel with one block per 128-key tile (0) and with as many
+    blocks per (token, key/value head) as keep the grid resident, each walking
+    over its tiles (18 blocks of one to two tiles, 5 blocks of up to seven, and
+    a step cut into more blocks than are resident):
+    the same attention. Lengths around the edges of tiles and of a block's
+    rounds; a far key that only one block sees; windows that move the first
+    tile."""
+    rng = np.random.default_rng(resident + heads)
+    totals = [1, 128, 129, 1024, 1025, 2047, 2049, 2176, 3000, 4097]
+    dtype = torch.bfloat16
+    q = [rounded(rng.normal(size=(1, heads, head_dim)), dtype) for n in totals]
+    k = [rounded(rng.normal(size=(n, kv_heads, head_dim)), dtype) for n in totals]
+    v = [rounded(rng.normal(size=(n, kv_heads, head_dim)), dtype) for n in totals]
+    far = {2176: 3, 3000: 2500, 4097: 1030}     # request length -> position of a key that takes all the weight
+    for r, total in enumerate(totals):
+        if total in far:
+            k[r][far[total], :, :] = 0.0
+            k[r][far[total], :, 5] = 24.0
+            q[r][0, :, :] = 0.0
+            q[r][0, :, 5] = 24.0
+    scale = head_dim ** -0.5
+    full_q = [np.concatenate([np.zeros((n - 1, heads, head_dim)), q[r]]) for r, n in enumerate(totals)]
+    try:
+        ops.set_decode_resident_blocks(resident, 48 if resident == 12 else 2048)   # 12: 24 pairs exceed it, 48 / 24 = 2 blocks each
+        for window in (0, 200, 1500):
+            out = run_decode_attention(ops, dtype, full_q, k, v, totals, page_tokens, scale, window=window, pad_rows=2)
+            for r, total in enumerate(totals):
+                first = max(0, total - window) if window else 0
+                ref = plain_last_row(q[r][0], k[r][first:], v[r][first:], scale)
+                assert np.abs(out[r] - ref).max() < 2e-2, (resident, window, total)
+                if total in far and (not window or far[total] >= first):
+                    assert np.abs(out[r] - v[r][far[total]].repeat(heads // kv_heads, axis=0)).max() < 1e-2
+    finally:
+        ops.set_decode_resident_blocks(444)
+
+
+def plain_last_row(q, k, v, scale):
+    """Attention of one query [heads, hd] over all of k, v [n, kv_heads, hd]."""
+    heads, group = q.shape[0], q.shape[0] // k.shape[1]
+    out = np.zeros_like(q)
+    for head in range(heads):
+        scores = (k[:, head // group, :] @ q[head]) * scale
+        weights = np.exp(scores - scores.max())
+        out[head] = (weights / weights.sum()) @ v[:, head // group, :]
+    return out
+
+
 def test_split_key_decode_bfloat16_head_dim_256_and_refusals(ops):
     rng = np.random.default_rng(21)
     totals = [300, 17]
