@@ -522,7 +522,9 @@ def workload(args):
     environment, prints how long each kernel of a layer holds the chain of one
     replayed step). ``prefill``: one prompt of ``--prompt-len`` tokens, three
     times (``--graphs``: then five replays, timed). ``gemm``: the tcgen05
-    product against the library's on one shape. ``attention``: the prompt
+    product against the library's on one shape. ``skinny``: the weight-streaming
+    kernels of a decode step on ``--m`` rows against a ``--n`` x ``--k`` weight
+    (``--swiglu``: with the activation). ``attention``: the prompt
     attention kernels alone on ``--prompt-len`` tokens behind ``--cached``
     keys. ``pick``: the samplers alone on ``--batch`` rows of logits."""
     import numpy as np
@@ -548,6 +550,40 @@ def workload(args):
             microseconds = event_time(function, 10) * 1e3
             print(f"{label}: {microseconds:.1f} us, {2 * args.m * args.n * args.k / microseconds / 1e6:.0f} TFLOP/s"
                   " (launch overhead included)")
+        ops.check_status("cuda")
+        return 0
+
+    if args.workload == "skinny":
+        # The products of a decode step (few rows of x, all of W read once):
+        # every kernel that takes the shape, over enough copies of W that none
+        # is still in L2 when its turn comes again.
+        ops.require_cuda()
+        peak, _ = peaks()
+        m, n, k = args.m, args.n, args.k
+        copies = max(2, int(300e6 // (n * k * 2)) + 1)
+        weights = [(torch.randn(n, k, device="cuda") * 0.05).bfloat16() for _ in range(copies)]
+        a = torch.randn(m, k, device="cuda").bfloat16()
+        kernels = [("stream", lambda w: ops.gemm_skinny(a, w, swiglu=args.swiglu, kernel="stream"),
+                    ops.gemm_stream_supported(a, weights[0], args.swiglu)),
+                   ("load", lambda w: ops.gemm_skinny(a, w, swiglu=args.swiglu, kernel="load"),
+                    ops.gemm_skinny_supported(a, weights[0])),
+                   ("library", (lambda w: ops.silu_mul(torch.mm(a, w.t()))) if args.swiglu else (lambda w: torch.mm(a, w.t())),
+                    True)]
+        for label, function, takes in kernels:
+            if not takes:
+                print(f"{label}: does not take [{m}, {k}] x [{n}, {k}]^T")
+                continue
+            for w in weights[:3]:
+                function(w)
+            torch.cuda.synchronize()
+            graph = torch.cuda.CUDAGraph()   # replayed: the launches from Python do not count
+            with torch.cuda.graph(graph):
+                for w in weights:
+                    function(w)
+            graph.replay()
+            microseconds = timed(torch, "cuda", lambda _: graph.replay(), 3) / 3 / copies * 1e3
+            rate = n * k * 2 / microseconds / 1e3
+            print(f"{label}: {microseconds:.2f} us, {rate:.0f} GB/s of W ({rate / peak['hbm_gbs'] * 100:.0f}% of the copy bandwidth)")
         ops.check_status("cuda")
         return 0
 
@@ -691,7 +727,7 @@ def main():
     parser.add_argument("--batches", default="1,8,32", help="32b: decode batch sizes")
     parser.add_argument("--context-32b", type=int, default=8192)
     # --workload
-    parser.add_argument("--workload", choices=("decode", "prefill", "gemm", "attention", "pick"))
+    parser.add_argument("--workload", choices=("decode", "prefill", "gemm", "skinny", "attention", "pick"))
     parser.add_argument("--graphs", action="store_true")
     parser.add_argument("--timeline", action="store_true")
     parser.add_argument("--m", type=int, default=2048)

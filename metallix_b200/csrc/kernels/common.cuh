@@ -119,11 +119,25 @@ template <typename T> __device__ __forceinline__ T* behind_wait(T* p) {
   return p;
 }
 
-bool chained_launches();  // whether launch_chained() asks for the overlap (csrc/kernels/embed_norm.cu)
+bool chained_launches();      // whether launch_chained() asks for the overlap (csrc/kernels/embed_norm.cu)
+unsigned chained_block_limit();            // ... for grids of up to this many blocks
+unsigned long long chained_byte_limit();   // ... and kernels that stream up to this many bytes
+
+// Whether a launch of `grid` that reads `bytes` (0: not known, small) asks for
+// the overlap. The overlap pays where a kernel is short: it hides the start-up
+// and lets weights be fetched ahead. A kernel that streams tens of megabytes
+// gains nothing from starting a few microseconds early, and a step made of
+// such kernels ran a third slower with the overlap than without (the layers
+// of an 8B- or 32B-shaped model at 1 to 8 rows), so those are launched the
+// ordinary way.
+inline bool chain_this(dim3 grid, unsigned long long bytes = 0) {
+  return chained_launches() && bytes <= chained_byte_limit() &&
+         static_cast<unsigned long long>(grid.x) * grid.y * grid.z <= chained_block_limit();
+}
 
 template <typename... KernelArgs, typename... Args>
-inline cudaError_t launch_chained(void (*kernel)(KernelArgs...), dim3 grid, dim3 block, size_t shared,
-                                  cudaStream_t stream, Args... args) {
+inline cudaError_t launch_chained_sized(unsigned long long bytes, void (*kernel)(KernelArgs...), dim3 grid, dim3 block,
+                                        size_t shared, cudaStream_t stream, Args... args) {
   cudaLaunchConfig_t config = {};
   config.gridDim = grid;
   config.blockDim = block;
@@ -133,8 +147,14 @@ inline cudaError_t launch_chained(void (*kernel)(KernelArgs...), dim3 grid, dim3
   attribute[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
   attribute[0].val.programmaticStreamSerializationAllowed = 1;
   config.attrs = attribute;
-  config.numAttrs = chained_launches() ? 1 : 0;
+  config.numAttrs = chain_this(grid, bytes) ? 1 : 0;
   return cudaLaunchKernelEx(&config, kernel, static_cast<KernelArgs>(args)...);
+}
+
+template <typename... KernelArgs, typename... Args>
+inline cudaError_t launch_chained(void (*kernel)(KernelArgs...), dim3 grid, dim3 block, size_t shared,
+                                  cudaStream_t stream, Args... args) {
+  return launch_chained_sized(0ull, kernel, grid, block, shared, stream, args...);
 }
 
 // The same for a kernel whose blocks run as clusters of `cluster_x` along x
@@ -156,7 +176,7 @@ inline cudaError_t launch_chained_clusters(void (*kernel)(KernelArgs...), dim3 g
   attribute[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
   attribute[1].val.programmaticStreamSerializationAllowed = 1;
   config.attrs = attribute;
-  config.numAttrs = chained_launches() ? 2 : 1;
+  config.numAttrs = chain_this(grid) ? 2 : 1;
   return cudaLaunchKernelEx(&config, kernel, static_cast<KernelArgs>(args)...);
 }
 

@@ -9,7 +9,11 @@
 namespace mxb {
 
 static bool g_chained_launches = false;
+static unsigned g_chained_block_limit = 0xffffffffu;
+static unsigned long long g_chained_byte_limit = 24ull << 20;
 bool chained_launches() { return g_chained_launches; }
+unsigned chained_block_limit() { return g_chained_block_limit; }
+unsigned long long chained_byte_limit() { return g_chained_byte_limit; }
 
 // out[t, :] = table[ids[t], :] as float32. A bad id sets the status word and
 // writes zeros.
@@ -230,5 +234,11 @@ MXB_API int mxb_add(float* x, const void* delta, int delta_dtype, long long coun
 // Turns the overlap of consecutive kernels (programmatic dependent launch) on
 // or off for every kernel of this library that supports it.
 MXB_API void mxb_set_chained_launches(int enabled) { mxb::g_chained_launches = enabled != 0; }
+// Grids of more blocks than `blocks`, and kernels that say they stream more
+// than `megabytes`, are launched without the overlap (0: no limit).
+MXB_API void mxb_set_chained_limits(unsigned blocks, unsigned megabytes) {
+  mxb::g_chained_block_limit = blocks == 0 ? 0xffffffffu : blocks;
+  mxb::g_chained_byte_limit = megabytes == 0 ? ~0ull : static_cast<unsigned long long>(megabytes) << 20;
+}
 
 MXB_TIMELINE_EXPORT(mxb_timeline_norms)

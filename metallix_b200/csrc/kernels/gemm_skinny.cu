@@ -187,7 +187,8 @@ static int launch_skinny(void* out, int out_dtype, const void* x, const void* w,
   // Narrow outputs take 8 rows of W per block so that at least ~2 blocks per SM exist.
   const bool narrow = columns <= 2048;
   dim3 grid((columns + (narrow ? 8 : 16) - 1) / (narrow ? 8 : 16));
-#define GO(TOUT, WROWS) return static_cast<int>(launch_chained(gemm_skinny_kernel<MB, SWIGLU, TOUT, WROWS>, grid, \
+  const unsigned long long streamed = static_cast<unsigned long long>(n) * k * 2;   // the bytes of W
+#define GO(TOUT, WROWS) return static_cast<int>(launch_chained_sized(streamed, gemm_skinny_kernel<MB, SWIGLU, TOUT, WROWS>, grid, \
       dim3(kSkinnyThreads), 0, stream, static_cast<TOUT*>(out), static_cast<const __nv_bfloat16*>(x), \
       static_cast<const __nv_bfloat16*>(w), m, n, k, ldx, ldw, ldo, inter))
   if (out_dtype == kBF16) { if (narrow) GO(__nv_bfloat16, 8); else GO(__nv_bfloat16, 16); }

@@ -181,7 +181,8 @@ static int launch_stream_rows(void* out, const void* x, const void* w, int m, in
     cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(shared));
     if (e != cudaSuccess) return static_cast<int>(e);
   }
-  return static_cast<int>(launch_chained(kernel, dim3((columns + R - 1) / R), dim3(kStreamThreads), shared, stream,
+  return static_cast<int>(launch_chained_sized(static_cast<unsigned long long>(n) * k * 2, kernel,
+                                               dim3((columns + R - 1) / R), dim3(kStreamThreads), shared, stream,
                                          static_cast<TOut*>(out), static_cast<const __nv_bfloat16*>(x),
                                          static_cast<const __nv_bfloat16*>(w), m, n, k, ldx, ldw, ldo, inter, status));
 }

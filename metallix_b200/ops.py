@@ -605,6 +605,9 @@ def gemm_stream_supported(a: torch.Tensor, w: torch.Tensor, swiglu: bool = False
                                                  n // 2 if swiglu else 0))
 
 
+STREAM_K = 3072   # beyond this k the load-based kernel reads W faster than whole rows by bulk copy
+
+
 def gemm_skinny_takes(a: torch.Tensor, w: torch.Tensor, swiglu: bool = False) -> bool:
     """Whether one of the two weight-streaming kernels takes the call."""
     return gemm_stream_supported(a, w, swiglu) or gemm_skinny_supported(a, w)
@@ -616,8 +619,11 @@ def gemm_skinny(a: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype = torch
     ``swiglu`` w holds gate rows then up rows and the result is
     silu(gate) * up, [m, n / 2]. ``kernel``: "stream" (rows of w by bulk copy
     into shared memory, m <= 16), "load" (16-byte loads into registers) or
-    "auto" (stream where it takes the shape and the output is not wider than
-    STREAM_COLUMNS)."""
+    "auto": stream where it takes the shape, the output is not wider than
+    STREAM_COLUMNS and k is at most STREAM_K (the layers of a small model,
+    where fetching W ahead of the wait for x is what counts; with the long
+    rows of a large model the loads read faster: 4.8 against 3.2 TB/s on
+    [8, 25600] x [5120, 25600])."""
     _need(a.is_cuda and w.is_cuda and a.shape[1] == w.shape[1], "operands do not fit a @ w.T on a CUDA device")
     _need(kernel in ("auto", "stream", "load"), f"unknown weight-streaming kernel {kernel!r}")
     streams = kernel != "load" and gemm_stream_supported(a, w, swiglu)
@@ -632,7 +638,8 @@ def gemm_skinny(a: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype = torch
     if out is None:
         out = torch.empty((m, columns), dtype=out_dtype, device=a.device)
     _need(out.shape == (m, columns) and out.dtype == out_dtype and out.stride(1) == 1, "out does not fit")
-    if streams and (kernel == "stream" or columns <= STREAM_COLUMNS or not gemm_skinny_supported(a, w)):
+    loads = gemm_skinny_supported(a, w)
+    if streams and (kernel == "stream" or not loads or (columns <= STREAM_COLUMNS and k <= STREAM_K)):
         _call("mxb_gemm_stream", out.data_ptr(), _CODES[out_dtype], a.data_ptr(), w.data_ptr(), m, n, k,
               a.stride(0), w.stride(0), out.stride(0), columns if swiglu else 0,
               status_word(a.device).data_ptr(), _stream())

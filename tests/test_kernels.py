@@ -620,8 +620,8 @@ def test_gemm_skinny(ops, m, n, k, kernel):
     # a row's result does not depend on how many other rows ride along
     alone = ops.gemm_skinny(a_d[m - 1:m].contiguous(), w_d, torch.float32, kernel=kernel)
     assert torch.equal(alone[0], out32[m - 1])
-    # what gemm_bf16 picks: the bulk-copy kernel where it takes the call, else the other
-    picked = "stream" if ops.gemm_stream_supported(a_d, w_d) else "load"
+    # what gemm_bf16 picks: the bulk-copy kernel where it takes the call and rows are short, else the other
+    picked = "stream" if ops.gemm_stream_supported(a_d, w_d) and (k <= ops.STREAM_K or k % 32) else "load"
     if kernel == picked and ops.gemm_skinny_supported(a_d, w_d):
         assert torch.equal(ops.gemm_bf16(a_d, w_d, torch.float32, backend="skinny"), out32)
         if m <= ops.SKINNY_ROWS:   # what "auto" picks for so few rows
