@@ -30,8 +30,14 @@ from .model import DecoderModel
 
 _DTYPES = {"bfloat16": torch.bfloat16, "bf16": torch.bfloat16, "float32": torch.float32,
            "fp32": torch.float32, torch.bfloat16: torch.bfloat16, torch.float32: torch.float32}
-STEP_GRAPHS = 8       # how many shapes of general steps keep a captured graph
+STEP_GRAPHS = 32      # how many shapes of general steps keep a captured graph
 STEP_GRAPH_TOKENS = 8192   # ... of steps up to this many tokens (a graph keeps its activations)
+# A graph saves the launches of a step (some 250 kernels from Python, a
+# millisecond or two of the host's time): worth it while the step itself is
+# short. Steps whose matrix products alone would take longer than this at the
+# rate below are launched kernel by kernel, which the device then hides.
+STEP_GRAPH_SECONDS = 5e-3
+DEVICE_FLOPS = 1.4e15      # a B200's sustained bfloat16 matrix rate
 CONTEXT_BUCKET = 2048  # a captured graph serves contexts up to a power of two times this many positions
 
 
@@ -113,6 +119,8 @@ class Engine:
         stateless = all(need is None or need.kind != "state" for need in self.cache.needs)
         self._step_graphs: Optional[Dict] = {} if self.graphs is not None and stateless else None
         self.replay_general_steps = True   # False: general steps are launched kernel by kernel (measurements)
+        values = self.model.weight_bytes() / torch.empty((), dtype=self.dtype).element_size()
+        self.step_graph_tokens = int(min(STEP_GRAPH_TOKENS, max(256, STEP_GRAPH_SECONDS * DEVICE_FLOPS / (2.0 * values))))
         self._shapes_seen: Dict = {}
         self._ids: Dict[Hashable, int] = {}   # request name -> manager id
         self._next_id = 1 << 40               # above any id a scheduler hands out
@@ -384,7 +392,7 @@ class Engine:
         # contexts inside the bucket are.
         bound = self.context_bucket(longest)
         shape_key = (tuple(counts), len(wanted), bound, tuple(p.graph_key for p in prepared.values()))
-        graphed = self._step_graphs is not None and self.replay_general_steps and total <= STEP_GRAPH_TOKENS and (
+        graphed = self._step_graphs is not None and self.replay_general_steps and total <= self.step_graph_tokens and (
             shape_key in self._step_graphs or self._shapes_seen.get(shape_key, 0) >= 1)
         if graphed:   # the parts' integers and bounds for every step of this shape
             plan = StepPlan(counts, starts, rows, bound, replayable=True)
@@ -458,12 +466,10 @@ class Engine:
         from .decode_graph import capture_quietly
         held = self._step_graphs.get(shape_key)
         if held is None:
+            # A step of this shape has run before, kernel by kernel: libraries
+            # and lazily loaded kernels have settled, the capture needs no
+            # warm-up run of its own.
             static = packed.to(self.device)
-            stream = torch.cuda.Stream(device=self.device)
-            stream.wait_stream(torch.cuda.current_stream(self.device))
-            with torch.cuda.stream(stream):
-                forward(static)   # libraries and lazily loaded kernels settle before the capture
-            torch.cuda.current_stream(self.device).wait_stream(stream)
             torch.cuda.synchronize(self.device)
             graph = torch.cuda.CUDAGraph()
             before = ops.launch_count()

@@ -665,7 +665,11 @@ def gemm_bf16(a: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype = torch.b
     _need(out_dtype in (torch.bfloat16, torch.float32), "out_dtype must be bfloat16 or float32")
     if backend == "simple":
         return gemm_simple(a, w, out_dtype=out_dtype, out=out)
-    if (backend == "skinny" or (backend == "auto" and a.shape[0] <= SKINNY_ROWS)) and gemm_skinny_takes(a, w):
+    # "auto": up to 16 rows; with the long rows of a large model up to 8 (beyond
+    # that the library reads them faster: 8B-shaped decode steps of 9 to 16
+    # requests took 5.6 ms, of 18 to 24 requests through the library 5.0)
+    few = SKINNY_ROWS if a.shape[1] <= STREAM_K else SKINNY_ROWS // 2
+    if (backend == "skinny" or (backend == "auto" and a.shape[0] <= few)) and gemm_skinny_takes(a, w):
         return gemm_skinny(a, w, out_dtype=out_dtype, out=out)
     _need(backend != "skinny", "the weight-streaming kernel does not take this shape")
     if backend == "tcgen05":

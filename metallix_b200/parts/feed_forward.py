@@ -30,7 +30,8 @@ class SwiGLU:
         self.intermediate_size = inter
 
     def forward(self, x: torch.Tensor, ctx: StepContext) -> torch.Tensor:
-        if (x.shape[0] <= ops.SKINNY_ROWS and self.gate_up.backend in ("auto", "skinny")
+        few = ops.SKINNY_ROWS if x.shape[1] <= ops.STREAM_K else ops.SKINNY_ROWS // 2   # as ops.gemm_bf16
+        if (x.shape[0] <= few and self.gate_up.backend in ("auto", "skinny")
                 and ops.gemm_skinny_takes(x, self.gate_up.weight, swiglu=True)):
             # A decode step: gate, up and the activation in one pass over the weights.
             return self.down.forward(ops.gemm_skinny(x, self.gate_up.weight, swiglu=True))
