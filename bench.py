@@ -263,6 +263,20 @@ def headline(args):
         other, _, _, _ = decode(batch)
         points[f"decode_b{batch}"] = batch * steps / other * 1e3
 
+    # The same decode step in an engine that allows the configuration's whole
+    # 40,960 positions (what `mxb gen` serves a model folder with): graphs are
+    # laid out for the contexts that are live, not for the limit.
+    if not args.no_points:
+        engine.release_all()
+        wide = Engine.from_random(config, seed=0, dtype="bfloat16", page_tokens=16, num_pages=args.batch * (-(-span // 16)) + 64,
+                                  max_requests=args.batch + 2, max_context=config.max_position_embeddings,
+                                  gemm_backend=args.gemm)
+        narrow, engine = engine, wide
+        other, _, _, _ = decode(args.batch)
+        points[f"decode_b{args.batch}_context_limit_{config.max_position_embeddings}"] = args.batch * steps / other * 1e3
+        engine = narrow
+        del wide
+
     # ------------------------------------------- end to end, the entry point
     engine.release_all()
     generator = Generator(engine, max_num_seqs=args.batch, max_tokens_per_step=4 * args.prompt_len)
