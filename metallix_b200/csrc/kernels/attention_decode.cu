@@ -19,6 +19,7 @@ namespace mxb {
 
 constexpr int kSplitKeys = 128;
 constexpr int kDecodeThreads = 128;
+constexpr unsigned kDecodeBlocksAtOnce = 444;   // blocks of the bfloat16 kernels a B200 holds at once: three an SM
 constexpr float kDecodeMinusHuge = -1.0e30f;
 
 template <typename T> struct Vec16;  // 16 bytes of T
@@ -476,7 +477,11 @@ paged_attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_cache,
   float* s_merge = reinterpret_cast<float*>(sK);  // [4 warps][8 heads][HD + 2], over K once the scores exist
   static_assert(4 * 8 * (HD + 2) * sizeof(float) <= TILE_BYTES, "the merge area must fit over the keys");
 
-  chain_release();
+  // A grid that is resident at once lets its successor start right away; one
+  // of several rounds only when a block is nearly done: a successor's blocks,
+  // resident and waiting, would take the places of this kernel's later rounds.
+  const bool release_late = gridDim.x * gridDim.y * gridDim.z > kDecodeBlocksAtOnce;
+  if (!release_late) chain_release();
   // What follows up to chain_wait() reads nothing a kernel of this step writes
   // (the step's integers and the pages of earlier positions), so it runs,
   // copies included, while the kernels before this one are still at work.
@@ -629,6 +634,7 @@ paged_attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_cache,
   }
   __syncthreads();  // every warp is done with K and V: the merge area lies over K
 
+  if (release_late) chain_release();
   // ---- merge the four warps in warp order
   if (g < group) {
     float* mine = s_merge + (warp * 8 + g) * (HD + 2);
@@ -691,7 +697,8 @@ paged_attention_decode_resident_kernel(const __grid_constant__ CUtensorMap map_c
   float* s_merge = reinterpret_cast<float*>(sK);           // [4 warps][8 heads][HD + 2], over K once the scores exist
   static_assert(4 * 8 * (HD + 2) * sizeof(float) <= TILE_BYTES, "the merge area must fit over the keys");
 
-  chain_release();
+  const bool release_late = gridDim.x * gridDim.y * gridDim.z > kDecodeBlocksAtOnce;   // as in the kernel above
+  if (!release_late) chain_release();
   // What follows up to chain_wait() reads nothing a kernel of this step writes.
   const int rank = blockIdx.x, slots = gridDim.x, kv = blockIdx.y, row = blockIdx.z;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -876,6 +883,7 @@ paged_attention_decode_resident_kernel(const __grid_constant__ CUtensorMap map_c
     }
   }
 
+  if (release_late) chain_release();
   // ---- the four warps in warp order: this block's partial result (the area lies over K, which is used up)
   if (g < group) {
     float* mine = s_merge + (warp * 8 + g) * (HD + 2);

@@ -79,7 +79,12 @@ gemm_skinny_kernel(TOut* __restrict__ out, const __nv_bfloat16* __restrict__ x,
   // they fetch up to 12 slices ahead (a k of 3072 is then wholly in flight).
   constexpr int PRE = MB <= 2 ? (WROWS == 8 && !SWIGLU ? 12 : 4) : 0;
   uint4 pre_lo[PRE > 0 ? PRE : 1][SETS], pre_hi[PRE > 0 ? PRE : 1][SETS];
-  chain_release();
+  // A small product lets its successor start at once (it fetches weights
+  // ahead); a large one only when this block is nearly done, so that the
+  // successor's blocks, resident and waiting, do not take the places that
+  // this kernel's later blocks need.
+  const bool release_late = static_cast<long long>(n) * k > (12ll << 20);
+  if (!release_late) chain_release();
 #pragma unroll
   for (int i = 0; i < PRE; ++i) {
     const int slice = warp + i * kSkinnyWarps;
@@ -134,6 +139,7 @@ gemm_skinny_kernel(TOut* __restrict__ out, const __nv_bfloat16* __restrict__ x,
         mma_16816(acc[s][j], a_lo[s].z, a_hi[s].z, a_lo[s].w, a_hi[s].w, b[j].z, b[j].w);
       }
   }
+  if (release_late) chain_release();
   // c0, c1: W row g, x rows 8j + 2t, 8j + 2t + 1; c2, c3: W row g + 8.
   constexpr int ITEMS = (WROWS * MB * 8 + kSkinnyThreads - 1) / kSkinnyThreads;
   float sums[SETS][ITEMS];
