@@ -6,7 +6,7 @@
     python bench.py --shape 32b                                   prefill and decode at 8,192-token contexts
     python bench.py --workload decode|prefill|gemm|attention|pick ...   small fixed workloads for profilers
 
-Default workload: the Qwen3-0.6B-shaped model of BASELINE.json (28 layers,
+Default workload: a Qwen3-0.6B-shaped model (28 layers,
 hidden 1024, 16 query and 8 key/value heads of 128, SwiGLU 3072, vocabulary
 151,936, tied head) with random weights in bfloat16, 8 requests that each hold
 a 2,048-token prompt in a cache laid out for 4,096-token contexts (pages of
@@ -49,7 +49,7 @@ def _qwen3(layers, hidden, heads, kv_heads, inter, tied):
                 max_position_embeddings=40960)
 
 
-# The shapes BASELINE.json names (configs 3, 4 and 5), as the config.json of each.
+# The three measured shapes, as the config.json of each.
 SHAPES = {"0.6b": ("Qwen3-0.6B-shaped", _qwen3(28, 1024, 16, 8, 3072, True)),
           "8b": ("Qwen3-8B-shaped", _qwen3(36, 4096, 32, 8, 12288, False)),
           "32b": ("Qwen3-32B-shaped", _qwen3(64, 5120, 64, 8, 25600, False))}
@@ -320,7 +320,7 @@ def headline(args):
 
 # ---------------------------------------------------- 8B: continuous batching
 def continuous_batching(args):
-    """BASELINE.json config 4: 64 requests with uniform-random prompt lengths
+    """Continuous batching at the 8B layer sizes: 64 requests with uniform-random prompt lengths
     128..2,048 and output lengths 64..512 through the scheduler (continuous
     batching, pages of 16, contexts up to 4,096), as the reference's batched
     decode throughput test and engine loop do
@@ -419,7 +419,7 @@ def continuous_batching(args):
 
 # ------------------------------------------- 32B: prefill and long-context decode
 def large_model(args):
-    """BASELINE.json config 5: prefill of a 2,048-token prompt, then decode at
+    """The 32B layer sizes: prefill of a 2,048-token prompt, then decode at
     batch 1, 8 and 32 with 8,192-token contexts. Weights (65.5 GB) and the
     cache of 32 such requests (68.7 GB) together come close to the device's
     memory: the pool is sized from what is free once the weights are resident."""
