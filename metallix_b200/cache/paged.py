@@ -107,6 +107,26 @@ class PagedCache:
     def pool_bytes(self) -> int:
         return sum(g.pool.numel() * g.pool.element_size() for g in self.groups if g.pool is not None)
 
+    # ------------------------------------------------------------------- fork
+    def fork(self, parent: int, child: int) -> None:
+        """``child`` starts from everything ``parent`` has computed: the manager
+        shares the full pages and names the partly filled ones and the state
+        slot, which are copied here, on the device, in every layer of a group at
+        once. Raises what the manager raises (no page, no slot) with nothing
+        changed."""
+        from .. import ops
+        source_slot, target_slot, copies = self.manager.fork(parent, child)
+        if self.device.type != "cuda":
+            return
+        for group in self.groups:
+            pairs = [(source, target) for g, source, target in copies if g == group.index]
+            if pairs and group.pool is not None:
+                ops.copy_units(group.pool, torch.tensor(pairs, dtype=torch.int32, device=self.device))
+        if self.states:
+            slots = torch.tensor([[source_slot, target_slot]], dtype=torch.int32, device=self.device)
+            for state in self.states.values():
+                ops.copy_units(state.unsqueeze(0), slots)
+
     # ------------------------------------------------------------- step views
     def zero_state(self, slot: int) -> None:
         for state in self.states.values():

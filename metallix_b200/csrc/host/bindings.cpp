@@ -47,6 +47,15 @@ PYBIND11_MODULE(_mxb_host, m) {
       .def("commit", &CacheManager::commit)
       .def("rollback", &CacheManager::rollback)
       .def("release", &CacheManager::release)
+      .def("fork",
+           [](CacheManager& manager, int64_t parent, int64_t child) {
+             CacheManager::Fork f = manager.fork(parent, child);
+             py::list copies;
+             for (const auto& c : f.copies) copies.append(py::make_tuple(c.group, c.source, c.target));
+             return py::make_tuple(f.source_slot, f.target_slot, copies);
+           },
+           "(source slot, target slot, [(group, source page, target page)]) the device has to copy")
+      .def("references", &CacheManager::references)
       .def("table", &CacheManager::table)
       .def("first_live_page", &CacheManager::first_live_page)
       .def("pages_handed_out", &CacheManager::pages_handed_out)

@@ -8,6 +8,14 @@
 // The protocol per step is the reference's (crates/core/engine/src/blocks.rs:17-45):
 // reserve (all or nothing) -> the forward pass writes -> commit.
 // Beside the pages every request holds one slot of fixed-size state.
+//
+// Pages are counted by reference, as the reference's blocks are
+// (manager.rs:614-628): fork() lets a new request start from everything
+// another has computed. The pages that are full are shared (a request only
+// ever writes at and beyond its own computed positions, so a full page is
+// never written again); the partly filled last page is copied for the child
+// (the reference's copy-on-write of a partial tail, manager.rs:749-763), which
+// the caller does on the device from the list fork() returns.
 #pragma once
 
 #include <algorithm>
@@ -47,13 +55,13 @@ class CacheManager {
       if (g.num_pages < 0) throw std::invalid_argument("num_pages must not be negative");
     }
     free_pages_.resize(groups_.size());
-    owner_.resize(groups_.size());
+    refs_.resize(groups_.size());
     ever_used_.resize(groups_.size());
     for (size_t g = 0; g < groups_.size(); ++g) {
       // Last-in first-out: the page given back last is handed out first, so a
       // small pool reuses pages at once.
       for (int p = groups_[g].num_pages - 1; p >= 0; --p) free_pages_[g].push_back(p);
-      owner_[g].assign(groups_[g].num_pages, kFree);
+      refs_[g].assign(groups_[g].num_pages, 0);
       ever_used_[g].assign(groups_[g].num_pages, false);
     }
     for (int s = max_requests_ - 1; s >= 0; --s) free_slots_.push_back(s);
@@ -127,14 +135,7 @@ class CacheManager {
         throw OutOfPages(static_cast<int>(g), need[g], free_pages(static_cast<int>(g)));
     for (size_t g = 0; g < groups_.size(); ++g) {
       for (int n = 0; n < need[g]; ++n) {
-        int page = free_pages_[g].back();
-        free_pages_[g].pop_back();
-        if (owner_[g][page] != kFree) throw std::logic_error("a free page has an owner");
-        owner_[g][page] = id;
-        if (ever_used_[g][page]) ++pages_reused_;
-        ever_used_[g][page] = true;
-        ++pages_handed_out_;
-        r.tables[g].push_back(page);
+        r.tables[g].push_back(take_page(static_cast<int>(g)));
       }
     }
     r.reserved += tokens;
@@ -156,7 +157,7 @@ class CacheManager {
       if (first_needed <= 0) continue;
       int64_t dead_pages = first_needed / cfg.page_tokens;  // pages wholly below
       for (int64_t p = r.first_live[g]; p < dead_pages && p < static_cast<int64_t>(r.tables[g].size()); ++p) {
-        give_back(static_cast<int>(g), r.tables[g][p], id);
+        give_back(static_cast<int>(g), r.tables[g][p]);
         r.tables[g][p] = -1;
       }
       if (dead_pages > r.first_live[g])
@@ -173,7 +174,7 @@ class CacheManager {
       while (static_cast<int64_t>(r.tables[g].size()) > keep) {
         int page = r.tables[g].back();
         r.tables[g].pop_back();
-        if (page >= 0) give_back(static_cast<int>(g), page, id);
+        if (page >= 0) give_back(static_cast<int>(g), page);
         shrank = true;
       }
     }
@@ -187,10 +188,64 @@ class CacheManager {
     Request& r = get(id);
     for (size_t g = 0; g < groups_.size(); ++g)
       for (auto it = r.tables[g].rbegin(); it != r.tables[g].rend(); ++it)
-        if (*it >= 0) give_back(static_cast<int>(g), *it, id);
+        if (*it >= 0) give_back(static_cast<int>(g), *it);
     free_slots_.push_back(r.slot);
     requests_.erase(id);
   }
+
+  // What the device has to copy after a fork: the partly filled last page of
+  // each group (`group`, from page `source` to page `target`) and the state slot.
+  struct PageCopy {
+    int group, source, target;
+  };
+  struct Fork {
+    int source_slot = -1, target_slot = -1;
+    std::vector<PageCopy> copies;
+  };
+
+  // A new request `child` that holds everything `parent` has computed: it
+  // shares the parent's full pages and gets a page of its own for the partly
+  // filled last one. All or nothing: throws OutOfPages (or for a lack of
+  // slots) and changes nothing. The parent must have no uncommitted positions.
+  Fork fork(int64_t parent, int64_t child) {
+    if (has(child)) throw std::invalid_argument("request " + std::to_string(child) + " is already live");
+    const Request& from = get(parent);
+    if (from.reserved != from.computed) throw std::invalid_argument("fork of a request with uncommitted positions");
+    if (free_slots_.empty()) throw std::runtime_error("no free request slot");
+    for (size_t g = 0; g < groups_.size(); ++g) {
+      const bool partial = from.computed % groups_[g].page_tokens != 0 && !from.tables[g].empty() &&
+                           from.tables[g].back() >= 0;
+      if (partial && free_pages(static_cast<int>(g)) < 1) throw OutOfPages(static_cast<int>(g), 1, 0);
+    }
+    Fork out;
+    Request r;
+    r.slot = free_slots_.back();
+    free_slots_.pop_back();
+    r.epoch = ++admissions_;
+    r.reserved = r.computed = from.computed;
+    r.first_live = from.first_live;
+    r.tables = from.tables;
+    out.source_slot = from.slot;
+    out.target_slot = r.slot;
+    for (size_t g = 0; g < groups_.size(); ++g) {
+      const int64_t full = from.computed / groups_[g].page_tokens;   // pages no one writes again
+      for (size_t p = 0; p < r.tables[g].size(); ++p) {
+        const int page = r.tables[g][p];
+        if (page < 0) continue;
+        if (static_cast<int64_t>(p) < full) {
+          ++refs_[g][page];
+        } else {
+          r.tables[g][p] = take_page(static_cast<int>(g));
+          out.copies.push_back({static_cast<int>(g), page, r.tables[g][p]});
+        }
+      }
+    }
+    requests_.emplace(child, std::move(r));
+    return out;
+  }
+
+  // How many requests hold a page (0: it is free).
+  int references(int g, int page) const { return refs_.at(g).at(page); }
 
   // Logical page -> physical page of one group, -1 where the window has
   // passed the page.
@@ -203,19 +258,20 @@ class CacheManager {
     return out;
   }
 
-  // Every page is free exactly once or held by exactly one request exactly
-  // once; every slot likewise (manager.rs:658-714 checks the same for blocks).
+  // Every page is free exactly once, or held by as many requests as its
+  // reference count says and not free; every slot is free or held exactly
+  // once (manager.rs:658-714 checks the same for blocks).
   void check_invariants() const {
     for (size_t g = 0; g < groups_.size(); ++g) {
-      std::vector<int> seen(groups_[g].num_pages, 0);
+      std::vector<int> free_count(groups_[g].num_pages, 0), held(groups_[g].num_pages, 0);
       for (int page : free_pages_[g]) {
         if (page < 0 || page >= groups_[g].num_pages) throw std::logic_error("free page out of range");
-        if (owner_[g][page] != kFree) throw std::logic_error("a free page has an owner");
-        if (++seen[page] > 1) throw std::logic_error("a page is free twice");
+        if (refs_[g][page] != 0) throw std::logic_error("a free page is still referred to");
+        if (++free_count[page] > 1) throw std::logic_error("a page is free twice");
       }
       for (const auto& kv : requests_) {
         const Request& r = kv.second;
-        int64_t live = 0;
+        std::vector<int> own(groups_[g].num_pages, 0);
         for (size_t p = 0; p < r.tables[g].size(); ++p) {
           int page = r.tables[g][p];
           if (page < 0) {
@@ -223,17 +279,21 @@ class CacheManager {
             continue;
           }
           if (page >= groups_[g].num_pages) throw std::logic_error("held page out of range");
-          if (owner_[g][page] != kv.first) throw std::logic_error("a held page names another owner");
-          if (++seen[page] > 1) throw std::logic_error("a page is held twice or held and free");
-          ++live;
+          if (++own[page] > 1) throw std::logic_error("a request holds a page twice");
+          if (free_count[page]) throw std::logic_error("a page is held and free");
+          ++held[page];
+          // a page that is shared lies wholly below what its holders have computed
+          if (refs_[g][page] > 1 && static_cast<int64_t>(p + 1) * groups_[g].page_tokens > r.computed)
+            throw std::logic_error("a shared page can still be written");
         }
         if (static_cast<int64_t>(r.tables[g].size()) != ceil_div(r.reserved, groups_[g].page_tokens))
           throw std::logic_error("table length does not match the reserved positions");
         if (r.computed > r.reserved) throw std::logic_error("computed beyond reserved");
-        (void)live;
       }
-      for (int page = 0; page < groups_[g].num_pages; ++page)
-        if (seen[page] != 1) throw std::logic_error("a page is lost");
+      for (int page = 0; page < groups_[g].num_pages; ++page) {
+        if (held[page] != refs_[g][page]) throw std::logic_error("a page's reference count is off");
+        if (held[page] == 0 && free_count[page] != 1) throw std::logic_error("a page is lost");
+      }
     }
     std::vector<int> slots(max_requests_, 0);
     for (int s : free_slots_) ++slots.at(s);
@@ -243,8 +303,6 @@ class CacheManager {
   }
 
  private:
-  static constexpr int64_t kFree = INT64_MIN;
-
   struct Request {
     int slot = -1;
     uint64_t epoch = 0;
@@ -267,16 +325,27 @@ class CacheManager {
     return it->second;
   }
 
-  void give_back(int g, int page, int64_t id) {
-    if (owner_[g][page] != id) throw std::logic_error("a page is freed by a request that does not hold it");
-    owner_[g][page] = kFree;
-    free_pages_[g].push_back(page);
+  int take_page(int g) {
+    int page = free_pages_[g].back();
+    free_pages_[g].pop_back();
+    if (refs_[g][page] != 0) throw std::logic_error("a free page is still referred to");
+    refs_[g][page] = 1;
+    if (ever_used_[g][page]) ++pages_reused_;
+    ever_used_[g][page] = true;
+    ++pages_handed_out_;
+    return page;
+  }
+
+  // One holder less; the page is free again when nobody holds it.
+  void give_back(int g, int page) {
+    if (refs_[g][page] <= 0) throw std::logic_error("a page is freed that nobody holds");
+    if (--refs_[g][page] == 0) free_pages_[g].push_back(page);
   }
 
   std::vector<GroupConfig> groups_;
   int max_requests_;
   std::vector<std::vector<int>> free_pages_;
-  std::vector<std::vector<int64_t>> owner_;
+  std::vector<std::vector<int>> refs_;   // [group][page] requests that hold the page
   std::vector<std::vector<bool>> ever_used_;
   std::vector<int> free_slots_;
   std::unordered_map<int64_t, Request> requests_;

@@ -164,6 +164,21 @@ class Engine:
         if request in self._ids:
             self.manager.release(self._ids.pop(request))
 
+    def fork(self, parent: Hashable, child: Hashable) -> None:
+        """A new request ``child`` that has ``parent``'s whole context in the
+        cache without computing it again: full pages are shared, the partly
+        filled last page and the state are copied on the device (the
+        reference's reference-counted blocks, crates/core/engine/src/manager.rs:614-628,
+        749-763). Both go on independently afterwards; either may end first."""
+        if parent not in self._ids:
+            raise KeyError(f"request {parent!r} is not live")
+        if child in self._ids:
+            raise ValueError(f"request {child!r} is already live")
+        rid = self._next_id
+        self.cache.fork(self._ids[parent], rid)
+        self._ids[child] = rid
+        self._next_id += 1
+
     def release_all(self) -> None:
         for request in list(self._ids):
             self.release(request)

@@ -31,6 +31,7 @@ _SIGNATURES = {
     "mxb_rmsnorm": [_P, _I, _P, _I, _P, _P, _I, _I, _F, _P],
     "mxb_add_rmsnorm": [_P, _P, _I, _P, _I, _P, _I, _I, _F, _P],
     "mxb_add": [_P, _P, _I, _L, _P],
+    "mxb_copy_units": [_P, _I, _I, _L, _P, _I, _P, _P],
     "mxb_qk_norm_rope_cache": [_P, _P, _P, _L, _L, _L, _P, _P, _P, _P, _P, _P, _P, _P,
                                _I, _I, _I, _I, _I, _I, _I, _I, _F, _I, _P, _P],
     "mxb_paged_attention_tile": [_P, _P, _P, _P, _I, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I,
@@ -290,6 +291,22 @@ def add_(x: torch.Tensor, delta: torch.Tensor) -> torch.Tensor:
     _need(delta.shape == x.shape, "delta and x differ in shape")
     _call("mxb_add", x.data_ptr(), delta.data_ptr(), _CODES[delta.dtype], x.numel(), _stream())
     return x
+
+
+# ------------------------------------------------------- copies in the cache
+def copy_units(pool: torch.Tensor, pairs: torch.Tensor) -> None:
+    """pool[:, target] = pool[:, source] for every (source, target) row of
+    ``pairs`` (int32 ``[count, 2]`` on the device); ``pool`` is contiguous
+    ``[entries, units, ...]``: the pages of a group's layers, or (with a leading
+    dimension of one) the slots of a state tensor. No target may be another
+    pair's source."""
+    _need(pool.is_cuda and pool.is_contiguous() and pool.dim() >= 2, "pool must be a contiguous device tensor")
+    _need(pairs.is_cuda and pairs.dtype == torch.int32 and pairs.dim() == 2 and pairs.shape[1] == 2
+          and pairs.is_contiguous(), "pairs must be int32 [count, 2] on the device")
+    entries, units = pool.shape[0], pool.shape[1]
+    unit_bytes = pool[0, 0].numel() * pool.element_size()
+    _call("mxb_copy_units", pool.data_ptr(), entries, units, unit_bytes, pairs.data_ptr(), pairs.shape[0],
+          status_word(pool.device).data_ptr(), _stream())
 
 
 # ------------------------------------------------- q/k norm, rotation, cache

@@ -1,6 +1,7 @@
 """The cache manager (no GPU): no page lost, held twice or freed twice under
 random orders of requests; windows give pages back; pages are used again;
-refusals change nothing. After the reference's random-operation model test
+refusals change nothing; forked requests share pages and never see each
+other's writes. After the reference's random-operation model test
 (crates/core/engine/src/blocks/tests.rs:329-892)."""
 import random
 
@@ -143,20 +144,107 @@ def test_groups_have_pages_of_their_own(host):
     assert (m.free_pages(0), m.free_pages(1)) == (6, 3)
 
 
-@pytest.mark.parametrize("seed", range(8))
+def test_fork_shares_full_pages_and_copies_the_partial_one(host):
+    m = make(host, pages=8, page_tokens=4)
+    m.admit(1)
+    m.reserve(1, 10)
+    with pytest.raises(ValueError, match="uncommitted"):
+        m.fork(1, 2)
+    m.commit(1, 10)
+    parent = m.table(1, 0)
+    source_slot, target_slot, copies = m.fork(1, 2)
+    child = m.table(2, 0)
+    assert (source_slot, target_slot) == (m.slot(1), m.slot(2)) and source_slot != target_slot
+    assert child[:2] == parent[:2] and child[2] != parent[2] and copies == [(0, parent[2], child[2])]
+    assert [m.references(0, p) for p in parent] == [2, 2, 1] and m.references(0, child[2]) == 1
+    assert m.computed(2) == m.reserved(2) == 10 and m.free_pages(0) == 4
+    m.check_invariants()
+    with pytest.raises(ValueError, match="already live"):
+        m.fork(1, 2)
+    m.release(1)                       # the shared pages stay with the child
+    assert m.free_pages(0) == 5 and [m.references(0, p) for p in child] == [1, 1, 1]
+    m.check_invariants()
+    m.reserve(2, 7)
+    m.commit(2, 7)
+    m.release(2)
+    assert m.free_pages(0) == 8
+    m.check_invariants()
+
+
+def test_fork_at_a_page_edge_copies_nothing_and_a_refused_fork_changes_nothing(host):
+    m = make(host, pages=3, page_tokens=4, requests=3)
+    m.admit(1)
+    m.reserve(1, 8)
+    m.commit(1, 8)
+    assert m.fork(1, 2)[2] == [] and m.table(2, 0) == m.table(1, 0) and m.free_pages(0) == 1
+    m.reserve(1, 2)
+    m.commit(1, 2)                      # the parent takes the last page: a partial one
+    with pytest.raises(RuntimeError, match="out of cache pages"):
+        m.fork(1, 3)
+    assert not m.has(3) and m.free_slots() == 1 and m.free_pages(0) == 0
+    m.check_invariants()
+    m.release(2)
+    assert m.free_pages(0) == 0         # both pages are still the parent's
+    m.release(1)
+    assert m.free_pages(0) == 3
+    m.check_invariants()
+
+
+def test_fork_under_a_window_shares_only_live_pages(host):
+    m = make(host, pages=8, page_tokens=4, window=6)
+    m.admit(1)
+    for _ in range(5):
+        m.reserve(1, 3)
+        m.commit(1, 3)                  # 15 positions: pages 0 and 1 are behind the window
+    parent = m.table(1, 0)
+    assert parent[:2] == [-1, -1]
+    _, _, copies = m.fork(1, 2)
+    child = m.table(2, 0)
+    assert child[:3] == parent[:3] and copies == [(0, parent[3], child[3])]
+    m.reserve(2, 8)
+    m.commit(2, 8)                      # the child's window passes the shared page
+    assert m.table(2, 0)[2] == -1 and m.references(0, parent[2]) == 1
+    m.check_invariants()
+    m.release(1)
+    m.release(2)
+    assert m.free_pages(0) == 8
+
+
+@pytest.mark.parametrize("seed", range(12))
 def test_random_orders(host, seed):
+    """Random admissions, reservations, commits, rollbacks, forks and releases
+    against a shadow: what each request wrote at each position (a number of its
+    own) must still be what its table leads to, whoever else shares the page."""
     rng = random.Random(seed)
     windows = [0, rng.choice([0, 3, 7, 16])]
     groups = [host.GroupConfig(rng.choice([1, 2, 4, 8]), w, rng.randint(6, 24)) for w in windows]
     page_tokens = [g.page_tokens for g in groups]
     m = host.CacheManager(groups, 5)
-    shadow = {}  # id -> [reserved, computed]
-    next_id = 0
-    for _ in range(600):
+    shadow = {}   # id -> [reserved, computed]
+    wrote = {}    # id -> the value at each position of the request
+    pages = [dict(), dict()]   # group -> (page, offset) -> value: the device memory
+    next_id, stamp = 0, 0
+    for _ in range(700):
         action = rng.random()
-        if action < 0.2 and m.free_slots() > 0:
+        if action < 0.15 and m.free_slots() > 0:
             m.admit(next_id)
-            shadow[next_id] = [0, 0]
+            shadow[next_id], wrote[next_id] = [0, 0], []
+            next_id += 1
+        elif action < 0.25 and shadow and m.free_slots() > 0:
+            parent = rng.choice(list(shadow))
+            if shadow[parent][0] != shadow[parent][1]:
+                continue
+            free = [m.free_pages(g) for g in range(2)]
+            try:
+                _, _, copies = m.fork(parent, next_id)
+            except RuntimeError:
+                assert free == [m.free_pages(g) for g in range(2)] and not m.has(next_id)
+                continue
+            for g, source, target in copies:
+                for offset in range(page_tokens[g]):
+                    if (source, offset) in pages[g]:
+                        pages[g][(target, offset)] = pages[g][(source, offset)]
+            shadow[next_id], wrote[next_id] = list(shadow[parent]), list(wrote[parent])
             next_id += 1
         elif action < 0.6 and shadow:
             rid = rng.choice(list(shadow))
@@ -165,6 +253,14 @@ def test_random_orders(host, seed):
                 continue
             if m.fits([(rid, count)]):
                 m.reserve(rid, count)
+                for position in range(shadow[rid][0], shadow[rid][0] + count):   # the step writes
+                    stamp += 1
+                    del wrote[rid][position:]
+                    wrote[rid].append(stamp)
+                    for g in range(2):
+                        page = m.table(rid, g)[position // page_tokens[g]]
+                        assert page >= 0 and m.references(g, page) == 1   # never into a shared page
+                        pages[g][(page, position % page_tokens[g])] = stamp
                 shadow[rid][0] += count
             else:
                 free = [m.free_pages(g) for g in range(2)]
@@ -184,24 +280,27 @@ def test_random_orders(host, seed):
         elif shadow:
             rid = rng.choice(list(shadow))
             m.release(rid)
-            del shadow[rid]
+            del shadow[rid], wrote[rid]
         m.check_invariants()
-        held = [0, 0]
+        held = [set(), set()]
         for rid, (reserved, computed) in shadow.items():
             assert (m.reserved(rid), m.computed(rid)) == (reserved, computed)
             for g in range(2):
                 table = m.table(rid, g)
                 assert len(table) == -(-reserved // page_tokens[g])
                 live = [p for p in table if p >= 0]
-                held[g] += len(live)
+                held[g].update(live)
+                first_needed = 0 if windows[g] == 0 else max(0, computed - windows[g] + 1)
                 if windows[g] == 0:
                     assert len(live) == len(table)
                 else:  # every position a later query can see is still held
-                    first_needed = max(0, computed - windows[g] + 1)
                     for page in range(first_needed // page_tokens[g], len(table)):
                         assert table[page] >= 0
+                for position in range(first_needed, computed):
+                    where = (table[position // page_tokens[g]], position % page_tokens[g])
+                    assert pages[g][where] == wrote[rid][position], (rid, g, position)
         for g in range(2):
-            assert held[g] + m.free_pages(g) == groups[g].num_pages
+            assert len(held[g]) + m.free_pages(g) == groups[g].num_pages
     for rid in list(shadow):
         m.release(rid)
     m.check_invariants()

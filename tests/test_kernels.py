@@ -827,3 +827,23 @@ def test_timeline_needs_a_build_of_its_own(ops):
     """The usual library records no timeline and says how to get one."""
     with pytest.raises(ops.KernelError, match="METALLIX_B200_TIMELINE"):
         ops.timeline()
+
+
+@pytest.mark.parametrize("shape,dtype", [((3, 9, 2, 2, 8, 16), torch.bfloat16),   # pages of three layers
+                                         ((1, 5, 7), torch.float32),             # state slots of 28 bytes
+                                         ((2, 6, 3), torch.int8)])               # units of no word size
+def test_copy_units(shape, dtype):
+    """pool[:, target] = pool[:, source] in every entry; other units untouched;
+    a unit outside the pool is reported, not copied."""
+    from metallix_b200 import ops
+    pool = (torch.randn(shape, device="cuda") * 50).to(dtype)
+    pairs = [(0, 3), (4, 1), (2, 2)]
+    expected = pool.clone()
+    for source, target in pairs:
+        expected[:, target] = pool[:, source]
+    ops.copy_units(pool, torch.tensor(pairs, dtype=torch.int32, device="cuda"))
+    assert torch.equal(pool, expected)
+    ops.copy_units(pool, torch.tensor([(0, shape[1])], dtype=torch.int32, device="cuda"))
+    assert torch.equal(pool, expected)
+    with pytest.raises(ops.KernelError, match="outside the page pool"):
+        ops.check_status(pool.device)

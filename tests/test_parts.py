@@ -251,6 +251,18 @@ def test_a_toy_mixer_with_state_of_its_own(model_folders):
         logits = engine.step([StepEntry("a", a[39:], [0]), StepEntry("c", c, [30])]).cpu().double().numpy()
         assert np.abs(logits[0] - reference["a"][39]).max() < 5e-5
         assert np.abs(logits[1] - reference["c"][30]).max() < 5e-5
+        # a fork takes the state with it: "e" goes on from "d"'s running sum
+        # with other tokens, while "d" goes on with its own
+        engine.release("a")
+        engine.release("c")
+        branch = a[:25] + c[:9]
+        expected = plain_with_running_mean(config, tensors, branch, 1, toy)
+        engine.step([StepEntry("d", a[:25], [])])
+        engine.fork("d", "e")
+        logits = engine.step([StepEntry("d", a[25:], list(range(15))),
+                              StepEntry("e", c[:9], list(range(9)))]).cpu().double().numpy()
+        assert np.abs(logits[:15] - reference["a"][25:]).max() < 5e-5
+        assert np.abs(logits[15:] - expected[25:]).max() < 5e-5
         engine.check()
     finally:
         unregister_part("mixer", "running_mean")

@@ -154,6 +154,59 @@ def test_equal_portions_replay_a_graph(model_folders, name, dtype):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name,prompt", [("B", 45), ("B", 48), ("D", 270)])
+def test_forked_requests_go_their_own_ways(model_folders, name, prompt, dtype):
+    """A request is forked after its prompt (in the middle of a page, or at a
+    page's edge); parent and child decode different tokens in the same steps;
+    the parent ends first and another request takes its pages while the child
+    goes on. Every logit matches the plain implementation of the whole
+    sequence; with so few pages that the freed ones are used again at once."""
+    from metallix_b200.engine import StepEntry
+    folder, config, tensors, page = model_folders[name]
+    vocab = config["vocab_size"]
+    shared = random_ids(5, prompt, vocab)
+    ways = {"parent": shared + random_ids(6, 20, vocab), "child": shared + random_ids(7, 40, vocab)}
+    other = random_ids(8, 2 * page + 3, vocab)
+    expected = {k: plain.forward_logits(config, tensors, ids) for k, ids in ways.items()}
+    expected["other"] = plain.forward_logits(config, tensors, other)
+    # just enough: the prompt's full pages once and each way's own pages while
+    # both live; later the child's whole context beside the newcomer's
+    up = lambda tokens: -(-tokens // page)
+    pages = max(up(prompt) + 2 * (up(prompt + 20) - prompt // page), up(prompt + 40) + up(len(other)))
+    engine = make_engine(model_folders, name, dtype, pages=pages)
+    limit, _ = bounds(dtype)
+    worst = 0.0
+
+    def compare(logits, pairs):
+        nonlocal worst
+        got = logits.cpu().double().numpy()
+        for row, (key, position) in enumerate(pairs):
+            worst = max(worst, float(np.abs(got[row] - expected[key][position]).max()))
+
+    compare(engine.step([StepEntry("parent", shared, [prompt - 1])]), [("parent", prompt - 1)])
+    before = engine.manager.free_pages(0)
+    engine.fork("parent", "child")
+    assert before - engine.manager.free_pages(0) == (1 if prompt % page else 0)   # only a partial page is copied
+    assert engine.context_length("child") == prompt
+    for position in range(prompt, prompt + 20):
+        compare(engine.step([StepEntry("parent", [ways["parent"][position]], [0]),
+                             StepEntry("child", [ways["child"][position]], [0])]),
+                [("parent", position), ("child", position)])
+    engine.release("parent")
+    compare(engine.step([StepEntry("child", [ways["child"][prompt + 20]], [0]),
+                         StepEntry("other", other, [len(other) - 1])]),
+            [("child", prompt + 20), ("other", len(other) - 1)])
+    assert engine.manager.pages_reused() > 0
+    for position in range(prompt + 21, prompt + 40):
+        compare(engine.step([StepEntry("child", [ways["child"][position]], [0])]), [("child", position)])
+    engine.check()
+    engine.release_all()
+    engine.manager.check_invariants()
+    assert engine.manager.free_pages(0) == pages
+    assert worst < limit
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_the_first_tokens_of_a_sequence(model_folders, dtype):
     """Position 0 alone, then 1, then 2: no earlier key, a single-token prompt."""
     from metallix_b200.engine import StepEntry
