@@ -979,6 +979,20 @@ paged_attention_merge_kernel(const float* __restrict__ partial, T* __restrict__ 
   out[(static_cast<size_t>(token) * heads + head) * head_dim + d] = from_float<T>(acc / l);
 }
 
+}  // namespace mxb
+#include "attention_decode_project.cuh"
+namespace mxb {
+
+// What follows the attention kernel of a decode step: the merge of the partial
+// results into `out`, or (project.w given) the kernel that merges and
+// multiplies by the output projection at once.
+struct DecodeProject {
+  const __nv_bfloat16* w = nullptr;  // W_o [hidden, heads * head_dim], rows ldw values apart
+  long long ldw = 0;
+  int hidden = 0, tokens = 0;
+  float* summands = nullptr;         // [heads, tokens, hidden]
+};
+
 template <typename T, int HD, int G>
 static int launch_decode(const void* q, const void* cache, void* out, float* partial,
                          const int* block_tables, int max_pages, const int* row_token,
@@ -1015,8 +1029,19 @@ static int launch_decode_mma(const void* q, const void* cache, void* out, float*
                              const int* block_tables, int max_pages, const int* row_token,
                              const int* row_request, const int* positions, int rows, int heads,
                              int kv_heads, int page_tokens, int num_pages, int max_splits, int window,
-                             float scale, int* status, cudaStream_t stream) {
+                             float scale, int* status, cudaStream_t stream, DecodeProject project = DecodeProject()) {
   static_assert(kSplitKeys == kDecodeThreads, "one thread per key row of a split");
+  auto finish = [&](int slots) -> int {
+    if (project.w != nullptr)
+      return static_cast<int>(launch_merge_project<HD>(partial, project.w, project.ldw, project.summands, row_token,
+                                                       positions, rows, project.tokens, heads, project.hidden,
+                                                       max_splits, window, slots, kSplitKeys, kDecodeMinusHuge, status,
+                                                       stream));
+    return static_cast<int>(launch_chained(paged_attention_merge_kernel<__nv_bfloat16>, dim3(rows, heads),
+                                           dim3(HD <= 64 ? 64 : (HD <= 128 ? 128 : 256)), 0, stream,
+                                           static_cast<const float*>(partial), static_cast<__nv_bfloat16*>(out),
+                                           row_token, positions, rows, heads, HD, max_splits, window, slots, status));
+  };
   static_assert(4 * 8 * (HD + 2) * sizeof(float) <= kSplitKeys * HD * 2, "the merge area must fit over the keys");
   dim3 grid(max_splits, kv_heads, rows);
   cudaError_t e;
@@ -1049,10 +1074,7 @@ static int launch_decode_mma(const void* q, const void* cache, void* out, float*
                          static_cast<const __nv_bfloat16*>(q), partial, block_tables, max_pages, row_token, row_request,
                          positions, heads, kv_heads, page_tokens, num_pages, max_splits, window, scale, status);
       if (e != cudaSuccess) return static_cast<int>(e);
-      return static_cast<int>(launch_chained(paged_attention_merge_kernel<__nv_bfloat16>, dim3(rows, heads),
-                                             dim3(HD <= 64 ? 64 : (HD <= 128 ? 128 : 256)), 0, stream,
-                                             static_cast<const float*>(partial), static_cast<__nv_bfloat16*>(out),
-                                             row_token, positions, rows, heads, HD, max_splits, window, slots, status));
+      return finish(slots);
     }
     auto kernel = paged_attention_decode_tma_kernel<HD>;
     cudaError_t attribute = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, shared);
@@ -1071,10 +1093,7 @@ static int launch_decode_mma(const void* q, const void* cache, void* out, float*
                        kv_heads, page_tokens, num_pages, max_splits, window, scale, status);
   }
   if (e != cudaSuccess) return static_cast<int>(e);
-  return static_cast<int>(launch_chained(paged_attention_merge_kernel<__nv_bfloat16>, dim3(rows, heads),
-                                         dim3(HD <= 64 ? 64 : (HD <= 128 ? 128 : 256)), 0, stream, static_cast<const float*>(partial),
-                                         static_cast<__nv_bfloat16*>(out), row_token, positions, rows, heads,
-                                         HD, max_splits, window, 0, status));
+  return finish(0);
 }
 
 }  // namespace mxb
@@ -1135,6 +1154,39 @@ MXB_API int mxb_paged_attention_decode(const void* q, const void* cache, void* o
 #undef BY_GROUP
 #undef ARGS
   return static_cast<int>(cudaErrorInvalidValue);
+}
+
+// Whether mxb_paged_attention_decode_project takes this shape.
+MXB_API int mxb_paged_attention_decode_project_supported(int head_dim, int heads, int kv_heads, int dtype, int tokens,
+                                                        const void* w, long long ldw) {
+  return dtype == kBF16 && mxb_paged_attention_decode_supported(head_dim, heads, kv_heads, dtype) &&
+                 decode_project_takes(head_dim, tokens, w, ldw) ? 1 : 0;
+}
+
+// The decode attention followed at once by the output projection (bfloat16):
+// summands[h, token, :] = (attention output of head h) * W_o[:, h * head_dim ...]^T
+// in float32, [heads, tokens, hidden]; their sum over h is the projected
+// output. Tokens that no row names give zeros. w: [hidden, heads * head_dim].
+MXB_API int mxb_paged_attention_decode_project(const void* q, const void* cache, float* partial,
+                                               const int* block_tables, int max_pages, const int* row_token,
+                                               const int* row_request, const int* positions, int rows, int tokens,
+                                               int heads, int kv_heads, int head_dim, int page_tokens, int num_pages,
+                                               int max_splits, int window, float scale, const void* w, long long ldw,
+                                               int hidden, float* summands, int* status, cudaStream_t stream) {
+  if (rows <= 0 || hidden <= 0 || max_splits <= 0) return static_cast<int>(cudaErrorInvalidValue);
+  if (!mxb_paged_attention_decode_project_supported(head_dim, heads, kv_heads, kBF16, tokens, w, ldw))
+    return static_cast<int>(cudaErrorInvalidValue);
+  DecodeProject project;
+  project.w = static_cast<const __nv_bfloat16*>(w);
+  project.ldw = ldw;
+  project.hidden = hidden;
+  project.tokens = tokens;
+  project.summands = summands;
+  void* out = nullptr;
+#define ARGS q, cache, out, partial, block_tables, max_pages, row_token, row_request, positions, rows, \
+             heads, kv_heads, page_tokens, num_pages, max_splits, window, scale, status, stream, project
+  return head_dim == 64 ? launch_decode_mma<64>(ARGS) : launch_decode_mma<128>(ARGS);
+#undef ARGS
 }
 
 // ---------------------------------------------------------------------------

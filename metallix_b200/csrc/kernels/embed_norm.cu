@@ -130,6 +130,79 @@ __global__ void add_rmsnorm_vec4_kernel(float* __restrict__ x, const TDelta* __r
   }
 }
 
+// x += summands[0] + summands[1] + ... (in that order), then the norm: the
+// summands are [parts, rows, size] float32, what a producer left that splits
+// its sum over k into parts (the output projection taken head by head).
+template <typename TOut, bool VEC4>
+__global__ void __launch_bounds__(256)   // what norm_threads() gives at most: room for a batch of loads in registers
+add_summands_rmsnorm_kernel(float* __restrict__ x, const float* __restrict__ summands, int parts,
+                                            size_t part_stride, TOut* __restrict__ y, const float* __restrict__ w,
+                                            int size, float eps) {
+  __shared__ float scratch[33];
+  chain_release();
+  constexpr int V = VEC4 ? 4 : 1;
+  constexpr int BATCH = 16;  // parts whose loads are on their way before the first of them is added
+  float* row = x + static_cast<size_t>(blockIdx.x) * size;
+  const int first = threadIdx.x * V;
+  // As in the kernel above: the thread's first values stay in registers
+  // between the passes, the norm weights come before the wait.
+  float4 held = make_float4(0.0f, 0.0f, 0.0f, 0.0f), held_gain = held;
+  if (VEC4 && first < size) held_gain = load4(w + first);
+  chain_wait();
+  row = behind_wait(row);      // both written by kernels ahead of this one
+  summands = behind_wait(summands) + static_cast<size_t>(blockIdx.x) * size;
+  float sum = 0.0f;
+  for (int i = first; i < size; i += blockDim.x * V) {
+    if (VEC4) {
+      // The adds wait for their loads in order: a loop of one load and one add
+      // would make a trip to memory per part.
+      float4 v = load4(row + i);
+      float4 d = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+      for (int part = 0; part < parts; part += BATCH) {
+        float4 more[BATCH];
+#pragma unroll
+        for (int j = 0; j < BATCH; ++j)
+          more[j] = load4(summands + min(part + j, parts - 1) * part_stride + i);   // no branch around a load
+#pragma unroll
+        for (int j = 0; j < BATCH; ++j) {
+          if (part + j < parts) {
+            d.x += more[j].x; d.y += more[j].y; d.z += more[j].z; d.w += more[j].w;
+          }
+        }
+      }
+      v.x += d.x; v.y += d.y; v.z += d.z; v.w += d.w;
+      store4(row + i, v);
+      if (i == first) held = v;
+      sum += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+    } else {
+      float d = 0.0f;
+      for (int part = 0; part < parts; part += BATCH) {
+        float more[BATCH];
+#pragma unroll
+        for (int j = 0; j < BATCH; ++j) more[j] = summands[min(part + j, parts - 1) * part_stride + i];
+#pragma unroll
+        for (int j = 0; j < BATCH; ++j)
+          if (part + j < parts) d += more[j];
+      }
+      const float v = row[i] + d;
+      row[i] = v;
+      sum += v * v;
+    }
+  }
+  sum = block_sum(sum, scratch);
+  const float scale = rsqrtf(sum / static_cast<float>(size) + eps);
+  TOut* dst = y + static_cast<size_t>(blockIdx.x) * size;
+  for (int i = first; i < size; i += blockDim.x * V) {
+    if (VEC4) {
+      const float4 v = i == first ? held : load4(row + i);
+      const float4 g = i == first ? held_gain : load4(w + i);
+      store4(dst + i, make_float4(v.x * scale * g.x, v.y * scale * g.y, v.z * scale * g.z, v.w * scale * g.w));
+    } else {
+      dst[i] = from_float<TOut>(row[i] * scale * w[i]);
+    }
+  }
+}
+
 static bool aligned16(const void* p) { return reinterpret_cast<uintptr_t>(p) % 16 == 0; }
 
 // x[r, :] += delta[r, :] alone (the last residual sum of a model).
@@ -217,6 +290,25 @@ MXB_API int mxb_add_rmsnorm(float* x, const void* delta, int delta_dtype, void* 
   else return static_cast<int>(cudaErrorInvalidValue);
 #undef LAUNCH
   return static_cast<int>(cudaGetLastError());
+}
+
+// x[r, :] += sum over parts of summands[part, r, :], y = RMSNorm(x) * w.
+MXB_API int mxb_add_summands_rmsnorm(float* x, const float* summands, int parts, void* y, int y_dtype,
+                                     const float* w, int rows, int size, float eps, cudaStream_t stream) {
+  if (rows <= 0) return 0;
+  if (parts <= 0 || size <= 0 || (y_dtype != kF32 && y_dtype != kBF16)) return static_cast<int>(cudaErrorInvalidValue);
+  const size_t part_stride = static_cast<size_t>(rows) * size;
+  const bool vec4 = size % 4 == 0 && aligned16(x) && aligned16(summands) && aligned16(w) &&
+                    (y_dtype == kF32 ? aligned16(y) : reinterpret_cast<uintptr_t>(y) % 8 == 0);
+  int threads = norm_threads(vec4 ? size / 4 : size);
+  if (vec4 && threads < 32) threads = 32;
+#define LAUNCH(TO, VEC) launch_chained(add_summands_rmsnorm_kernel<TO, VEC>, dim3(rows), dim3(threads), 0, stream, x, \
+                                       summands, parts, part_stride, static_cast<TO*>(y), w, size, eps)
+  cudaError_t e;
+  if (y_dtype == kF32) e = vec4 ? LAUNCH(float, true) : LAUNCH(float, false);
+  else e = vec4 ? LAUNCH(__nv_bfloat16, true) : LAUNCH(__nv_bfloat16, false);
+#undef LAUNCH
+  return static_cast<int>(e);
 }
 
 MXB_API int mxb_add(float* x, const void* delta, int delta_dtype, long long count,

@@ -30,6 +30,7 @@ _SIGNATURES = {
     "mxb_embed": [_P, _P, _I, _P, _I, _I, _I, _P, _P],
     "mxb_rmsnorm": [_P, _I, _P, _I, _P, _P, _I, _I, _F, _P],
     "mxb_add_rmsnorm": [_P, _P, _I, _P, _I, _P, _I, _I, _F, _P],
+    "mxb_add_summands_rmsnorm": [_P, _P, _I, _P, _I, _P, _I, _I, _F, _P],
     "mxb_add": [_P, _P, _I, _L, _P],
     "mxb_copy_units": [_P, _I, _I, _L, _P, _I, _P, _P],
     "mxb_qk_norm_rope_cache": [_P, _P, _P, _L, _L, _L, _P, _P, _P, _P, _P, _P, _P, _P,
@@ -39,6 +40,9 @@ _SIGNATURES = {
     "mxb_paged_attention_decode": [_P, _P, _P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I,
                                    _F, _I, _P, _P],
     "mxb_paged_attention_decode_supported": [_I, _I, _I, _I],
+    "mxb_paged_attention_decode_project_supported": [_I, _I, _I, _I, _I, _P, _L],
+    "mxb_paged_attention_decode_project": [_P, _P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _I,
+                                           _F, _P, _L, _I, _P, _P, _P],
     "mxb_paged_attention_split_keys": [],
     "mxb_set_decode_resident_blocks": [_I, _I],
     "mxb_flash_prefill": [_P, _P, _P, _P, _I, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _F, _I, _P, _P],
@@ -268,17 +272,25 @@ def rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float, out_dtype: torch.
 
 def add_rmsnorm(x: torch.Tensor, delta: torch.Tensor, weight: torch.Tensor, eps: float,
                 out_dtype: torch.dtype, out: Optional[torch.Tensor] = None) -> torch.Tensor:
-    """x += delta in float32 (in place), then returns RMSNorm(x) * w."""
+    """x += delta in float32 (in place), then returns RMSNorm(x) * w. A delta
+    of three dimensions, float32 ``[parts, rows, size]``, is a sum its producer
+    left in parts: they are added up in their order first."""
     _check(x, "x", (torch.float32,), 2)
-    _check(delta, "delta", tuple(_CODES), 2)
     _check(weight, "weight", (torch.float32,), 1)
-    _need(delta.shape == x.shape, "delta and x differ in shape")
     rows, size = x.shape
     _need(weight.numel() == size, "weight has the wrong size")
     if out is None:
         out = torch.empty((rows, size), dtype=out_dtype, device=x.device)
     _check(out, "out", (out_dtype,), 2)
     _need(out.shape == x.shape, "out has the wrong shape")
+    if delta.dim() == 3:
+        _check(delta, "delta", (torch.float32,), 3)
+        _need(delta.shape[1:] == x.shape and delta.shape[0] >= 1, "the summands and x differ in shape")
+        _call("mxb_add_summands_rmsnorm", x.data_ptr(), delta.data_ptr(), delta.shape[0], out.data_ptr(),
+              _CODES[out_dtype], weight.data_ptr(), rows, size, float(eps), _stream())
+        return out
+    _check(delta, "delta", tuple(_CODES), 2)
+    _need(delta.shape == x.shape, "delta and x differ in shape")
     _call("mxb_add_rmsnorm", x.data_ptr(), delta.data_ptr(), _CODES[delta.dtype], out.data_ptr(),
           _CODES[out_dtype], weight.data_ptr(), rows, size, float(eps), _stream())
     return out
@@ -566,6 +578,48 @@ def paged_attention_decode(q: torch.Tensor, cache: torch.Tensor, out: torch.Tens
           positions.data_ptr(), rows, heads, kv_heads, head_dim, page_tokens, num_pages, splits,
           int(window or 0), float(scale), _CODES[dtype], status_word(q.device).data_ptr(), _stream())
     return out
+
+
+def decode_project_supported(head_dim: int, heads: int, kv_heads: int, dtype: torch.dtype, tokens: int,
+                             weight: torch.Tensor) -> bool:
+    """Whether ``paged_attention_decode_project`` takes this shape."""
+    if dtype not in _CODES or weight.dtype != torch.bfloat16 or weight.dim() != 2 or weight.stride(1) != 1:
+        return False
+    return bool(_fn("mxb_paged_attention_decode_project_supported")(
+        head_dim, heads, kv_heads, _CODES[dtype], tokens, weight.data_ptr(), weight.stride(0)))
+
+
+def paged_attention_decode_project(q: torch.Tensor, cache: torch.Tensor, block_tables: torch.Tensor,
+                                   row_token: torch.Tensor, row_request: torch.Tensor, positions: torch.Tensor,
+                                   scale: float, longest_context: int, weight: torch.Tensor,
+                                   window: int = 0) -> torch.Tensor:
+    """``paged_attention_decode`` followed at once by the output projection
+    ``weight`` ``[hidden, heads * head_dim]``, for steps of up to 16 tokens in
+    bfloat16. Returns float32 ``[heads, tokens, hidden]``: the projection's sum
+    over k left in one summand per head, for ``add_rmsnorm`` to add up."""
+    _check(q, "q", (torch.bfloat16,), 3)
+    _check(cache, "cache", (torch.bfloat16,), 5)
+    tokens, heads, head_dim = q.shape
+    num_pages, two, kv_heads, page_tokens, cache_dim = cache.shape
+    _need(two == 2 and cache_dim == head_dim, "cache must be [pages, 2, kv_heads, page_tokens, head_dim]")
+    _need(weight.is_cuda and weight.dim() == 2 and weight.shape[1] == heads * head_dim, "weight does not fit the heads")
+    _need(decode_project_supported(head_dim, heads, kv_heads, q.dtype, tokens, weight),
+          f"the decode kernel with the projection does not take {tokens} tokens of {heads}/{kv_heads} heads of {head_dim}")
+    _check(block_tables, "block_tables", (torch.int32,), 2)
+    for name, tensor in (("row_token", row_token), ("row_request", row_request), ("positions", positions)):
+        _check(tensor, name, (torch.int32,), 1)
+    rows = row_token.numel()
+    _need(row_request.numel() == rows and positions.numel() == tokens, "row lists do not fit")
+    splits = max(1, -(-int(longest_context) // decode_split_keys()))
+    partial = torch.empty(rows * heads * splits * (head_dim + 2), dtype=torch.float32, device=q.device)
+    hidden = weight.shape[0]
+    summands = torch.empty((heads, tokens, hidden), dtype=torch.float32, device=q.device)
+    _call("mxb_paged_attention_decode_project", q.data_ptr(), cache.data_ptr(), partial.data_ptr(),
+          block_tables.data_ptr(), block_tables.shape[1], row_token.data_ptr(), row_request.data_ptr(),
+          positions.data_ptr(), rows, tokens, heads, kv_heads, head_dim, page_tokens, num_pages, splits,
+          int(window or 0), float(scale), weight.data_ptr(), weight.stride(0), hidden, summands.data_ptr(),
+          status_word(q.device).data_ptr(), _stream())
+    return summands
 
 
 # ------------------------------------------------------------ matrix products

@@ -161,6 +161,16 @@ class GQAttention:
         return tiles
 
     def forward(self, x: torch.Tensor, ctx: StepContext, cache: CacheView) -> torch.Tensor:
+        return self._attend(x, ctx, cache, summands=False)
+
+    def forward_summands(self, x: torch.Tensor, ctx: StepContext, cache: CacheView) -> torch.Tensor:
+        """``forward`` for a caller that adds up summands: where one kernel can
+        put the splits of a decode step together and project them head by head,
+        the result is float32 ``[heads, tokens, hidden]`` whose sum over the
+        heads is ``forward``'s output; otherwise ``forward``'s output itself."""
+        return self._attend(x, ctx, cache, summands=True)
+
+    def _attend(self, x: torch.Tensor, ctx: StepContext, cache: CacheView, summands: bool) -> torch.Tensor:
         tokens = x.shape[0]
         qkv = self.qkv.forward(x)
         q = qkv[:, :self.q_size]
@@ -192,10 +202,18 @@ class GQAttention:
                 q_heads = q.contiguous().view(tokens, self.num_heads, self.head_dim)
             if write:
                 ops.write_cache(k, v, cache.pool, cache.slots, ctx.positions)
-        out = torch.empty_like(q_heads)
         tiles = self._tiles(ctx)
         multi_tiles = tiles["multi_tiles"]
         split = tiles["decode_rows"] and self.split_decode
+        if (summands and split and multi_tiles == 0 and self.o.streams_few_rows(tokens)
+                and ops.decode_project_supported(self.head_dim, self.num_heads, self.num_kv_heads, self.dtype,
+                                                 tokens, self.o.weight)):
+            # Only single tokens, few of them: the splits are merged and
+            # projected by one kernel, one summand per head.
+            return ops.paged_attention_decode_project(
+                q_heads, cache.pool, cache.block_tables, tiles["decode_token"], tiles["decode_request"],
+                ctx.positions, self.scale, tiles["longest_context"], self.o.weight, self.window)
+        out = torch.empty_like(q_heads)
         if split:
             # Requests that bring one token: split along the keys.
             ops.paged_attention_decode(q_heads, cache.pool, out, cache.block_tables, tiles["decode_token"],

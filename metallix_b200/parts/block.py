@@ -27,6 +27,11 @@ class PreNormResidualBlock:
         self.feed_forward_norm = build_part("norm", layer.feed_forward_norm, weights, runtime)
         self.feed_forward = build_part("feed_forward", layer.feed_forward, weights, runtime)
         self.dtype = runtime.dtype
+        # A mixer may leave its output as summands [parts, tokens, hidden] when
+        # the norm that takes it next adds them up in its own pass over the row.
+        summands = getattr(self.mixer, "forward_summands", None)
+        self.mix = summands if summands is not None and getattr(self.feed_forward_norm, "adds_summands", False) \
+            else self.mixer.forward
 
     def parts(self):
         return [self.mixer_norm, self.mixer, self.feed_forward_norm, self.feed_forward]
@@ -37,7 +42,7 @@ class PreNormResidualBlock:
         layer's input; returns the feed-forward output, to be added by
         whoever runs next."""
         mixer_in = self.mixer_norm.add_forward(residual, pending, self.dtype)
-        mixed = self.mixer.forward(mixer_in, ctx, cache)
+        mixed = self.mix(mixer_in, ctx, cache)
         feed_in = self.feed_forward_norm.add_forward(residual, mixed, self.dtype)
         return self.feed_forward.forward(feed_in, ctx)
 

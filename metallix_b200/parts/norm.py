@@ -14,6 +14,7 @@ from .registry import Runtime, WeightStore, register_part
 
 class RMSNorm:
     kind = "rmsnorm"
+    adds_summands = True   # add_forward also takes [parts, rows, size]: a sum its producer left in parts
 
     def __init__(self, weight: torch.Tensor, eps: float, runtime: Runtime):
         self.weight = weight.to(device=runtime.device, dtype=torch.float32).contiguous()
@@ -26,7 +27,8 @@ class RMSNorm:
 
     def add_forward(self, residual: torch.Tensor, delta: Optional[torch.Tensor],
                     out_dtype: torch.dtype) -> torch.Tensor:
-        """residual += delta (float32, in place), then the norm of the sum."""
+        """residual += delta (float32, in place), then the norm of the sum.
+        ``delta`` may be float32 ``[parts, rows, size]``: its parts are added up first."""
         if delta is None:
             return ops.rmsnorm(residual, self.weight, self.eps, out_dtype)
         return ops.add_rmsnorm(residual, delta, self.weight, self.eps, out_dtype)

@@ -401,8 +401,11 @@ def test_flash_prefill_with_a_tile_s_keys_shared_out(ops, shares):
         ops.KEY_SHARES = None
 
 
-def run_decode_attention(ops, dtype, q, k, v, totals, page_tokens, scale, window=0, pad_rows=0, seed=0):
-    """One query (the last position) per request through the split-key kernel."""
+def run_decode_attention(ops, dtype, q, k, v, totals, page_tokens, scale, window=0, pad_rows=0, seed=0,
+                         project=None):
+    """One query (the last position) per request through the split-key kernel;
+    with ``project`` (a weight on the device) through the kernel that also
+    projects: the summands [heads, tokens, hidden] then."""
     heads, head_dim, kv_heads = q[0].shape[1], q[0].shape[2], k[0].shape[1]
     rng = np.random.default_rng(seed)
     pages_needed = [-(-total // page_tokens) for total in totals]
@@ -420,6 +423,13 @@ def run_decode_attention(ops, dtype, q, k, v, totals, page_tokens, scale, window
     q_all = dev(np.stack([q[r][total - 1] for r, total in enumerate(totals)]), dtype)
     out = torch.full_like(q_all, float("nan"))
     rows = list(range(len(totals))) + [-1] * pad_rows
+    if project is not None:
+        summands = ops.paged_attention_decode_project(
+            q_all, dev(host_cache, dtype), dev(tables, torch.int32), dev(rows, torch.int32),
+            dev([max(r, 0) for r in rows], torch.int32), dev([t - 1 for t in totals], torch.int32), scale,
+            max(totals) + 300, project, window)
+        ops.check_status("cuda")
+        return summands.cpu().double().numpy()
     ops.paged_attention_decode(q_all, dev(host_cache, dtype), out, dev(tables, torch.int32),
                                dev(rows, torch.int32), dev([max(r, 0) for r in rows], torch.int32),
                                dev([t - 1 for t in totals], torch.int32), scale, max(totals) + 300, window)
@@ -487,6 +497,76 @@ def test_decode_attention_with_blocks_that_walk_over_tiles(ops, resident, heads,
                     assert np.abs(out[r] - v[r][far[total]].repeat(heads // kv_heads, axis=0)).max() < 1e-2
     finally:
         ops.set_decode_resident_blocks(444)
+
+
+@pytest.mark.parametrize("resident", [0, 444, 12])
+@pytest.mark.parametrize("heads, kv_heads, head_dim, page_tokens, hidden, totals", [
+    (6, 2, 64, 8, 200, [1, 128, 129, 1025, 3000]),                 # a width that is no multiple of the 128 columns of a block
+    (4, 2, 128, 16, 384, [5, 2049, 700, 4097, 130, 2176, 64, 1, 999, 1024, 300, 4500, 77]),   # 13 tokens: two blocks of eight
+    (16, 8, 128, 32, 1024, [2048] * 8)])
+def test_decode_attention_with_the_output_projection(ops, resident, heads, kv_heads, head_dim, page_tokens, hidden,
+                                                     totals):
+    """The kernel that puts a decode step's splits together and projects them
+    head by head: summand h is (the attention output of head h, as the merge
+    kernel rounds it to bfloat16) times W_o's columns of that head, summed in
+    float32; tokens that no row names give zeros; with one block per tile and
+    with blocks that walk over tiles, with and without a window."""
+    rng = np.random.default_rng(resident + heads)
+    dtype = torch.bfloat16
+    q = [rounded(rng.normal(size=(1, heads, head_dim)), dtype) for n in totals]
+    k = [rounded(rng.normal(size=(n, kv_heads, head_dim)), dtype) for n in totals]
+    v = [rounded(rng.normal(size=(n, kv_heads, head_dim)), dtype) for n in totals]
+    full_q = [np.concatenate([np.zeros((n - 1, heads, head_dim)), q[r]]) for r, n in enumerate(totals)]
+    weight = rounded(rng.normal(size=(hidden, heads * head_dim)), dtype)
+    scale = head_dim ** -0.5
+    assert ops.decode_project_supported(head_dim, heads, kv_heads, dtype, len(totals), dev(weight, dtype))
+    try:
+        ops.set_decode_resident_blocks(resident, 48 if resident == 12 else 2048)
+        for window in (0, 1500):
+            out = run_decode_attention(ops, dtype, full_q, k, v, totals, page_tokens, scale, window=window, pad_rows=2)
+            summands = run_decode_attention(ops, dtype, full_q, k, v, totals, page_tokens, scale, window=window,
+                                            pad_rows=2, project=dev(weight, dtype))
+            assert summands.shape == (heads, len(totals), hidden)
+            for head in range(heads):
+                expected = out[:, head, :] @ weight[:, head * head_dim:(head + 1) * head_dim].T
+                assert np.abs(summands[head] - expected).max() < 2e-5 * np.abs(expected).max(), (window, head)
+    finally:
+        ops.set_decode_resident_blocks(444)
+
+
+def test_decode_projection_refusals_and_tokens_without_a_row(ops):
+    dtype = torch.bfloat16
+    weight = dev(np.ones((96, 256)), dtype)
+    assert not ops.decode_project_supported(128, 2, 1, dtype, 17, weight)          # more than 16 tokens
+    assert not ops.decode_project_supported(128, 2, 1, torch.float32, 4, weight)   # bfloat16 only
+    assert not ops.decode_project_supported(256, 1, 1, dtype, 4, weight)           # heads of 64 or 128 values
+    assert not ops.decode_project_supported(128, 2, 1, dtype, 4, weight[:, 4:])    # rows that no bulk copy can fetch
+    # three tokens, the middle one named by no row: its summands are zeros
+    q = torch.randn(3, 2, 128, device="cuda").to(dtype)
+    cache = torch.randn(4, 2, 1, 16, 128, device="cuda").to(dtype)
+    tables = dev([[0, 1], [2, 3], [1, 0]], torch.int32)
+    summands = ops.paged_attention_decode_project(q, cache, tables, dev([0, -1, 2], torch.int32),
+                                                  dev([0, 0, 2], torch.int32), dev([20, 0, 31], torch.int32), 0.1, 32,
+                                                  weight)
+    ops.check_status("cuda")
+    assert torch.all(summands[:, 1] == 0) and torch.all(summands[:, 0] != 0) and torch.all(summands[:, 2] != 0)
+
+
+@pytest.mark.parametrize("rows, size, parts", [(8, 1024, 16), (3, 200, 5), (5, 331, 3), (16, 96, 1)])
+@pytest.mark.parametrize("out_dtype", DTYPES)
+def test_add_rmsnorm_of_summands(ops, rows, size, parts, out_dtype):
+    """x += the sum of the parts, then the norm; widths with and without the
+    four-values-a-thread kernel."""
+    rng = np.random.default_rng(rows + size)
+    x = rng.normal(size=(rows, size))
+    summands = rng.normal(size=(parts, rows, size))
+    weight = 1 + 0.1 * rng.normal(size=size)
+    x_dev = dev(x, torch.float32)
+    out = ops.add_rmsnorm(x_dev, dev(summands, torch.float32), dev(weight, torch.float32), 1e-5, out_dtype)
+    total = x.astype(np.float32).astype(np.float64) + summands.astype(np.float32).astype(np.float64).sum(axis=0)
+    assert np.abs(x_dev.cpu().double().numpy() - total).max() < 1e-5
+    expected = plain.rms_norm(total, weight.astype(np.float32).astype(np.float64), 1e-5)
+    assert np.abs(out.cpu().double().numpy() - expected).max() < tol(out_dtype, 1e-5, 2e-2)
 
 
 def plain_last_row(q, k, v, scale):

@@ -131,6 +131,48 @@ def test_attention_part_with_its_cache(model_folders, dtype):
     assert np.abs(np.concatenate([other, both[20:]]) - ref[:12]).max() < limit
 
 
+def test_attention_part_leaves_summands_where_one_kernel_merges_and_projects(model_folders):
+    """A decode step of few single tokens in bfloat16: ``forward_summands``
+    gives [heads, tokens, hidden] in float32 whose sum is ``forward``'s output
+    and the whole-sequence attention; a step with a portion in it, or float32,
+    gives the plain output. The block adds the summands up in its norm."""
+    from metallix_b200.config import Qwen3Config
+    from metallix_b200.parts import CacheView, build_part
+    _, config, tensors, _ = model_folders["D"]     # heads of 64 values, three query heads a key/value head
+    spec = Qwen3Config.from_dict(config).to_model_spec().layers[1].mixer
+    rng = np.random.default_rng(5)
+    x = torch.tensor(rng.normal(size=(41, 128))).bfloat16()
+    ref = plain.attention_block(x.double().numpy(), np.arange(41), tensors, "model.layers.1.self_attn", config)
+    tables = torch.tensor([[5, 2, 9], [1, 4, 6]], dtype=torch.int32, device="cuda")
+    for dtype in (torch.bfloat16, torch.float32):
+        mixer = build_part("mixer", spec, store(tensors), runtime(dtype))
+        need = mixer.cache_need()
+        pool = torch.zeros(12, 2, 2, 16, 64, dtype=dtype, device="cuda")
+
+        def run(call, counts, starts, rows, xs):
+            where = [np.arange(s, s + c) for s, c in zip(starts, counts)]
+            slots = np.concatenate([tables[r].cpu().numpy()[w // 16] * 16 + w % 16 for r, w in zip(rows, where)])
+            view = CacheView(need=need, pool=pool, block_tables=tables[rows],
+                             slots=torch.tensor(slots, dtype=torch.int32, device="cuda"))
+            return call(torch.cat(xs).to(dtype).cuda(), context(dtype, counts, starts), view)
+
+        run(mixer.forward, [40], [0], [0], [x[:40]])
+        run(mixer.forward, [20], [0], [1], [x[:20]])
+        decode = ([1, 1], [40, 20], [0, 1], [x[40:41], x[20:21]])
+        plain_out = run(mixer.forward, *decode)
+        summed = run(mixer.forward_summands, *decode)
+        if dtype == torch.bfloat16:
+            assert summed.shape == (6, 2, 128) and summed.dtype == torch.float32
+            total = summed.sum(dim=0)
+        else:
+            assert summed.shape == (2, 128)
+            total = summed
+        assert np.abs(total.cpu().double().numpy() - plain_out.cpu().double().numpy()).max() < 2e-2
+        assert np.abs(total.cpu().double().numpy() - ref[[40, 20]]).max() < (3e-2 if dtype == torch.bfloat16 else 1e-5)
+        mixed = run(mixer.forward_summands, [3, 1], [37, 20], [0, 1], [x[37:40], x[20:21]])
+        assert mixed.shape == (4, 128)      # a portion beside the single token: the plain output
+
+
 def test_layer_order_is_data(model_folders):
     """A layer named twice (with a cache entry of its own for the second run)
     and a layer that reads the cache another layer wrote."""
