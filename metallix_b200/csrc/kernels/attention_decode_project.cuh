@@ -33,9 +33,10 @@ decode_merge_project_kernel(const float* __restrict__ partial, const __nv_bfloat
                             int max_splits, int window, int slots, int split_keys, float minus_huge, int* status) {
   constexpr int PITCH = HD * 2 + 16;  // bytes per row of a tile: rows a warp reads together fall on all banks
   constexpr int X_ROWS = MB * 8;
-  __shared__ __align__(128) unsigned char s_w[kProjectColumns * PITCH];
-  __shared__ __align__(16) unsigned char s_x[X_ROWS * PITCH];
-  __shared__ float s_out[X_ROWS][kProjectColumns + 1];
+  extern __shared__ __align__(128) unsigned char project_shared[];
+  unsigned char* s_w = project_shared;                                   // [128 columns][PITCH]
+  unsigned char* s_x = s_w + kProjectColumns * PITCH;                    // [X_ROWS][PITCH]
+  float (*s_out)[kProjectColumns + 1] = reinterpret_cast<float (*)[kProjectColumns + 1]>(s_x + X_ROWS * PITCH);
   __shared__ __align__(8) uint64_t barrier;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int head = blockIdx.y, n0 = blockIdx.x * kProjectColumns;
@@ -201,10 +202,12 @@ decode_merge_project_kernel(const float* __restrict__ partial, const __nv_bfloat
   }
 }
 
+constexpr int kProjectTokens = 64;  // the most tokens of a step the kernel takes
+
 // Whether the kernel takes this projection: bfloat16 heads of 64 or 128
-// values, up to 16 tokens, rows of W_o that the bulk copies can fetch.
+// values, up to 64 tokens, rows of W_o that the bulk copies can fetch.
 static bool decode_project_takes(int head_dim, int tokens, const void* w, long long ldw) {
-  return (head_dim == 64 || head_dim == 128) && tokens >= 1 && tokens <= 16 &&
+  return (head_dim == 64 || head_dim == 128) && tokens >= 1 && tokens <= kProjectTokens &&
          reinterpret_cast<uintptr_t>(w) % 16 == 0 && (ldw * 2) % 16 == 0;
 }
 
@@ -214,13 +217,23 @@ static cudaError_t launch_merge_project(const float* partial, const __nv_bfloat1
                                         int hidden, int max_splits, int window, int slots, int split_keys,
                                         float minus_huge, int* status, cudaStream_t stream) {
   const dim3 grid((hidden + kProjectColumns - 1) / kProjectColumns, heads);
-  if (tokens <= 8)
-    return launch_chained(decode_merge_project_kernel<HD, 1>, grid, dim3(kProjectThreads), 0, stream, partial, w, ldw,
-                          summands, row_token, positions, rows, tokens, heads, hidden, max_splits, window, slots,
-                          split_keys, minus_huge, status);
-  return launch_chained(decode_merge_project_kernel<HD, 2>, grid, dim3(kProjectThreads), 0, stream, partial, w, ldw,
-                        summands, row_token, positions, rows, tokens, heads, hidden, max_splits, window, slots,
-                        split_keys, minus_huge, status);
+#define GO(MB)                                                                                                       \
+  {                                                                                                                  \
+    auto kernel = decode_merge_project_kernel<HD, MB>;                                                               \
+    const int shared = (kProjectColumns + MB * 8) * (HD * 2 + 16) + MB * 8 * (kProjectColumns + 1) * 4;              \
+    if (shared > 48 * 1024) {                                                                                        \
+      cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, shared);             \
+      if (e != cudaSuccess) return e;                                                                                \
+    }                                                                                                                \
+    return launch_chained(kernel, grid, dim3(kProjectThreads), shared, stream, partial, w, ldw, summands, row_token,  \
+                          positions, rows, tokens, heads, hidden, max_splits, window, slots, split_keys, minus_huge,  \
+                          status);                                                                                   \
+  }
+  if (tokens <= 8) GO(1)
+  if (tokens <= 16) GO(2)
+  if (tokens <= 32) GO(4)
+  GO(8)
+#undef GO
 }
 
 }  // namespace mxb

@@ -594,7 +594,7 @@ def paged_attention_decode_project(q: torch.Tensor, cache: torch.Tensor, block_t
                                    scale: float, longest_context: int, weight: torch.Tensor,
                                    window: int = 0) -> torch.Tensor:
     """``paged_attention_decode`` followed at once by the output projection
-    ``weight`` ``[hidden, heads * head_dim]``, for steps of up to 16 tokens in
+    ``weight`` ``[hidden, heads * head_dim]``, for steps of up to 64 tokens in
     bfloat16. Returns float32 ``[heads, tokens, hidden]``: the projection's sum
     over k left in one summand per head, for ``add_rmsnorm`` to add up."""
     _check(q, "q", (torch.bfloat16,), 3)

@@ -27,6 +27,7 @@ from .registry import (CacheView, Prepared, Runtime, StepContext, StepPlan, Weig
 
 TILE_TOKENS = 16     # query tokens per tile of the general kernel (csrc/kernels/attention_tile.cu)
 WIDE_TOKENS = 128    # ... of the tensor-core prompt kernels (csrc/kernels/attention_prefill*.cu)
+PROJECT_TOKENS = 32  # decode steps of up to this many tokens merge their splits and project in one kernel
 LONG_CONTEXT = 2048  # a portion of a prompt that sees this many keys or more counts as behind a long context
 
 
@@ -205,11 +206,11 @@ class GQAttention:
         tiles = self._tiles(ctx)
         multi_tiles = tiles["multi_tiles"]
         split = tiles["decode_rows"] and self.split_decode
-        if (summands and split and multi_tiles == 0 and self.o.streams_few_rows(tokens)
+        if (summands and split and multi_tiles == 0 and tokens <= PROJECT_TOKENS and self.o.rows_are_short()
                 and ops.decode_project_supported(self.head_dim, self.num_heads, self.num_kv_heads, self.dtype,
                                                  tokens, self.o.weight)):
-            # Only single tokens, few of them: the splits are merged and
-            # projected by one kernel, one summand per head.
+            # Only single tokens, at most 64 of them: the splits are merged
+            # and projected by one kernel, one summand per head.
             return ops.paged_attention_decode_project(
                 q_heads, cache.pool, cache.block_tables, tiles["decode_token"], tiles["decode_request"],
                 ctx.positions, self.scale, tiles["longest_context"], self.o.weight, self.window)

@@ -38,12 +38,12 @@ class Linear:
             return ops.gemm_simple(x, self.weight, out_dtype=torch.float32, out=out)
         return ops.gemm_bf16(x, self.weight, out_dtype=out_dtype, backend=self.backend, out=out)
 
-    def streams_few_rows(self, rows: int) -> bool:
-        """Whether a product of that many rows is one of the short,
-        overlapped kernels of a decode step (few rows over a weight whose rows
-        are short), where a hand-over between kernels costs as much as the work."""
-        return (self.dtype == torch.bfloat16 and self.backend == "auto" and rows <= ops.SKINNY_ROWS
-                and self.in_features <= ops.STREAM_K)
+    def rows_are_short(self) -> bool:
+        """Whether this is a weight of the kind whose decode-step products are
+        short, overlapped kernels (rows of at most ``ops.STREAM_K`` values, the
+        kernel chosen by this library), where a hand-over between kernels costs
+        as much as the work."""
+        return self.dtype == torch.bfloat16 and self.backend == "auto" and self.in_features <= ops.STREAM_K
 
     def weight_bytes(self) -> int:
         return self.weight.numel() * self.weight.element_size()

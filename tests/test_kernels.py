@@ -503,7 +503,9 @@ def test_decode_attention_with_blocks_that_walk_over_tiles(ops, resident, heads,
 @pytest.mark.parametrize("heads, kv_heads, head_dim, page_tokens, hidden, totals", [
     (6, 2, 64, 8, 200, [1, 128, 129, 1025, 3000]),                 # a width that is no multiple of the 128 columns of a block
     (4, 2, 128, 16, 384, [5, 2049, 700, 4097, 130, 2176, 64, 1, 999, 1024, 300, 4500, 77]),   # 13 tokens: two blocks of eight
-    (16, 8, 128, 32, 1024, [2048] * 8)])
+    (16, 8, 128, 32, 1024, [2048] * 8),
+    (2, 1, 128, 16, 136, [300 + 7 * i for i in range(33)]),                   # 33 tokens: five blocks of eight
+    (6, 2, 64, 16, 72, [40 + 29 * i for i in range(64)])])                    # 64 tokens
 def test_decode_attention_with_the_output_projection(ops, resident, heads, kv_heads, head_dim, page_tokens, hidden,
                                                      totals):
     """The kernel that puts a decode step's splits together and projects them
@@ -537,7 +539,7 @@ def test_decode_attention_with_the_output_projection(ops, resident, heads, kv_he
 def test_decode_projection_refusals_and_tokens_without_a_row(ops):
     dtype = torch.bfloat16
     weight = dev(np.ones((96, 256)), dtype)
-    assert not ops.decode_project_supported(128, 2, 1, dtype, 17, weight)          # more than 16 tokens
+    assert not ops.decode_project_supported(128, 2, 1, dtype, 65, weight)          # more than 64 tokens
     assert not ops.decode_project_supported(128, 2, 1, torch.float32, 4, weight)   # bfloat16 only
     assert not ops.decode_project_supported(256, 1, 1, dtype, 4, weight)           # heads of 64 or 128 values
     assert not ops.decode_project_supported(128, 2, 1, dtype, 4, weight[:, 4:])    # rows that no bulk copy can fetch
