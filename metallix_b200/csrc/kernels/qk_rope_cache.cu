@@ -123,11 +123,14 @@ qk_norm_rope_cache_warp_kernel(
   // cos/sin tables, none of which a kernel of this step writes.
   const int lane = threadIdx.x & 31, sub = lane % LANES;
   const int per_token = heads + 2 * kv_heads;
-  const long long total = static_cast<long long>(tokens) * per_token;
-  const long long item = (static_cast<long long>(blockIdx.x) * 8 + (threadIdx.x >> 5)) * HEADS + lane / LANES;
+  // The launcher keeps tokens * per_token below 2^31: 32-bit division, which
+  // is a fraction of the instructions the 64-bit one takes.
+  const unsigned total = static_cast<unsigned>(tokens) * static_cast<unsigned>(per_token);
+  const unsigned item = (blockIdx.x * 8u + (threadIdx.x >> 5)) * HEADS + lane / LANES;
   // Lanes without work stay to the end: the sums below shuffle within a head's lanes.
   bool active = item < total;
-  const int t = active ? static_cast<int>(item / per_token) : 0, h = active ? static_cast<int>(item % per_token) : 0;
+  const int t = active ? static_cast<int>(item / static_cast<unsigned>(per_token)) : 0;
+  const int h = active ? static_cast<int>(item - static_cast<unsigned>(t) * static_cast<unsigned>(per_token)) : 0;
   const bool is_q = h < heads;
   const bool is_k = !is_q && h < heads + kv_heads;
   const int kv = is_q ? 0 : (is_k ? h - heads : h - heads - kv_heads);
@@ -202,6 +205,8 @@ qk_norm_rope_cache_warp_kernel(
     }
     active = false;
   }
+  // A warp whose heads are all values (or past the end) has nothing left to do.
+  if (__all_sync(0xffffffffu, !active)) return;
   float x[2 * V];
   float sum = 0.0f;
 #pragma unroll
@@ -261,6 +266,7 @@ MXB_API int mxb_qk_norm_rope_cache(
   if ((head_dim == 64 || head_dim == 128 || head_dim == 256) && (cos_table == nullptr || rotary_dim == head_dim) &&
       vector_ok && (dtype == kF32 || dtype == kBF16)) {
     const long long items = static_cast<long long>(tokens) * (heads + 2 * kv_heads);
+    if (items >= 0x7fffffffLL) return static_cast<int>(cudaErrorInvalidValue);
     const int heads_per_warp = 32 / (head_dim / 2 / (16 / element));
     const unsigned blocks = static_cast<unsigned>((items + 8 * heads_per_warp - 1) / (8 * heads_per_warp));
     cudaError_t launch_status = cudaSuccess;
