@@ -435,7 +435,7 @@ def large_model(args):
     config = parse_config(dict(raw, num_hidden_layers=args.layers or layers_of_config))
     context = args.context_32b
     batches = [int(b) for b in args.batches.split(",")]
-    span = context + warmup + repeats * steps + 16
+    span = context + len(batches) * (warmup + repeats * steps) + 16   # the first request decodes in every batch size
     started = time.perf_counter()
     engine = Engine.from_random(config, seed=0, dtype="bfloat16", page_tokens=16, max_requests=max(batches) + 2,
                                 max_context=-(-span // 256) * 256, gemm_backend=args.gemm,

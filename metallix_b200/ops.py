@@ -676,6 +676,13 @@ def gemm_stream_supported(a: torch.Tensor, w: torch.Tensor, swiglu: bool = False
                                                  n // 2 if swiglu else 0))
 
 
+# With rows of W longer than STREAM_K the load-based kernel is ahead of the
+# library up to this many columns (at 1 / 8 rows 3.2 / 3.1 against 2.5 / 2.7 TB/s
+# on 4,096 x 4,096, 4.1 / 3.9 against 3.1 / 3.3 on 4,096 x 12,288) and behind it
+# from 5,120 columns on (4.4 / 4.1 against 4.8 / 4.8 TB/s on 5,120 x 8,192, 5.2 /
+# 5.0 against 5.7 / 5.8 on 5,120 x 25,600, 4.3 / 4.1 against 4.8 / 5.1 on 10,240 x
+# 5,120), until the width of a vocabulary gives it thousands of blocks.
+LOAD_COLUMNS = 4096
 STREAM_K = 3072   # beyond this k the load-based kernel reads W faster than whole rows by bulk copy
 
 
@@ -740,6 +747,8 @@ def gemm_bf16(a: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype = torch.b
     # that the library reads them faster: 8B-shaped decode steps of 9 to 16
     # requests took 5.6 ms, of 18 to 24 requests through the library 5.0)
     few = SKINNY_ROWS if a.shape[1] <= STREAM_K else SKINNY_ROWS // 2
+    if a.shape[1] > STREAM_K and LOAD_COLUMNS < w.shape[0] <= STREAM_COLUMNS:
+        few = 0   # long rows and a middling width: the library reads these faster at any row count
     if (backend == "skinny" or (backend == "auto" and a.shape[0] <= few)) and gemm_skinny_takes(a, w):
         return gemm_skinny(a, w, out_dtype=out_dtype, out=out)
     _need(backend != "skinny", "the weight-streaming kernel does not take this shape")
