@@ -453,3 +453,62 @@ def test_a_routed_feed_forward_and_another_position_encoding(model_folders):
     finally:
         unregister_part("feed_forward", "top1_experts")
         unregister_part("position", "pairwise_rotary")
+
+
+# ------------------------------------------------------- a norm somebody else wrote
+class TorchRMSNorm:
+    """RMSNorm in torch operations, with the interface a norm part must have
+    and nothing more: it says nothing about summands, so the block must hand
+    it the mixer's plain output."""
+
+    def __init__(self, spec, weights, runtime):
+        self.weight = weights.take(spec["weight"]).to(runtime.device, torch.float32)
+        self.eps = float(spec["eps"])
+
+    def forward(self, x, out_dtype, rows_index=None):
+        x = x.float() if rows_index is None else x.float()[rows_index.long()]
+        return (x * torch.rsqrt((x * x).mean(dim=-1, keepdim=True) + self.eps) * self.weight).to(out_dtype)
+
+    def add_forward(self, residual, delta, out_dtype):
+        assert delta is None or delta.dim() == 2, "a norm that does not add summands was handed some"
+        if delta is not None:
+            residual += delta.float()
+        return self.forward(residual, out_dtype)
+
+
+def test_a_norm_that_adds_no_summands_gets_the_mixers_plain_output(model_folders):
+    """Configuration D in bfloat16: decode steps of the engine's own attention
+    leave one summand per head for the engine's own norm to add up; with a
+    norm of another kind behind the mixer of layer 0 that layer's mixer gives
+    its plain output, and the logits still match the plain implementation."""
+    from metallix_b200.config import PartSpec, Qwen3Config
+    from metallix_b200.engine import Engine, StepEntry
+    from metallix_b200.parts import register_part, unregister_part
+    from metallix_b200.weights import load_tensors
+    folder, config, tensors, page = model_folders["D"]
+    typed = Qwen3Config.from_dict(config)
+    register_part("norm", "torch_rmsnorm", TorchRMSNorm)
+    try:
+        base = typed.to_model_spec()
+        layers = list(base.layers)
+        own = layers[0].feed_forward_norm
+        layers[0] = dataclasses.replace(layers[0], feed_forward_norm=PartSpec("torch_rmsnorm", {
+            "weight": own["weight"], "eps": own["eps"]}))
+        spec = dataclasses.replace(base, layers=tuple(layers))
+        engine = Engine(typed, load_tensors(folder, typed, device="cuda:0"), dtype="bfloat16", page_tokens=page,
+                        num_pages=64, spec=spec)
+        assert engine.model.blocks[0].mix == engine.model.blocks[0].mixer.forward
+        assert engine.model.blocks[1].mix == engine.model.blocks[1].mixer.forward_summands
+        ids = {"a": random_ids(21, 90, config["vocab_size"]), "b": random_ids(22, 40, config["vocab_size"])}
+        reference = {k: plain.forward_logits(config, tensors, v) for k, v in ids.items()}
+        engine.step([StepEntry("a", ids["a"][:70], []), StepEntry("b", ids["b"][:20], [])])
+        worst = 0.0
+        for step in range(20):
+            logits = engine.step([StepEntry("a", [ids["a"][70 + step]], [0]),
+                                  StepEntry("b", [ids["b"][20 + step]], [0])]).cpu().double().numpy()
+            worst = max(worst, np.abs(logits[0] - reference["a"][70 + step]).max(),
+                        np.abs(logits[1] - reference["b"][20 + step]).max())
+        engine.check()
+        assert worst < 3e-2
+    finally:
+        unregister_part("norm", "torch_rmsnorm")
