@@ -160,10 +160,16 @@ class Generator:
             tokens: List[int] = []
             if logits is not None:
                 picked = pick(logits, rows, positions)
-                self.engine.check_later()                       # the status word rides behind the tokens
                 host_tokens = self._token_buffer(len(rows))
-                host_tokens.copy_(picked, non_blocking=True)
-                self._tokens_copied.record()
+                # The tokens and the status word go to the host on a stream of
+                # their own, behind the pick: the copy engine's turn does not
+                # stand between this step's last kernel and the next step.
+                self._picked.record()
+                with torch.cuda.stream(self._reader):
+                    self._reader.wait_event(self._picked)
+                    self.engine.check_later()                   # the status word rides with the tokens
+                    host_tokens.copy_(picked, non_blocking=True)
+                    self._tokens_copied.record()
                 foreseen = self._launch_ahead(plan, picked)     # the device goes on while the host reads
                 self._tokens_copied.synchronize()
                 tokens = host_tokens.tolist()
@@ -236,6 +242,8 @@ class Generator:
         if self._host_tokens is None or self._host_tokens.numel() < count:
             self._host_tokens = torch.empty(max(count, 64), dtype=torch.int32, pin_memory=True)
             self._tokens_copied = torch.cuda.Event()
+            self._picked = torch.cuda.Event()
+            self._reader = torch.cuda.Stream(device=self.engine.device)
         return self._host_tokens[:count]
 
     def _launch_ahead(self, plan, picked: torch.Tensor):
