@@ -36,6 +36,7 @@ BUCKETS = (1, 2, 4, 8, 16, 24, 32, 48, 64, 96, 128, 192, 256)
 # construction), each timed on the step's own rows, and the fastest kept.
 PLACEMENTS = 4
 PLACEMENT_REPLAYS = 6
+PLACEMENT_WORTH_MS = 2.0   # a step that takes longer is bound by what it reads, not by where its buffers lie
 _GENERIC = ("ids", "positions", "token_request", "request_slots", "wanted")
 
 
@@ -286,6 +287,8 @@ class DecodeGraphs:
             if best_ms is None or ms < best_ms:
                 best, best_ms = candidate, ms       # the one before goes when its last reference does
             candidate = None
+            if ms >= PLACEMENT_WORTH_MS:
+                break
         self.placement_ms[(size, bound)] = timings
         return best
 
