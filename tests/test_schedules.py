@@ -2,7 +2,7 @@
 decode graphs of 16 rows and more with rows that turn into padding, a general
 step that holds decoded tokens beside portions replayed as a graph, more
 shapes than graphs are kept for, a part that may not ride in a graph, a
-window that gives pages back; and bit-equality of float32 logits wherever one
+window that gives pages back, decode steps captured in several placements; and bit-equality of float32 logits wherever one
 kernel family serves both ways of cutting."""
 import dataclasses
 
@@ -294,3 +294,29 @@ def test_a_windowed_layer_beside_full_ones(model_folders, name, dtype):
     engine.release_all()
     engine.manager.check_invariants()
     assert engine.manager.free_pages(windowed) == pages
+
+
+def test_a_decode_step_is_captured_in_several_placements(model_folders):
+    """The first decode step of a (rows, context) bucket is captured several
+    times and the fastest capture kept; each candidate replays the real step,
+    which must change nothing: the logits are those of an engine that captures
+    once, bit for bit, and the cache goes on from the same state."""
+    from metallix_b200.engine import StepEntry
+    _, config, tensors, page = model_folders["D"]
+    ids = {"a": random_ids(31, 60, config["vocab_size"]), "b": random_ids(32, 45, config["vocab_size"])}
+    outputs = []
+    for placements in (1, 4):
+        engine = make_engine(model_folders, "D", "bfloat16")
+        engine.graphs.placements = placements
+        engine.step([StepEntry("a", ids["a"][:40], []), StepEntry("b", ids["b"][:25], [])])
+        seen = []
+        for step in range(20):
+            logits = engine.step([StepEntry("a", [ids["a"][40 + step]], [0]), StepEntry("b", [ids["b"][25 + step]], [0])])
+            seen.append(logits.cpu().clone())
+        engine.check()
+        timings = engine.graphs.placement_ms
+        assert (len(timings) == 0) if placements == 1 else all(len(t) == 4 for t in timings.values()) and timings
+        outputs.append(torch.stack(seen))
+    assert torch.equal(outputs[0], outputs[1])
+    reference = plain.forward_logits(config, tensors, ids["a"])
+    assert np.abs(outputs[1][:, 0].double().numpy() - reference[40:60]).max() < TOL_BF16_VS_EXACT
