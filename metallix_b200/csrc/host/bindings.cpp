@@ -131,7 +131,7 @@ PYBIND11_MODULE(_mxb_host, m) {
            py::keep_alive<1, 2>())
       .def("add", &Scheduler::add, py::arg("prompt"), py::arg("max_new_tokens"),
            py::arg("stop_ids") = std::vector<int32_t>{}, py::arg("ignore_eos") = false,
-           py::arg("sampling") = SamplingParams{})
+           py::arg("sampling") = SamplingParams{}, py::arg("deadline") = 0.0)
       .def("cancel", &Scheduler::cancel)
       .def("idle", &Scheduler::idle)
       .def("num_waiting", &Scheduler::num_waiting)
@@ -140,7 +140,7 @@ PYBIND11_MODULE(_mxb_host, m) {
       .def("waiting", &Scheduler::waiting)
       .def("request", &Scheduler::request, py::return_value_policy::copy)
       .def("forget", &Scheduler::forget)
-      .def("plan", &Scheduler::plan)
+      .def("plan", &Scheduler::plan, py::arg("now") = 0.0)
       .def("update", &Scheduler::update)
       .def("fail_plan", &Scheduler::fail_plan);
 }

@@ -50,8 +50,9 @@ struct RequestInfo {
   bool ignore_eos = false;
   SamplingParams sampling;
   int preemptions = 0;
-  std::string finish_reason;  // "", "eos", "length", "cancelled", or an error text
+  std::string finish_reason;  // "", "eos", "length", "cancelled", "deadline", or an error text
   bool failed = false;
+  double deadline = 0.0;      // on the caller's clock, seconds; 0: none
 };
 
 struct PlanEntry {
@@ -86,7 +87,7 @@ class Scheduler {
   }
 
   int64_t add(std::vector<int32_t> prompt, int max_new_tokens, std::vector<int32_t> stop_ids,
-              bool ignore_eos, SamplingParams sampling) {
+              bool ignore_eos, SamplingParams sampling, double deadline = 0.0) {
     if (prompt.empty()) throw std::invalid_argument("a request needs at least one prompt token");
     if (max_new_tokens <= 0) throw std::invalid_argument("max_new_tokens must be positive");
     RequestInfo r;
@@ -96,6 +97,7 @@ class Scheduler {
     r.stop_ids = std::move(stop_ids);
     r.ignore_eos = ignore_eos;
     r.sampling = sampling;
+    r.deadline = deadline;
     int64_t id = r.id;
     requests_.emplace(id, std::move(r));
     waiting_.push_back(id);
@@ -120,9 +122,13 @@ class Scheduler {
   // Decides the next step. Changes the cache manager only by releasing
   // preempted, cancelled or failed requests and by admitting (a slot, no
   // pages); the step function reserves the pages the plan was costed for.
-  StepPlan plan() {
+  // `now`: the caller's clock, for the requests that have a deadline: one whose
+  // deadline has passed leaves as a cancelled one does, whether it waits, is
+  // in its prompt or decodes (engine_loop.rs:631-653, :932-943).
+  StepPlan plan(double now = 0.0) {
     StepPlan plan;
     drop_cancelled();
+    drop_overdue(now);
     for (;;) {
       plan_once(plan);
       if (!plan.entries.empty() || running_.empty()) break;
@@ -371,6 +377,15 @@ class Scheduler {
       finish(id, "cancelled");
     }
     cancelled_.clear();
+  }
+
+  void drop_overdue(double now) {
+    std::vector<int64_t> overdue;
+    for (int64_t id : waiting_)
+      if (requests_.at(id).deadline > 0.0 && now >= requests_.at(id).deadline) overdue.push_back(id);
+    for (int64_t id : running_)
+      if (requests_.at(id).deadline > 0.0 && now >= requests_.at(id).deadline) overdue.push_back(id);
+    for (int64_t id : overdue) finish(id, "deadline");
   }
 
   CacheManager* cache_;

@@ -94,8 +94,13 @@ class Generator:
         self._launch_events: Dict[int, tuple] = {}   # id(plan) -> CUDA events around its launch
 
     def add(self, prompt: Sequence[int], max_new_tokens: int, params: SamplingParams = SamplingParams(),
-            eos_ids: Sequence[int] = (), ignore_eos: bool = False) -> int:
+            eos_ids: Sequence[int] = (), ignore_eos: bool = False, deadline_s: Optional[float] = None) -> int:
+        """Queues a request. ``deadline_s``: seconds from now after which the
+        request leaves with finish_reason "deadline", wherever it then is
+        (waiting, in its prompt, decoding), keeping what it has generated."""
         params.validate()
+        if deadline_s is not None and not deadline_s > 0:
+            raise ValueError("deadline_s must be positive")
         prompt = [int(t) for t in prompt]
         vocab = self.engine.spec.vocab_size
         if not prompt:
@@ -109,12 +114,15 @@ class Generator:
         rid = self.scheduler.add(prompt, int(max_new_tokens), [int(e) for e in eos_ids],
                                  bool(ignore_eos),
                                  self.host.SamplingParams(params.temperature, params.seed,
-                                                          params.top_p, params.top_k, code))
+                                                          params.top_p, params.top_k, code),
+                                 0.0 if deadline_s is None else self._clock() + float(deadline_s))
         self._params[rid] = params
         self._limits[rid] = int(max_new_tokens)
         self._timing[rid] = GenerationResult(input_ids=prompt, generated_ids=[], finish_reason="")
         self._started[rid] = time.perf_counter()
         return rid
+
+    _clock = staticmethod(time.perf_counter)   # what deadlines are measured on; a test may set another
 
     def cancel(self, rid: int) -> None:
         self.scheduler.cancel(rid)
@@ -146,7 +154,7 @@ class Generator:
             if self._planned is not None:
                 plan, self._planned = self._planned, None
             else:
-                plan = self.scheduler.plan()
+                plan = self.scheduler.plan(self._clock())
                 self.stats.preemptions += len(plan.preempted)
             if not plan.entries:
                 return []
@@ -186,7 +194,7 @@ class Generator:
         events = self.scheduler.update(plan, tokens)
         if foreseen is not None:
             requests, ahead_logits = foreseen
-            following = self.scheduler.plan()
+            following = self.scheduler.plan(self._clock())
             self.stats.preemptions += len(following.preempted)
             if (not following.preempted and not following.failed
                     and [e.id for e in following.entries] == requests

@@ -128,6 +128,36 @@ def test_eos_stops_and_is_reported(model_folders):
     assert ignored.generated_ids == free_run and ignored.finish_reason == "length"
 
 
+def test_a_deadline_ends_generation_and_keeps_what_was_generated(model_folders):
+    """A request with a deadline leaves when the deadline has passed (the
+    generator's clock is set by hand here), with the tokens it had; the request
+    beside it, launched ahead with it until then, goes on to its limit with the
+    tokens it would have had alone."""
+    from metallix_b200.engine import Engine
+    from metallix_b200.engine.generate import Generator, generate
+    from metallix_b200.sampling import SamplingParams
+    folder, config, tensors, page = model_folders["A"]
+    prompts = [random_ids(51, 9, config["vocab_size"]), random_ids(52, 14, config["vocab_size"])]
+    engine = Engine.from_folder(folder, dtype="float32", page_tokens=page, num_pages=64)
+    alone = [r.generated_ids for r in generate(engine, prompts, max_new_tokens=20, eos_ids=())]
+    generator = Generator(engine, max_num_seqs=2)
+    now = [100.0]
+    generator._clock = lambda: now[0]
+    hurried = generator.add(prompts[0], 20, SamplingParams(), eos_ids=(), deadline_s=5.0)
+    patient = generator.add(prompts[1], 20, SamplingParams(), eos_ids=())
+    for _ in range(6):
+        generator.step()
+    now[0] = 106.0
+    generator.run()
+    first, second = generator.result(hurried), generator.result(patient)
+    assert first.finish_reason == "deadline" and 0 < len(first.generated_ids) < 20
+    assert first.generated_ids == alone[0][:len(first.generated_ids)]
+    assert second.finish_reason == "length" and second.generated_ids == alone[1]
+    assert engine.manager.live_requests() == 0
+    with pytest.raises(ValueError, match="deadline_s"):
+        generator.add(prompts[0], 4, SamplingParams(), deadline_s=0.0)
+
+
 def test_steps_launched_ahead_change_nothing(model_folders):
     """While all requests decode, the generator launches the next step before
     the tokens of this one have reached the host. The tokens are those of a

@@ -206,6 +206,48 @@ def test_cancel_frees_pages(host):
     assert d.manager.free_pages(0) == 32
 
 
+def test_a_deadline_ends_a_request_wherever_it_is(host):
+    """Deadlines on the caller's clock (engine_loop.rs:631-653, :932-943): a
+    request whose deadline has passed leaves at the next plan, keeping what it
+    generated and giving its pages back, whether it decodes, waits or is in its
+    prompt; requests without a deadline go on."""
+    d = Driver(host, pages=32, max_num_seqs=2, max_tokens_per_step=8)
+    sampling = host.SamplingParams()
+    decoding = d.scheduler.add(list(PROMPTS[1]), 50, [], False, sampling, 10.0)
+    free = d.scheduler.add(list(PROMPTS[0]), 6, [], False, sampling)
+    waiting = d.scheduler.add(list(PROMPTS[2]), 6, [], False, sampling, 10.0)
+
+    def step(now):
+        plan = d.scheduler.plan(now)
+        tokens = []
+        for entry in plan.entries:
+            d.manager.reserve(entry.id, len(entry.tokens))
+            d.manager.commit(entry.id, len(entry.tokens))
+            info = d.scheduler.request(entry.id)
+            if entry.wants_token:
+                tokens.append(next_token(list(info.prompt) + list(info.output)))
+        d.scheduler.update(plan, tokens)
+
+    for now in (1.0, 2.0, 3.0, 9.9):
+        step(now)
+    assert d.scheduler.request(decoding).finish_reason == "" and d.scheduler.waiting() == [waiting]
+    generated = len(d.scheduler.request(decoding).output)
+    step(10.0)
+    assert d.scheduler.request(decoding).finish_reason == "deadline"
+    assert d.scheduler.request(waiting).finish_reason == "deadline"
+    assert len(d.scheduler.request(decoding).output) == generated and not d.manager.has(decoding)
+    while not d.scheduler.idle():
+        step(11.0)
+    assert d.output(free) == serial(PROMPTS[0], 6) and d.scheduler.request(free).finish_reason == "length"
+    assert d.manager.free_pages(0) == 32
+    # in its prompt: portions of 8 tokens, the deadline passes after the first
+    long_prompt = d.scheduler.add([3] * 30, 4, [], False, sampling, 20.0)
+    step(19.0)
+    assert d.manager.has(long_prompt) and 0 < d.manager.computed(long_prompt) < 30
+    step(20.5)
+    assert d.scheduler.request(long_prompt).finish_reason == "deadline" and d.manager.free_pages(0) == 32
+
+
 def test_failed_step_releases_its_requests(host):
     d = Driver(host, pages=32, max_num_seqs=2)
     a = d.add(PROMPTS[0], 4)
