@@ -68,6 +68,10 @@ def build_parser() -> argparse.ArgumentParser:
     gen.add_argument("--max-tokens-per-step", type=int, default=8192)
     gen.add_argument("--prefill-chunk-tokens", type=int, default=0,
                      help="most prompt tokens of one request per step; 0: no cap")
+    gen.add_argument("--context-tokens", type=int, default=0,
+                     help="the longest context the engine is laid out for; 0: the longest prompt plus --max-tokens")
+    gen.add_argument("--generation-timeout-ms", type=float, default=0.0,
+                     help="a request leaves with finish_reason 'deadline' this long after it was queued; 0: never")
     gen.add_argument("--eos-ids", type=_ids, help="stop ids; default: the configuration's")
     gen.add_argument("--ignore-eos", action="store_true")
     gen.add_argument("--verify-cache", action="store_true",
@@ -155,7 +159,9 @@ def run_gen(args) -> int:
         options["pool_bytes"] = args.kv_pool_mib * 2 ** 20
     # Rotation tables and graphs are laid out for the contexts this call can reach.
     longest = max(len(prompt) for prompt in prompts) + args.max_tokens
-    options["max_context"] = max(-(-longest // 256) * 256, 256)
+    if args.context_tokens and args.context_tokens < longest:
+        raise SystemExit(f"--context-tokens {args.context_tokens} is below the longest prompt plus --max-tokens ({longest})")
+    options["max_context"] = max(-(-max(longest, args.context_tokens) // 256) * 256, 256)
     if args.model:
         engine = Engine.from_folder(args.model, **options)
     else:
@@ -167,7 +173,8 @@ def run_gen(args) -> int:
                        seed=args.seed or 0, top_p=args.top_p, top_k=args.top_k,
                        sampler=args.sampler, eos_ids=args.eos_ids, ignore_eos=args.ignore_eos,
                        max_num_seqs=args.max_num_seqs, max_tokens_per_step=args.max_tokens_per_step,
-                       prefill_chunk=args.prefill_chunk_tokens, trace_out=args.trace_out)
+                       prefill_chunk=args.prefill_chunk_tokens, trace_out=args.trace_out,
+                       deadline_s=args.generation_timeout_ms / 1e3 if args.generation_timeout_ms > 0 else None)
     from ..config.registry import resolve
     family = resolve(config.to_dict()).model_type   # "qwen3": the reference's receipts name the family so
     checker, verified = None, True

@@ -327,11 +327,14 @@ def generate(engine: Engine, prompts: Sequence[Sequence[int]], max_new_tokens: i
              temperature: float = 0.0, seed: int = 0, top_p: float = 1.0, top_k: int = 0,
              sampler: str = "icdf", eos_ids: Optional[Sequence[int]] = None,
              ignore_eos: bool = False, max_num_seqs: int = 8, max_tokens_per_step: int = 8192,
-             prefill_chunk: int = 0, run_ahead: bool = True, trace_out: Optional[str] = None) -> List[GenerationResult]:
+             prefill_chunk: int = 0, run_ahead: bool = True, trace_out: Optional[str] = None,
+             deadline_s: Optional[float] = None) -> List[GenerationResult]:
     """Generates for every prompt (lists of token ids) and returns the results
     in the prompts' order. ``temperature`` 0 is greedy; otherwise request i
     draws from (seed, stream i). ``eos_ids`` defaults to the configuration's.
-    ``trace_out``: a file for the timeline of the steps (``Generator.write_trace``)."""
+    ``trace_out``: a file for the timeline of the steps (``Generator.write_trace``).
+    ``deadline_s``: every request leaves with finish_reason "deadline" that long
+    after it was queued, as the reference's --generation-timeout-ms."""
     if eos_ids is None:
         eos_ids = tuple(getattr(engine.config, "eos_token_ids", ()) or ())
     generator = Generator(engine, max_num_seqs=max_num_seqs,
@@ -340,7 +343,7 @@ def generate(engine: Engine, prompts: Sequence[Sequence[int]], max_new_tokens: i
     ids = [generator.add(prompt, max_new_tokens,
                          SamplingParams(temperature=temperature, seed=seed, stream=index,
                                         top_p=top_p, top_k=top_k, sampler=sampler),
-                         eos_ids=eos_ids, ignore_eos=ignore_eos)
+                         eos_ids=eos_ids, ignore_eos=ignore_eos, deadline_s=deadline_s)
            for index, prompt in enumerate(prompts)]
     generator.run()
     if trace_out is not None:

@@ -227,6 +227,7 @@ def test_command_line(model_folders, tmp_path):
     result = subprocess.run([sys.executable, os.path.join(ROOT, "bin", "mxb"), "gen", "--model", folder,
                              "--input-ids", ",".join(map(str, prompt)), "--max-tokens", "6",
                              "--dtype", "float32", "--block-size", str(page), "--num-pages", "32",
+                             "--context-tokens", "100", "--generation-timeout-ms", "600000",
                              "--verify-cache", "--trace-out", str(tmp_path / "trace.json")],
                             capture_output=True, text=True, timeout=600)
     assert result.returncode == 0, result.stderr[-2000:]
