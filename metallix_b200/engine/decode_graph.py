@@ -268,7 +268,10 @@ class DecodeGraphs:
         candidate = first
         for attempt in range(tries):
             if candidate is None:
-                candidate = self._capture(size, bound, pool=None)   # memory of its own, beside the others'
+                try:
+                    candidate = self._capture(size, bound, pool=None)   # memory of its own, beside the others'
+                except torch.cuda.OutOfMemoryError:
+                    break   # no room for another placement: the best so far serves
             stage = candidate.staging[0]
             self._host_fill(candidate, rows, stage)
             stage["filled"] = len(rows)
