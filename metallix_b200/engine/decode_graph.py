@@ -34,7 +34,7 @@ BUCKETS = (1, 2, 4, 8, 16, 24, 32, 48, 64, 96, 128, 192, 256)
 # weights and the cache where they were. So a step is captured this many times,
 # each capture's buffers alive beside the others (different memory by
 # construction), each timed on the step's own rows, and the fastest kept.
-PLACEMENTS = 4
+PLACEMENTS = 8             # at most; fewer once one capture has come out 2% faster than another
 PLACEMENT_REPLAYS = 6
 PLACEMENT_WORTH_MS = 2.0   # a step that takes longer is bound by what it reads, not by where its buffers lie
 _GENERIC = ("ids", "positions", "token_request", "request_slots", "wanted")
@@ -290,8 +290,8 @@ class DecodeGraphs:
             if best_ms is None or ms < best_ms:
                 best, best_ms = candidate, ms       # the one before goes when its last reference does
             candidate = None
-            if ms >= PLACEMENT_WORTH_MS:
-                break
+            if ms >= PLACEMENT_WORTH_MS or best_ms <= 0.98 * max(timings):
+                break   # too long a step to gain, or both of the two times have been seen
         self.placement_ms[(size, bound)] = timings
         return best
 

@@ -315,7 +315,7 @@ def test_a_decode_step_is_captured_in_several_placements(model_folders):
             seen.append(logits.cpu().clone())
         engine.check()
         timings = engine.graphs.placement_ms
-        assert (len(timings) == 0) if placements == 1 else all(len(t) == 4 for t in timings.values()) and timings
+        assert (len(timings) == 0) if placements == 1 else all(2 <= len(t) <= 4 for t in timings.values()) and timings
         outputs.append(torch.stack(seen))
     assert torch.equal(outputs[0], outputs[1])
     reference = plain.forward_logits(config, tensors, ids["a"])
