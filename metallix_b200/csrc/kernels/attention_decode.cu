@@ -909,7 +909,8 @@ paged_attention_decode_resident_kernel(const __grid_constant__ CUtensorMap map_c
       l_all += weight * theirs[HD + 1];
     }
     const int head = kv * group + h;
-    float* dst_partial = partial + ((static_cast<size_t>(row) * heads + head) * max_splits + rank) * (HD + 2);
+    // the blocks of a pair lie side by side: gridDim.x partial results a pair, not max_splits
+    float* dst_partial = partial + ((static_cast<size_t>(row) * heads + head) * gridDim.x + rank) * (HD + 2);
     dst_partial[d] = sum;
     if (d == 0) { dst_partial[HD] = m_all * 0.6931471805599453f; dst_partial[HD + 1] = l_all; }  // the merge kernel works in natural units
   }
@@ -948,7 +949,8 @@ paged_attention_merge_kernel(const float* __restrict__ partial, T* __restrict__ 
   // resident kernel: slot s gathered the tiles first + s, first + s + slots, ...
   const int splits = slots > 0 ? min(slots, last_split - first_split + 1) : last_split - first_split + 1;
   const int stride = head_dim + 2;
-  const float* base = partial + ((static_cast<size_t>(row) * heads + head) * max_splits + (slots > 0 ? 0 : first_split)) * stride;
+  const float* base = partial + (slots > 0 ? (static_cast<size_t>(row) * heads + head) * slots
+                                            : (static_cast<size_t>(row) * heads + head) * max_splits + first_split) * stride;
   chain_wait();
   base = behind_wait(base);  // the partial results are written by the kernel ahead of this one
   float m = kDecodeMinusHuge, acc = 0.0f, l = 0.0f;

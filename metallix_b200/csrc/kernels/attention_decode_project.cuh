@@ -82,7 +82,8 @@ decode_merge_project_kernel(const float* __restrict__ partial, const __nv_bfloat
     }
     turn_token[turn] = token;
     turn_splits[turn] = slots > 0 ? min(slots, last_split - first_split + 1) : last_split - first_split + 1;
-    turn_base[turn] = ((static_cast<size_t>(row) * heads + head) * max_splits + (slots > 0 ? 0 : first_split)) * stride;
+    turn_base[turn] = (slots > 0 ? (static_cast<size_t>(row) * heads + head) * slots
+                                 : (static_cast<size_t>(row) * heads + head) * max_splits + first_split) * stride;
   }
   chain_wait();
   partial = behind_wait(partial);  // written by the attention kernel ahead of this one
