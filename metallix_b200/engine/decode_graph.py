@@ -29,11 +29,11 @@ from ..parts.registry import StepContext, StepPlan, block_parts, graph_safe
 
 BUCKETS = (1, 2, 4, 8, 16, 24, 32, 48, 64, 96, 128, 192, 256)
 # A captured decode step runs in one of two times some 4% apart (0.87 or 0.90
-# ms for 8 requests at the 0.6B shapes), whichever memory its buffers were
-# given: the same engine recaptures the same step faster or slower, with the
-# weights and the cache where they were. So a step is captured this many times,
-# each capture's buffers alive beside the others (different memory by
-# construction), each timed on the step's own rows, and the fastest kept.
+# ms for 8 requests at the 0.6B shapes): the same engine recaptures the same
+# step faster or slower, with the weights, the cache and the kernels' own
+# times unchanged; what differs lies between the kernels of the replayed graph.
+# So a step is captured several times, each capture alive beside the others,
+# each timed on the step's own rows, and the fastest kept.
 PLACEMENTS = 8             # at most; fewer once one capture has come out 2% faster than another
 PLACEMENT_REPLAYS = 6
 PLACEMENT_WORTH_MS = 2.0   # a step that takes longer is bound by what it reads, not by where its buffers lie
