@@ -296,6 +296,54 @@ def test_a_windowed_layer_beside_full_ones(model_folders, name, dtype):
     assert engine.manager.free_pages(windowed) == pages
 
 
+def test_a_fork_under_a_window(model_folders):
+    """A request forked behind a window: in the windowed group the child
+    shares only the pages the window still covers (and copies the partial
+    one), in the full group all of them; both go their own ways and match the
+    plain implementation; ending the parent leaves the child whole."""
+    from metallix_b200.config import PartSpec, Qwen3Config
+    from metallix_b200.engine import Engine, StepEntry
+    from metallix_b200.weights import load_tensors
+    folder, config, tensors, page = model_folders["D"]
+    typed = Qwen3Config.from_dict(config)
+    base = typed.to_model_spec()
+    layers = list(base.layers)
+    window = 40
+    layers[0] = dataclasses.replace(layers[0], mixer=PartSpec("gqa_attention", dict(layers[0].mixer.params, window=window)))
+    spec = dataclasses.replace(base, layers=tuple(layers))
+    windows = [window if layer == 0 else None for layer in range(config["num_hidden_layers"])]
+    vocab = config["vocab_size"]
+    shared = random_ids(71, 107, vocab)                    # 6 pages of 16 and 11 positions of a seventh
+    ways = {"parent": shared + random_ids(72, 30, vocab), "child": shared + random_ids(73, 60, vocab)}
+    reference = {k: plain_with_windows(config, tensors, v, windows) for k, v in ways.items()}
+    engine = Engine(typed, load_tensors(folder, typed, device="cuda:0"), dtype="float32", page_tokens=page,
+                    num_pages=24, max_requests=4, spec=spec)
+    windowed = [g.index for g in engine.cache.groups if g.need.window][0]
+    full = 1 - windowed
+    engine.step([StepEntry("parent", shared, [])])
+    engine.fork("parent", "child")
+    parent_id, child_id = engine._ids["parent"], engine._ids["child"]
+    held = engine.manager.table(parent_id, windowed)
+    assert held[0] == -1 and engine.manager.table(child_id, windowed)[0] == -1
+    assert engine.manager.table(child_id, full)[:6] == engine.manager.table(parent_id, full)[:6]
+    assert engine.manager.table(child_id, full)[6] != engine.manager.table(parent_id, full)[6]
+    worst = 0.0
+    for step in range(30):
+        logits = engine.step([StepEntry("parent", [ways["parent"][107 + step]], [0]),
+                              StepEntry("child", [ways["child"][107 + step]], [0])]).cpu().double().numpy()
+        worst = max(worst, np.abs(logits[0] - reference["parent"][107 + step]).max(),
+                    np.abs(logits[1] - reference["child"][107 + step]).max())
+    engine.release("parent")
+    for step in range(30, 60):
+        logits = engine.step([StepEntry("child", [ways["child"][107 + step]], [0])]).cpu().double().numpy()
+        worst = max(worst, np.abs(logits[0] - reference["child"][107 + step]).max())
+    engine.check()
+    engine.manager.check_invariants()
+    engine.release_all()
+    assert engine.manager.free_pages(windowed) == 24 and engine.manager.free_pages(full) == 24
+    assert worst < TOL_F32
+
+
 def test_a_decode_step_is_captured_in_several_placements(model_folders):
     """The first decode step of a (rows, context) bucket is captured several
     times and the fastest capture kept; each candidate replays the real step,
